@@ -1,0 +1,181 @@
+/* weta_b200.h -- C ABI of the B200-native tensor-operator backend for weta.
+ *
+ * Every entry point below stands in for one method of `weta_core::Backend`
+ * (crates/weta-core/src/backend.rs:65-106) or for one piece of glue the reference CUDA crate
+ * exposes to `weta-tensor` (crates/weta-cuda/src/lib.rs:129-156).  The citation on each
+ * declaration names the reference interface it replaces.  Entry points under "extension" have
+ * no trait method today: in Rust they would be default-bodied trait methods, the way `random`
+ * already is (backend.rs:94-105), so existing crates keep compiling.
+ *
+ * Conventions (same as the trait, backend.rs:59-64):
+ *   - shapes, strides and offsets count ELEMENTS, at most WB_MAX_DIMS dimensions;
+ *   - inputs are strided views (stride 0 = broadcast); every op produces fresh contiguous output;
+ *   - all work is asynchronous on the backend's one stream; only wb_to_host / wb_synchronize wait;
+ *   - every function returns a WbStatus; on failure wb_last_error() holds the message (per thread).
+ *     The reference panics where this ABI returns non-zero (e.g. lib.rs:207, 387, 518).
+ *   - there is no CPU fallback: without a usable CUDA device wb_backend_create fails with
+ *     WB_ERR_DEVICE_UNAVAILABLE, the counterpart of Error::DeviceUnavailable (lib.rs:131-133).
+ */
+#ifndef WETA_B200_H
+#define WETA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WB_MAX_DIMS 8 /* crates/weta-cuda/src/lib.rs:67 */
+
+typedef enum WbStatus {
+    WB_OK = 0,
+    WB_ERR_INVALID = 1,            /* bad argument (shape/dtype mismatch, null pointer) */
+    WB_ERR_UNSUPPORTED = 2,        /* op not defined for this dtype (the reference panics) */
+    WB_ERR_CUDA = 3,               /* a CUDA call failed */
+    WB_ERR_OOM = 4,
+    WB_ERR_DEVICE_UNAVAILABLE = 5, /* weta_core::Error::DeviceUnavailable */
+    WB_ERR_TIMEOUT = 6             /* a bounded device-side wait ran out */
+} WbStatus;
+
+/* crates/weta-core/src/dtype.rs:9-14 */
+typedef enum WbDType { WB_F32 = 0, WB_F64 = 1, WB_I64 = 2 } WbDType;
+
+/* crates/weta-core/src/ops.rs:7-36, numbered as crates/weta-cuda/src/lib.rs:256-278.
+ * AFFINE uses (p1, p2) = (mul, add); POWF, GT_SCALAR, MAX_SCALAR, MIN_SCALAR use p1. */
+typedef enum WbUnaryOp {
+    WB_NEG = 0, WB_EXP, WB_LOG, WB_SQRT, WB_ABS, WB_SIGN, WB_RELU, WB_STEP, WB_TANH, WB_SIGMOID, WB_ERF,
+    WB_SIN, WB_COS, WB_RECIP, WB_AFFINE, WB_POWF, WB_GT_SCALAR, WB_MAX_SCALAR, WB_MIN_SCALAR
+} WbUnaryOp;
+
+/* crates/weta-core/src/ops.rs:68-82, numbered as crates/weta-cuda/src/lib.rs:280-296 */
+typedef enum WbBinaryOp {
+    WB_ADD = 0, WB_SUB, WB_MUL, WB_DIV, WB_POW, WB_MAXIMUM, WB_MINIMUM, WB_EQ, WB_NE, WB_LT, WB_LE, WB_GT, WB_GE
+} WbBinaryOp;
+
+/* crates/weta-core/src/ops.rs:106-112 */
+typedef enum WbReduceOp { WB_SUM = 0, WB_MAX, WB_MIN, WB_ARGMAX, WB_ARGMIN } WbReduceOp;
+
+/* crates/weta-core/src/ops.rs:154-157 */
+typedef enum WbDistribution { WB_UNIFORM = 0 /* a = lo, b = hi */, WB_NORMAL = 1 /* a = mean, b = std */ } WbDistribution;
+
+/* How float32 contractions are evaluated.  The reference calls cuBLAS in its default FP32 mode
+ * (crates/weta-cuda/src/lib.rs:351-389). */
+typedef enum WbMatmulMode {
+    WB_MM_TF32X3 = 0, /* tcgen05 kind::tf32, three products per term: FP32-grade accuracy (default) */
+    WB_MM_TF32 = 1,   /* tcgen05 kind::tf32, one product per term */
+    WB_MM_FP32 = 2    /* CUDA-core FP32 FMA tiles (also what f64 and irregular layouts use) */
+} WbMatmulMode;
+
+/* A strided look at device memory: crates/weta-core/src/backend.rs:4-8 (`View`) with the layout
+ * of crates/weta-core/src/layout.rs:16-21 flattened the way the reference's kernels receive it
+ * (`Strides`, crates/weta-cuda/src/lib.rs:52-61).  `data` is the storage's base device pointer. */
+typedef struct WbView {
+    void* data;
+    int32_t dtype;
+    int32_t ndim;
+    int64_t shape[WB_MAX_DIMS];
+    int64_t stride[WB_MAX_DIMS];
+    int64_t offset;
+} WbView;
+
+/* crates/weta-core/src/ops.rs:122-128 (`Im2ColParams`) */
+typedef struct WbConvParams {
+    int64_t kh, kw, sh, sw, ph, pw, dh, dw;
+} WbConvParams;
+
+typedef struct WbBackend WbBackend; /* crates/weta-cuda/src/lib.rs:122-127 (`CudaBackend`) */
+typedef struct WbStorage WbStorage; /* crates/weta-cuda/src/lib.rs:26-48 (`CudaStorage`) */
+
+/* ---- device and backend ------------------------------------------------------------------ */
+
+/* weta_cuda::device_count (lib.rs:149-152): 0 when no driver or no device. */
+int wb_device_count(void);
+/* weta_cuda::backend(ordinal) (lib.rs:137-146, 176-192): context, stream, kernels.  The kernels
+ * are AOT sm_100a code inside this library; nothing is compiled at run time. */
+int wb_backend_create(int ordinal, WbBackend** out);
+/* Same, but all work goes to the caller's CUDA stream (a cudaStream_t), so a host framework can
+ * order its own copies and collectives against the backend's kernels. */
+int wb_backend_create_on_stream(int ordinal, void* cuda_stream, WbBackend** out);
+int wb_backend_destroy(WbBackend* b);
+int wb_backend_ordinal(const WbBackend* b);   /* CudaStorage::ordinal (lib.rs:38-40) */
+void* wb_backend_stream(const WbBackend* b);  /* the cudaStream_t every op is issued on */
+int wb_synchronize(WbBackend* b);
+const char* wb_last_error(void);
+/* weta_cuda::profile_report (crates/weta-cuda/src/profile.rs:58-73): per-op call counts and
+ * device time.  Profiling is on when wb_set_profiling(b, 1) was called or WETA_B200_PROFILE=1. */
+int wb_set_profiling(WbBackend* b, int on);
+const char* wb_profile_report(WbBackend* b);
+int wb_set_matmul_mode(WbBackend* b, int mode);
+int wb_get_matmul_mode(const WbBackend* b);
+/* Number of kernels this backend has launched since creation (for launch accounting). */
+int64_t wb_launch_count(const WbBackend* b);
+
+/* ---- storage (Backend::Storage) ----------------------------------------------------------- */
+
+/* `uninit` (lib.rs:204-208): uninitialised device storage from the stream-ordered arena.
+ * Zero-length requests get one element, like the reference (lib.rs:206-207). */
+int wb_alloc(WbBackend* b, int64_t len, int dtype, WbStorage** out);
+/* Backend::zeros (backend.rs:74; lib.rs:457-461) */
+int wb_zeros(WbBackend* b, int64_t len, int dtype, WbStorage** out);
+/* Drop of CudaStorage: the block returns to the arena, ordered after queued work. */
+int wb_free(WbBackend* b, WbStorage* s);
+/* Wraps device memory owned by someone else (no copy, never freed by the backend). */
+int wb_storage_wrap(WbBackend* b, void* device_ptr, int64_t len, int dtype, WbStorage** out);
+void* wb_storage_data(const WbStorage* s);
+int64_t wb_storage_len(const WbStorage* s);
+int wb_storage_dtype(const WbStorage* s);
+/* Backend::from_host (backend.rs:71; lib.rs:423-434): `host` holds `len` elements of `dtype`. */
+int wb_from_host(WbBackend* b, const void* host, int64_t len, int dtype, WbStorage** out);
+/* Backend::to_host (backend.rs:73; lib.rs:436-455): elements of the view in row-major order. */
+int wb_to_host(WbBackend* b, const WbView* x, void* host_out);
+/* Asynchronous variants for pinned host buffers (ordered on the backend stream, no wait). */
+int wb_upload_async(WbBackend* b, const void* pinned_host, void* device_dst, int64_t bytes);
+int wb_download_async(WbBackend* b, const void* device_src, void* pinned_host, int64_t bytes);
+int64_t wb_arena_bytes_reserved(const WbBackend* b);
+
+/* ---- the trait's kernels ------------------------------------------------------------------ */
+/* Each op exists twice: `wb_x(..., WbStorage** out)` allocates the fresh contiguous result like
+ * the trait method does; `wb_x_into(..., void* out)` writes it to caller-provided device memory
+ * of the right size and allocates nothing. */
+
+/* Backend::copy_strided (backend.rs:79; lib.rs:463-480): dst view elements <- src view elements. */
+int wb_copy_strided(WbBackend* b, const WbView* src, const WbView* dst);
+/* Backend::unary (backend.rs:81; lib.rs:482-494; CPU semantics crates/weta-cpu/src/lib.rs:133-203) */
+int wb_unary(WbBackend* b, int op, double p1, double p2, const WbView* x, WbStorage** out);
+int wb_unary_into(WbBackend* b, int op, double p1, double p2, const WbView* x, void* out);
+/* Backend::binary (backend.rs:83; lib.rs:496-521; CPU semantics weta-cpu/src/lib.rs:205-241) */
+int wb_binary(WbBackend* b, int op, const WbView* a, const WbView* bb, WbStorage** out);
+int wb_binary_into(WbBackend* b, int op, const WbView* a, const WbView* bb, void* out);
+/* Backend::reduce (backend.rs:85; lib.rs:523-580; CPU semantics weta-cpu/src/lib.rs:245-300).
+ * ARGMAX/ARGMIN produce i64. */
+int wb_reduce(WbBackend* b, int op, const WbView* x, int axis, WbStorage** out);
+int wb_reduce_into(WbBackend* b, int op, const WbView* x, int axis, void* out);
+/* Backend::matmul (backend.rs:87; lib.rs:603-628): [B,M,K] x [B,K,N] -> [B,M,N], any strides,
+ * batch stride 0 allowed; f32 and f64. */
+int wb_matmul(WbBackend* b, const WbView* a, const WbView* bb, WbStorage** out);
+int wb_matmul_into(WbBackend* b, const WbView* a, const WbView* bb, void* out);
+/* Backend::im2col (backend.rs:89; lib.rs:630-642; weta-cpu/src/lib.rs:367-408) */
+int wb_im2col(WbBackend* b, const WbView* x, const WbConvParams* p, WbStorage** out);
+int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams* p, void* out);
+/* Backend::col2im (backend.rs:91; lib.rs:644-656; weta-cpu/src/lib.rs:410-446) */
+int wb_col2im(WbBackend* b, const WbView* cols, const WbConvParams* p, int64_t c, int64_t h, int64_t w, WbStorage** out);
+int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvParams* p, int64_t c, int64_t h, int64_t w, void* out);
+/* Backend::cast (backend.rs:92; lib.rs:658-679; weta-cpu/src/lib.rs:552-565); same dtype = contiguous(). */
+int wb_cast(WbBackend* b, const WbView* x, int dtype, WbStorage** out);
+int wb_cast_into(WbBackend* b, const WbView* x, int dtype, void* out);
+/* Backend::random (backend.rs:97-105; lib.rs:582-601; crates/weta-core/src/ops.rs:164-189):
+ * element i = Distribution::sample(seed, i), bit-identical to the CPU backend for uniform fills. */
+int wb_random(WbBackend* b, int64_t len, int dtype, int dist, double pa, double pb, uint64_t seed, WbStorage** out);
+int wb_random_into(WbBackend* b, int64_t len, int dtype, int dist, double pa, double pb, uint64_t seed, void* out);
+
+/* ---- host RNG seed stream (crates/weta-tensor/src/random.rs:21-110) ----------------------- */
+typedef struct WbPcg { uint64_t state, inc; } WbPcg;
+void wb_pcg_seed(WbPcg* g, uint64_t seed); /* Rng::new */
+uint32_t wb_pcg_next_u32(WbPcg* g);
+uint64_t wb_pcg_next_u64(WbPcg* g);        /* the per-tensor seed */
+uint64_t wb_splitmix64(uint64_t seed, uint64_t i); /* crates/weta-core/src/ops.rs:164-169 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WETA_B200_H */

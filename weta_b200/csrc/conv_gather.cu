@@ -1,0 +1,149 @@
+// Backend::im2col and Backend::col2im (crates/weta-core/src/backend.rs:89-91).
+//
+// im2col is a pure gather: out[n][c*kh*kw + ki*kw + kj][oy*OW + ox] = x[n][c][oy*s - p + ki*d][ox*s - p + kj*d]
+// or 0 outside the image (crates/weta-cpu/src/lib.rs:367-408), so results are bit-exact.  Threads run
+// along the output's inner (oy, ox) index, which makes the stores coalesced and, for unit stride,
+// the loads too.
+// col2im is its adjoint.  The CPU loops (ki, kj) outermost and adds into the image
+// (crates/weta-cpu/src/lib.rs:410-446); for one pixel that is a sum over (ki, kj) ascending, which the
+// gather form below reproduces without atomics: same order, same roundings.
+#include "common.h"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+struct GP {
+    int64_t n, c, h, w, kh, kw, sh, sw, ph, pw, dh, dw, oh, ow;
+    int64_t xs0, xs1, xs2, xs3, xoff;  // input strides (elements)
+};
+
+template <class T>
+__global__ void __launch_bounds__(THREADS) im2col_kernel(T* __restrict__ out, const T* __restrict__ x, GP p, int64_t total) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+    if (i >= total) return;
+    int64_t l = p.oh * p.ow;
+    int64_t col = i % l;
+    int64_t r = i / l;
+    int64_t kk = p.kh * p.kw;
+    int64_t kidx = r % kk;
+    int64_t nc = r / kk;
+    int64_t ci = nc % p.c, n = nc / p.c;
+    int64_t ki = kidx / p.kw, kj = kidx % p.kw;
+    int64_t oy = col / p.ow, ox = col % p.ow;
+    int64_t iy = oy * p.sh + ki * p.dh - p.ph;
+    int64_t ix = ox * p.sw + kj * p.dw - p.pw;
+    T v = T(0);
+    if (iy >= 0 && iy < p.h && ix >= 0 && ix < p.w) v = x[p.xoff + n * p.xs0 + ci * p.xs1 + iy * p.xs2 + ix * p.xs3];
+    out[i] = v;
+}
+
+// cols: contiguous [N, C*kh*kw, OH*OW] or strided (cs0, cs1, cs2).
+template <class T>
+__global__ void __launch_bounds__(THREADS) col2im_kernel(T* __restrict__ out, const T* __restrict__ cols, GP p, int64_t cs0,
+                                                          int64_t cs1, int64_t cs2, int64_t coff, int64_t total) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+    if (i >= total) return;
+    int64_t ix = i % p.w;
+    int64_t t = i / p.w;
+    int64_t iy = t % p.h;
+    t /= p.h;
+    int64_t ci = t % p.c, n = t / p.c;
+    T acc = T(0);
+    const T* base = cols + coff + n * cs0 + ci * p.kh * p.kw * cs1;
+    for (int64_t ki = 0; ki < p.kh; ++ki) {
+        int64_t ny = iy + p.ph - ki * p.dh;
+        if (ny < 0 || ny % p.sh != 0) continue;
+        int64_t oy = ny / p.sh;
+        if (oy >= p.oh) continue;
+        for (int64_t kj = 0; kj < p.kw; ++kj) {
+            int64_t nx = ix + p.pw - kj * p.dw;
+            if (nx < 0 || nx % p.sw != 0) continue;
+            int64_t ox = nx / p.sw;
+            if (ox >= p.ow) continue;
+            acc = acc + base[(ki * p.kw + kj) * cs1 + (oy * p.ow + ox) * cs2];
+        }
+    }
+    out[i] = acc;
+}
+
+inline int64_t out_size1(int64_t x, int64_t k, int64_t s, int64_t p, int64_t d) {  // crates/weta-core/src/ops.rs:136-149
+    int64_t span = d * (k - 1) + 1;
+    if (x + 2 * p < span) return 0;
+    return (x + 2 * p - span) / s + 1;
+}
+
+GP make_gp(const WbConvParams& cp, int64_t n, int64_t c, int64_t h, int64_t w) {
+    GP p{};
+    p.n = n; p.c = c; p.h = h; p.w = w;
+    p.kh = cp.kh; p.kw = cp.kw; p.sh = cp.sh; p.sw = cp.sw; p.ph = cp.ph; p.pw = cp.pw; p.dh = cp.dh; p.dw = cp.dw;
+    p.oh = out_size1(h, cp.kh, cp.sh, cp.ph, cp.dh);
+    p.ow = out_size1(w, cp.kw, cp.sw, cp.pw, cp.dw);
+    return p;
+}
+
+bool params_ok(const WbConvParams* p) { return p && p->kh > 0 && p->kw > 0 && p->sh > 0 && p->sw > 0 && p->dh > 0 && p->dw > 0 && p->ph >= 0 && p->pw >= 0; }
+
+}  // namespace
+
+extern "C" int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams* cp, void* out) {
+    WB_REQUIRE(b && x && out, WB_ERR_INVALID, "wb_im2col: null pointer");
+    WB_REQUIRE(params_ok(cp), WB_ERR_INVALID, "im2col: kernel, stride and dilation must be positive");
+    WB_REQUIRE(x->ndim == 4, WB_ERR_INVALID, "im2col: expected [N, C, H, W], got %d dims", x->ndim);
+    GP p = make_gp(*cp, x->shape[0], x->shape[1], x->shape[2], x->shape[3]);
+    p.xs0 = x->stride[0]; p.xs1 = x->stride[1]; p.xs2 = x->stride[2]; p.xs3 = x->stride[3]; p.xoff = x->offset;
+    int64_t total = p.n * p.c * p.kh * p.kw * p.oh * p.ow;
+    if (total == 0) return WB_OK;
+    WbProfileScope ps(b, "im2col");
+    unsigned grid = static_cast<unsigned>((total + THREADS - 1) / THREADS);
+    switch (x->dtype) {
+        case WB_F32: im2col_kernel<float><<<grid, THREADS, 0, b->stream>>>(static_cast<float*>(out), static_cast<const float*>(x->data), p, total); break;
+        case WB_F64: im2col_kernel<double><<<grid, THREADS, 0, b->stream>>>(static_cast<double*>(out), static_cast<const double*>(x->data), p, total); break;
+        case WB_I64: im2col_kernel<int64_t><<<grid, THREADS, 0, b->stream>>>(static_cast<int64_t*>(out), static_cast<const int64_t*>(x->data), p, total); break;
+        default: wb_set_error("im2col: unknown dtype %d", x->dtype); return WB_ERR_INVALID;
+    }
+    WB_LAUNCH_OK(b);
+    return WB_OK;
+}
+
+extern "C" int wb_im2col(WbBackend* b, const WbView* x, const WbConvParams* cp, WbStorage** out) {
+    WB_REQUIRE(b && x && out && params_ok(cp), WB_ERR_INVALID, "wb_im2col: bad arguments");
+    WB_REQUIRE(x->ndim == 4, WB_ERR_INVALID, "im2col: expected [N, C, H, W], got %d dims", x->ndim);
+    GP p = make_gp(*cp, x->shape[0], x->shape[1], x->shape[2], x->shape[3]);
+    WB_TRY(wb_new_storage(b, p.n * p.c * p.kh * p.kw * p.oh * p.ow, x->dtype, out));
+    int s = wb_im2col_into(b, x, cp, (*out)->ptr);
+    if (s != WB_OK) { wb_free(b, *out); *out = nullptr; }
+    return s;
+}
+
+extern "C" int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvParams* cp, int64_t c, int64_t h, int64_t w, void* out) {
+    WB_REQUIRE(b && cols && out, WB_ERR_INVALID, "wb_col2im: null pointer");
+    WB_REQUIRE(params_ok(cp), WB_ERR_INVALID, "col2im: kernel, stride and dilation must be positive");
+    WB_REQUIRE(cols->ndim == 3, WB_ERR_INVALID, "col2im: expected [N, C*kh*kw, L], got %d dims", cols->ndim);
+    WB_REQUIRE(cols->dtype != WB_I64, WB_ERR_UNSUPPORTED, "col2im: unsupported dtype i64");
+    GP p = make_gp(*cp, cols->shape[0], c, h, w);
+    WB_REQUIRE(cols->shape[1] == c * p.kh * p.kw && cols->shape[2] == p.oh * p.ow, WB_ERR_INVALID,
+               "col2im: columns [%lld, %lld] do not match image [%lld, %lld, %lld]", (long long)cols->shape[1],
+               (long long)cols->shape[2], (long long)c, (long long)h, (long long)w);
+    int64_t total = p.n * c * h * w;
+    if (total == 0) return WB_OK;
+    WbProfileScope ps(b, "col2im");
+    unsigned grid = static_cast<unsigned>((total + THREADS - 1) / THREADS);
+    if (cols->dtype == WB_F32)
+        col2im_kernel<float><<<grid, THREADS, 0, b->stream>>>(static_cast<float*>(out), static_cast<const float*>(cols->data), p,
+                                                             cols->stride[0], cols->stride[1], cols->stride[2], cols->offset, total);
+    else
+        col2im_kernel<double><<<grid, THREADS, 0, b->stream>>>(static_cast<double*>(out), static_cast<const double*>(cols->data), p,
+                                                              cols->stride[0], cols->stride[1], cols->stride[2], cols->offset, total);
+    WB_LAUNCH_OK(b);
+    return WB_OK;
+}
+
+extern "C" int wb_col2im(WbBackend* b, const WbView* cols, const WbConvParams* cp, int64_t c, int64_t h, int64_t w, WbStorage** out) {
+    WB_REQUIRE(b && cols && out, WB_ERR_INVALID, "wb_col2im: null pointer");
+    WB_REQUIRE(cols->ndim == 3, WB_ERR_INVALID, "col2im: expected [N, C*kh*kw, L], got %d dims", cols->ndim);
+    WB_TRY(wb_new_storage(b, cols->shape[0] * c * h * w, cols->dtype, out));
+    int s = wb_col2im_into(b, cols, cp, c, h, w, (*out)->ptr);
+    if (s != WB_OK) { wb_free(b, *out); *out = nullptr; }
+    return s;
+}

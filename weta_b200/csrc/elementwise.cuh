@@ -1,0 +1,297 @@
+// Element-wise kernel templates shared by unary / binary / cast / copy.
+//
+// Three kernels cover every layout the trait can hand over:
+//   ew_flat   : every operand is one contiguous (or stride-0) run          -> 128-bit loads/stores
+//   ew_strided: collapsed rank <= 8, arbitrary strides; VEC consecutive outputs per thread share
+//               one index decomposition; an operand with unit inner stride is read with one
+//               128-bit load, a stride-0 operand with one scalar load
+//   ew_tile   : an operand whose unit-stride dim is not the output's inner dim (a transposed
+//               view) is staged through a 32x33 shared-memory tile so both its reads and the
+//               output's writes are coalesced
+// All arithmetic is done by a functor, so each op compiles to straight-line code.
+#pragma once
+
+#include "common.h"
+
+namespace ew {
+
+constexpr int THREADS = 256;
+
+template <class T> struct VecOf;
+template <> struct VecOf<float> { using type = float4; static constexpr int N = 4; };
+template <> struct VecOf<double> { using type = double2; static constexpr int N = 2; };
+template <> struct VecOf<int64_t> { using type = longlong2; static constexpr int N = 2; };
+
+template <class T, int N> struct alignas(sizeof(T) * N) Pack { T v[N]; };
+
+struct Plan {
+    int nd;
+    int64_t n;
+    int64_t size[WB_MAX_DIMS];
+    int64_t st[WB_PLAN_MAX_OPS][WB_MAX_DIMS];
+    int64_t off[WB_PLAN_MAX_OPS];
+    int mode[WB_PLAN_MAX_OPS];  // 0 scalar loads, 1 vector load (unit inner stride, aligned), 2 inner broadcast
+};
+
+// ---- flat ---------------------------------------------------------------------------------------
+// Each block covers THREADS*VEC*UNROLL consecutive outputs.  bcast[o] != 0: operand o is a scalar.
+template <class TI, class TO, int NOPS, int VEC, int UNROLL, class F>
+__global__ void __launch_bounds__(THREADS) ew_flat(TO* __restrict__ out, const TI* __restrict__ a, const TI* __restrict__ b,
+                                                    int64_t n, int bcast_a, int bcast_b, F f) {
+    int64_t base = static_cast<int64_t>(blockIdx.x) * (THREADS * VEC * UNROLL) + threadIdx.x * VEC;
+    Pack<TI, VEC> va[UNROLL], vb[UNROLL];
+    TI sa = bcast_a ? a[0] : TI(0);
+    TI sb = (NOPS > 1 && bcast_b) ? b[0] : TI(0);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        int64_t i = base + static_cast<int64_t>(u) * THREADS * VEC;
+        if (i + VEC <= n) {
+            if (!bcast_a) va[u] = *reinterpret_cast<const Pack<TI, VEC>*>(a + i);
+            if (NOPS > 1 && !bcast_b) vb[u] = *reinterpret_cast<const Pack<TI, VEC>*>(b + i);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        int64_t i = base + static_cast<int64_t>(u) * THREADS * VEC;
+        if (i + VEC <= n) {
+            Pack<TO, VEC> r;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                TI x = bcast_a ? sa : va[u].v[k];
+                if constexpr (NOPS > 1) {
+                    TI y = bcast_b ? sb : vb[u].v[k];
+                    r.v[k] = f(x, y);
+                } else {
+                    r.v[k] = f(x);
+                }
+            }
+            *reinterpret_cast<Pack<TO, VEC>*>(out + i) = r;
+        } else {
+            for (int64_t j = i; j < n; ++j) {  // ragged tail
+                TI x = bcast_a ? sa : a[j];
+                if constexpr (NOPS > 1) {
+                    TI y = bcast_b ? sb : b[j];
+                    out[j] = f(x, y);
+                } else {
+                    out[j] = f(x);
+                }
+            }
+        }
+    }
+}
+
+// ---- strided ------------------------------------------------------------------------------------
+template <class TI, class TO, int NOPS, int VEC, class IdxT, class F>
+__global__ void __launch_bounds__(THREADS) ew_strided(TO* __restrict__ out, const TI* __restrict__ a,
+                                                       const TI* __restrict__ b, Plan p, F f) {
+    int64_t groups = p.n / VEC;
+    int64_t g = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+    if (g >= groups) return;
+    int64_t e0 = g * VEC;
+    int64_t oa = p.off[0], ob = p.off[1];
+    IdxT rem = static_cast<IdxT>(e0);
+#pragma unroll 1
+    for (int d = p.nd - 1; d >= 0; --d) {
+        IdxT sz = static_cast<IdxT>(p.size[d]);
+        IdxT q = rem / sz;
+        IdxT c = rem - q * sz;
+        rem = q;
+        oa += static_cast<int64_t>(c) * p.st[0][d];
+        if (NOPS > 1) ob += static_cast<int64_t>(c) * p.st[1][d];
+    }
+    Pack<TI, VEC> va, vb;
+    int64_t ia = p.st[0][p.nd - 1], ib = p.st[1][p.nd - 1];
+    if (p.mode[0] == 1) va = *reinterpret_cast<const Pack<TI, VEC>*>(a + oa);
+    else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) va.v[k] = a[oa + k * ia];
+    }
+    if constexpr (NOPS > 1) {
+        if (p.mode[1] == 1) vb = *reinterpret_cast<const Pack<TI, VEC>*>(b + ob);
+        else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) vb.v[k] = b[ob + k * ib];
+        }
+    }
+    Pack<TO, VEC> r;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        if constexpr (NOPS > 1) r.v[k] = f(va.v[k], vb.v[k]);
+        else r.v[k] = f(va.v[k]);
+    }
+    *reinterpret_cast<Pack<TO, VEC>*>(out + e0) = r;
+}
+
+// ---- tile ---------------------------------------------------------------------------------------
+// Output viewed as [..outer.., P, ..mid.., L] (collapsed dims).  `pd` is the dim along which the
+// transposed operand(s) have unit stride; L is the output's inner dim.  A block owns a 32(P) x
+// 32(L) tile for one setting of all other dims.  tmode[o]: 1 = operand o is read along P through
+// shared memory, 0 = it is read along L directly.
+constexpr int TILE = 32;
+constexpr int TILE_ROWS = 8;
+
+template <class TI, class TO, int NOPS, class F>
+__global__ void __launch_bounds__(TILE * TILE_ROWS) ew_tile(TO* __restrict__ out, const TI* __restrict__ a,
+                                                            const TI* __restrict__ b, Plan p, int pd, int tmode_a,
+                                                            int tmode_b, int64_t tiles_p, int64_t tiles_l, F f) {
+    __shared__ TI sm[NOPS][TILE][TILE + 1];
+    const int L = p.nd - 1;
+    int64_t bid = blockIdx.x;
+    int64_t tl = bid % tiles_l;
+    bid /= tiles_l;
+    int64_t tp = bid % tiles_p;
+    bid /= tiles_p;
+    // Remaining dims (all but pd and L), innermost first.
+    int64_t oa = p.off[0], ob = p.off[1], oo = 0;
+    int64_t ostride[WB_MAX_DIMS];
+    {
+        int64_t s = 1;
+        for (int d = p.nd - 1; d >= 0; --d) {
+            ostride[d] = s;
+            s *= p.size[d];
+        }
+    }
+    for (int d = p.nd - 2; d >= 0; --d) {
+        if (d == pd) continue;
+        int64_t c = bid % p.size[d];
+        bid /= p.size[d];
+        oa += c * p.st[0][d];
+        if (NOPS > 1) ob += c * p.st[1][d];
+        oo += c * ostride[d];
+    }
+    const int64_t p0 = tp * TILE, l0 = tl * TILE;
+    const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+    const int64_t szp = p.size[pd], szl = p.size[L];
+    // Stage transposed operands: threads run along P (their unit-stride dim).
+    if (tmode_a) {
+#pragma unroll
+        for (int j = 0; j < TILE; j += TILE_ROWS) {
+            int64_t pi = p0 + tx, li = l0 + ty + j;
+            if (pi < szp && li < szl) sm[0][ty + j][tx] = a[oa + pi * p.st[0][pd] + li * p.st[0][L]];
+        }
+    }
+    if constexpr (NOPS > 1) {
+        if (tmode_b) {
+#pragma unroll
+            for (int j = 0; j < TILE; j += TILE_ROWS) {
+                int64_t pi = p0 + tx, li = l0 + ty + j;
+                if (pi < szp && li < szl) sm[1][ty + j][tx] = b[ob + pi * p.st[1][pd] + li * p.st[1][L]];
+            }
+        }
+    }
+    __syncthreads();
+    // Compute: threads run along L (the output's unit-stride dim).
+#pragma unroll
+    for (int j = 0; j < TILE; j += TILE_ROWS) {
+        int64_t pi = p0 + ty + j, li = l0 + tx;
+        if (pi < szp && li < szl) {
+            TI x = tmode_a ? sm[0][tx][ty + j] : a[oa + pi * p.st[0][pd] + li * p.st[0][L]];
+            TO r;
+            if constexpr (NOPS > 1) {
+                TI y = tmode_b ? sm[1][tx][ty + j] : b[ob + pi * p.st[1][pd] + li * p.st[1][L]];
+                r = f(x, y);
+            } else {
+                r = f(x);
+            }
+            out[oo + pi * ostride[pd] + li] = r;
+        }
+    }
+}
+
+// ---- host-side launcher -------------------------------------------------------------------------
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Launches f over the operands described by `plan` (built by wb_make_plan over NOPS views).
+template <class TI, class TO, int NOPS, class F>
+int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& wp, F f) {
+    if (wp.n == 0) return WB_OK;
+    // Vector width: 16 bytes of the wider of the two element types.
+    constexpr int VEC = 16 / (sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO));
+    const int L = wp.nd - 1;
+    cudaStream_t st = be->stream;
+    // flat: one collapsed dim whose stride is 1 or 0 for every operand
+    bool flat = wp.nd == 1;
+    for (int o = 0; o < NOPS && flat; ++o) flat = wp.st[o][0] == 1 || wp.st[o][0] == 0 || wp.n == 1;
+    if (flat) {
+        const TI* pa = a + wp.off[0];
+        const TI* pb = NOPS > 1 ? b + wp.off[1] : nullptr;
+        int ba = wp.st[0][0] != 1 && wp.n > 1, bb = NOPS > 1 && wp.st[1][0] != 1 && wp.n > 1;
+        if (wp.n == 1) { ba = 0; bb = 0; }
+        bool vec_ok = aligned16(out) && (ba || aligned16(pa)) && (NOPS == 1 || bb || aligned16(pb));
+        if (vec_ok) {
+            constexpr int UNROLL = 4;
+            int64_t per_block = THREADS * VEC * UNROLL;
+            unsigned grid = static_cast<unsigned>((wp.n + per_block - 1) / per_block);
+            ew_flat<TI, TO, NOPS, VEC, UNROLL, F><<<grid, THREADS, 0, st>>>(out, pa, pb, wp.n, ba, bb, f);
+        } else {
+            constexpr int UNROLL = 4;
+            int64_t per_block = THREADS * UNROLL;
+            unsigned grid = static_cast<unsigned>((wp.n + per_block - 1) / per_block);
+            ew_flat<TI, TO, NOPS, 1, UNROLL, F><<<grid, THREADS, 0, st>>>(out, pa, pb, wp.n, ba, bb, f);
+        }
+        WB_LAUNCH_OK(be);
+        return WB_OK;
+    }
+    Plan p;
+    p.nd = wp.nd;
+    p.n = wp.n;
+    for (int d = 0; d < WB_MAX_DIMS; ++d) {
+        p.size[d] = wp.size[d];
+        for (int o = 0; o < WB_PLAN_MAX_OPS; ++o) p.st[o][d] = wp.st[o][d];
+    }
+    for (int o = 0; o < WB_PLAN_MAX_OPS; ++o) p.off[o] = wp.off[o];
+    // tile: some operand has a non-unit, non-zero inner stride but unit stride along another dim
+    // that is reasonably long; the other operands must be readable along L (inner stride 1 or 0)
+    // or share that unit-stride dim.
+    int pd = -1;
+    bool tile_ok = wp.size[L] >= 8;
+    int tmode[WB_PLAN_MAX_OPS] = {0, 0, 0};
+    for (int o = 0; o < NOPS && tile_ok; ++o) {
+        int64_t is = wp.st[o][L];
+        if (is == 1 || is == 0) continue;
+        int found = -1;
+        for (int d = 0; d < L; ++d)
+            if (wp.st[o][d] == 1 && wp.size[d] >= 8) found = d;
+        if (found < 0 || (pd >= 0 && pd != found)) tile_ok = false;
+        else { pd = found; tmode[o] = 1; }
+    }
+    if (tile_ok && pd >= 0) {
+        int64_t tiles_p = (wp.size[pd] + TILE - 1) / TILE, tiles_l = (wp.size[L] + TILE - 1) / TILE;
+        int64_t rest = wp.n / (wp.size[pd] * wp.size[L]);
+        int64_t blocks = tiles_p * tiles_l * rest;
+        if (blocks < (int64_t(1) << 31)) {
+            ew_tile<TI, TO, NOPS, F><<<static_cast<unsigned>(blocks), TILE * TILE_ROWS, 0, st>>>(
+                out, a, b, p, pd, tmode[0], tmode[1], tiles_p, tiles_l, f);
+            WB_LAUNCH_OK(be);
+            return WB_OK;
+        }
+    }
+    // strided
+    bool vec = wp.size[L] % VEC == 0 && aligned16(out);
+    const TI* ptrs[2] = {a, b};
+    for (int o = 0; o < NOPS; ++o) {
+        int64_t is = wp.st[o][L];
+        p.mode[o] = 0;
+        if (is == 1 && vec) {
+            bool ok = aligned16(ptrs[o]) && wp.off[o] % VEC == 0;
+            for (int d = 0; d < L; ++d) ok = ok && wp.st[o][d] % VEC == 0;
+            p.mode[o] = ok ? 1 : 0;
+        }
+    }
+    bool small = wp.n < (int64_t(1) << 31);
+    if (vec) {
+        int64_t groups = wp.n / VEC;
+        unsigned grid = static_cast<unsigned>((groups + THREADS - 1) / THREADS);
+        if (small) ew_strided<TI, TO, NOPS, VEC, uint32_t, F><<<grid, THREADS, 0, st>>>(out, a, b, p, f);
+        else ew_strided<TI, TO, NOPS, VEC, int64_t, F><<<grid, THREADS, 0, st>>>(out, a, b, p, f);
+    } else {
+        p.mode[0] = p.mode[1] = 0;
+        unsigned grid = static_cast<unsigned>((wp.n + THREADS - 1) / THREADS);
+        if (small) ew_strided<TI, TO, NOPS, 1, uint32_t, F><<<grid, THREADS, 0, st>>>(out, a, b, p, f);
+        else ew_strided<TI, TO, NOPS, 1, int64_t, F><<<grid, THREADS, 0, st>>>(out, a, b, p, f);
+    }
+    WB_LAUNCH_OK(be);
+    return WB_OK;
+}
+
+}  // namespace ew
