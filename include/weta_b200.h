@@ -175,6 +175,13 @@ uint32_t wb_pcg_next_u32(WbPcg* g);
 uint64_t wb_pcg_next_u64(WbPcg* g);        /* the per-tensor seed */
 uint64_t wb_splitmix64(uint64_t seed, uint64_t i); /* crates/weta-core/src/ops.rs:164-169 */
 
+/* ==== extension: entry points with no trait method today ===================================== */
+
+/* Reads the device-side flag a tensor-core kernel raises when one of its bounded barrier waits
+ * runs out (WB_ERR_TIMEOUT), then clears it.  Synchronises the stream.  The reference has no
+ * counterpart: cuBLAS reports its own failures through the call's status (lib.rs:387). */
+int wb_gemm_check(WbBackend* b);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,99 @@
+"""The tcgen05 TF32 GEMM against float64 numpy: every operand layout the trait can hand over
+(row-major, transposed, batched, batch-broadcast), ragged edges, split-K, 1x and 3x TF32."""
+import numpy as np
+import pytest
+
+from weta_b200.tensor import Tensor
+
+pytestmark = pytest.mark.gpu
+
+TF32X3, TF32, FP32 = 0, 1, 2
+RNG = np.random.default_rng(1)
+
+
+def rnd(*shape):
+    return RNG.standard_normal(shape).astype(np.float32)
+
+
+def check(gpu, a_np, b_np, fa, fb, mode, name):
+    gpu.set_matmul_mode(mode)
+    a, b = fa(Tensor.from_numpy(a_np, gpu)), fb(Tensor.from_numpy(b_np, gpu))
+    got = a.matmul(b).numpy().astype(np.float64)
+    gpu.gemm_check()
+    an = fa(_NP(a_np)).arr.astype(np.float64)
+    bn = fb(_NP(b_np)).arr.astype(np.float64)
+    want = an @ bn
+    k = an.shape[-1]
+    tol = {TF32: 2e-3, TF32X3: 4e-6, FP32: 2e-6}[mode] * np.sqrt(k) * 1.5
+    err = np.abs(got - want).max()
+    assert got.shape == want.shape, name
+    assert err <= tol, f"{name} mode {mode}: max err {err:.3e} > {tol:.3e}"
+    gpu.set_matmul_mode(TF32X3)
+
+
+class _NP:
+    """numpy stand-in with the view methods used by the cases below."""
+
+    def __init__(self, arr):
+        self.arr = arr
+
+    def t(self):
+        return _NP(np.swapaxes(self.arr, -1, -2))
+
+    def step_by(self, dim, step):
+        idx = [slice(None)] * self.arr.ndim
+        idx[dim] = slice(None, None, step)
+        return _NP(self.arr[tuple(idx)])
+
+    def narrow(self, dim, start, length):
+        idx = [slice(None)] * self.arr.ndim
+        idx[dim] = slice(start, start + length)
+        return _NP(self.arr[tuple(idx)])
+
+
+ident = lambda x: x
+tr = lambda x: x.t()
+
+
+@pytest.mark.parametrize("mode", [TF32, TF32X3])
+def test_operand_layouts(gpu, mode):
+    m, n, k = 256, 384, 512
+    check(gpu, rnd(m, k), rnd(k, n), ident, ident, mode, "NN (A K-major, B N-major)")
+    check(gpu, rnd(m, k), rnd(n, k), ident, tr, mode, "NT (both K-major)")
+    check(gpu, rnd(k, m), rnd(k, n), tr, ident, mode, "TN (both MN-major)")
+    check(gpu, rnd(k, m), rnd(n, k), tr, tr, mode, "TT (A M-major, B K-major)")
+
+
+@pytest.mark.parametrize("mode", [TF32, TF32X3])
+def test_ragged_edges_and_small_k(gpu, mode):
+    for m, n, k in [(200, 136, 100), (129, 127, 36), (1000, 12, 260), (128, 128, 32), (130, 260, 1028)]:
+        check(gpu, rnd(m, k), rnd(k, n), ident, ident, mode, f"NN {m}x{n}x{k}")
+        check(gpu, rnd(m, k), rnd(n, k), ident, tr, mode, f"NT {m}x{n}x{k}")
+        check(gpu, rnd(k, m), rnd(k, n), tr, ident, mode, f"TN {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("mode", [TF32, TF32X3])
+def test_batched_and_broadcast(gpu, mode):
+    check(gpu, rnd(6, 128, 96), rnd(6, 96, 192), ident, ident, mode, "batched")
+    check(gpu, rnd(64, 288), rnd(5, 288, 196), ident, ident, mode, "weight broadcast over the batch (conv forward)")
+    check(gpu, rnd(5, 64, 196), rnd(5, 288, 196), ident, tr, mode, "batched NT (conv weight gradient)")
+    check(gpu, rnd(64, 288), rnd(5, 64, 196), tr, ident, mode, "broadcast transposed weight (conv input gradient)")
+
+
+@pytest.mark.parametrize("mode", [TF32, TF32X3])
+def test_split_k(gpu, mode):
+    check(gpu, rnd(4096, 128), rnd(4096, 256), tr, ident, mode, "long K, few tiles (a weight gradient)")
+    check(gpu, rnd(128, 8192), rnd(8192, 128), ident, ident, mode, "one tile, K = 8192")
+
+
+def test_fallback_layouts(gpu):
+    """Operands TMA cannot describe go to the CUDA-core tiles and still give the right answer."""
+    check(gpu, rnd(64, 130), rnd(65, 70), lambda a: a.step_by(1, 2), ident, TF32X3, "strided by 2")
+    check(gpu, rnd(70, 67), rnd(67, 33), ident, ident, TF32X3, "pitch not a multiple of 4")
+    check(gpu, rnd(512, 516), rnd(512, 256), lambda a: a.narrow(1, 1, 512), ident, TF32X3, "unaligned base")
+    check(gpu, rnd(256, 256), rnd(256, 256), ident, ident, FP32, "fp32 mode")
+
+
+def test_large_square(gpu):
+    check(gpu, rnd(2048, 2048), rnd(2048, 2048), ident, ident, TF32, "2048^3 tf32")
+    check(gpu, rnd(2048, 2048), rnd(2048, 2048), ident, tr, TF32X3, "2048^3 3xtf32 NT")

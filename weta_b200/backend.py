@@ -90,6 +90,7 @@ def load_library():
         "wb_random": ([P, i64, i32, i32, f64, f64, u64, PP], i32),
         "wb_random_into": ([P, i64, i32, i32, f64, f64, u64, P], i32),
         "wb_splitmix64": ([u64, u64], u64),
+        "wb_gemm_check": ([P], i32),
     }
     for name, (args, res) in sig.items():
         fn = getattr(lib, name)
@@ -165,6 +166,10 @@ class B200Backend:
 
     def launch_count(self) -> int:
         return self.lib.wb_launch_count(self.handle)
+
+    def gemm_check(self):
+        """Raises if a tensor-core kernel gave up on a pipeline barrier since the last check."""
+        self.check(self.lib.wb_gemm_check(self.handle))
 
     def set_matmul_mode(self, mode: int):
         self.check(self.lib.wb_set_matmul_mode(self.handle, mode))

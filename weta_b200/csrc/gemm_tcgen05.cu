@@ -1,10 +1,271 @@
-// Backend::matmul entry point (crates/weta-core/src/backend.rs:87) and its dispatch between the
-// tensor-core path and the CUDA-core tiles.
-#include "common.h"
+// Backend::matmul (crates/weta-core/src/backend.rs:87) and the internal GEMM service used by the
+// fused Linear / conv2d entry points.
+//
+// The reference hands every f32/f64 product to cuBLAS after classifying each operand as
+// "readable in place" or "copy first" (crates/weta-cuda/src/lib.rs:331-349, 603-628).  Here the
+// same classification picks between the tcgen05 TF32 kernel (tc_gemm.cuh), which reads row-major,
+// transposed and batch-broadcast operands in place through TMA, and the CUDA-core tiles
+// (matmul_simt.cu) for f64, tiny problems and layouts TMA cannot describe.
+#include <cuda.h>
+
+#include "tc_gemm.cuh"
 
 int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);
 
-void wb_gemm_state_destroy(WbBackend* b) { (void)b; }
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct GemmState {
+    EncodeFn encode = nullptr;
+    int* error_flag = nullptr;       // device
+    int* error_host = nullptr;       // pinned
+    bool attrs_set = false;
+};
+
+int get_state(WbBackend* b, GemmState** out) {
+    if (!b->gemm_state) {
+        GemmState* st = new GemmState();
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            delete st;
+            (void)cudaGetLastError();
+            wb_set_error("cuTensorMapEncodeTiled is not available from this driver");
+            return WB_ERR_CUDA;
+        }
+        st->encode = reinterpret_cast<EncodeFn>(fn);
+        WB_CHECK_CUDA(cudaMalloc(&st->error_flag, sizeof(int)));
+        WB_CHECK_CUDA(cudaMemsetAsync(st->error_flag, 0, sizeof(int), b->stream));
+        WB_CHECK_CUDA(cudaMallocHost(&st->error_host, sizeof(int)));
+        *st->error_host = 0;
+        b->gemm_state = st;
+    }
+    *out = static_cast<GemmState*>(b->gemm_state);
+    return WB_OK;
+}
+
+}  // namespace
+
+void wb_gemm_state_destroy(WbBackend* b) {
+    if (!b->gemm_state) return;
+    GemmState* st = static_cast<GemmState*>(b->gemm_state);
+    if (st->error_flag) cudaFree(st->error_flag);
+    if (st->error_host) cudaFreeHost(st->error_host);
+    delete st;
+    b->gemm_state = nullptr;
+}
+
+// One GEMM operand as the tensor core sees it: `rows` x `k` elements, either K-major (element
+// (r, kk) at ptr + r*ld + kk) or MN-major (element (r, kk) at ptr + kk*ld + r).
+struct WbGemmOperand {
+    const float* ptr;
+    int64_t rows, k, ld, batch_stride;  // batch_stride 0 = shared by every batch
+    bool mn_major;
+};
+
+namespace {
+
+bool operand_ok(const WbGemmOperand& o, int64_t batch) {
+    if ((reinterpret_cast<uintptr_t>(o.ptr) & 15) != 0) return false;
+    int64_t outer = o.mn_major ? o.k : o.rows;
+    if (outer > 1 && o.ld % 4 != 0) return false;
+    int64_t inner = o.mn_major ? o.rows : o.k;
+    if (o.ld < inner && outer > 1) return false;
+    if (batch > 1 && o.batch_stride != 0 && o.batch_stride % 4 != 0) return false;
+    return true;
+}
+
+int make_map(GemmState* st, const WbGemmOperand& o, int64_t batch, int box_rows, CUtensorMap* map) {
+    const int64_t inner = o.mn_major ? o.rows : o.k;
+    const int64_t outer = o.mn_major ? o.k : o.rows;
+    const int64_t nb = (o.batch_stride != 0) ? batch : 1;
+    int64_t ld = o.ld;
+    if (outer <= 1) ld = (inner + 3) / 4 * 4;  // pitch is irrelevant for a single row, but must be 16-byte granular
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer), static_cast<cuuint64_t>(nb)};
+    int64_t bstride = nb > 1 ? o.batch_stride : outer * ld;
+    if (bstride % 4 != 0 || bstride <= 0) bstride = (outer * ld + 3) / 4 * 4;
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 4, static_cast<cuuint64_t>(bstride) * 4};
+    cuuint32_t box[3] = {32u, static_cast<cuuint32_t>(o.mn_major ? tc::BK : box_rows), 1u};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(o.ptr), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        wb_set_error("cuTensorMapEncodeTiled failed with %d (inner %lld, outer %lld, ld %lld, batch %lld)", static_cast<int>(r),
+                     (long long)inner, (long long)outer, (long long)ld, (long long)nb);
+        return WB_ERR_CUDA;
+    }
+    return WB_OK;
+}
+
+// Split-K finish: out = epilogue(sum over splits of partial).
+__global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
+                                                     int m, int n, tc::Epilogue ep) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    int64_t per = static_cast<int64_t>(m) * n;
+    int64_t batch = i / per, r = i % per;
+    int row = static_cast<int>(r / n), col = static_cast<int>(r % n);
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += part[s * split_stride + i];
+    if (ep.bias_m) acc += ep.bias_m[row];
+    if (ep.bias_n) acc += ep.bias_n[col];
+    if (ep.relu) acc = fmaxf(acc, 0.f);
+    float* dst = ep.out + batch * ep.batch_stride_d + static_cast<int64_t>(row) * ep.ldd + col;
+    *dst = ep.accumulate ? *dst + acc : acc;
+}
+
+// hi = x with the 13 low mantissa bits cleared (exactly a tf32 value), lo = x - hi (exact in f32).
+__global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                                   int64_t nb, int64_t outer, int64_t inner, int64_t bs, int64_t ld, int64_t inner_p) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    int64_t total = nb * outer * inner_p;
+    if (i >= total) return;
+    int64_t c = i % inner_p, t = i / inner_p;
+    int64_t r = t % outer, bz = t / outer;
+    float v = c < inner ? x[bz * bs + r * ld + c] : 0.f;
+    float h = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    hi[i] = h;
+    lo[i] = v - h;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
+    using SS = tc::SharedStorage<BN, STAGES>;
+    constexpr size_t smem = sizeof(SS) + 1024;
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        attr_done = true;
+    }
+    kern<<<grid, tc::THREADS, smem, be->stream>>>(args);
+    WB_LAUNCH_OK(be);
+    return WB_OK;
+}
+
+}  // namespace
+
+// Runs D = A x B (+ epilogue) on the tensor cores.  mode: WB_MM_TF32 or WB_MM_TF32X3.
+// Returns WB_ERR_UNSUPPORTED (without setting an error message) if an operand cannot be read by TMA.
+int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int mode,
+               int force_splits) {
+    if (!operand_ok(A, batch) || !operand_ok(B, batch)) return WB_ERR_UNSUPPORTED;
+    GemmState* st = nullptr;
+    WB_TRY(get_state(be, &st));
+    constexpr int BN = 128;
+    tc::Args args{};
+    void *hi_a = nullptr, *hi_b = nullptr;
+    size_t ka = 0, kb = 0;
+    WbGemmOperand Ah = A, Al = A, Bh = B, Bl = B;
+    if (mode == WB_MM_TF32X3) {
+        auto split = [&](const WbGemmOperand& o, WbGemmOperand& oh, WbGemmOperand& ol, void** buf, size_t* klass) -> int {
+            int64_t inner = o.mn_major ? o.rows : o.k, outer = o.mn_major ? o.k : o.rows;
+            int64_t nb = o.batch_stride != 0 ? batch : 1;
+            int64_t inner_p = (inner + 3) / 4 * 4;
+            int64_t count = nb * outer * inner_p;
+            WB_TRY(wb_arena_alloc(be, static_cast<size_t>(2 * count) * sizeof(float), buf, klass));
+            float* h = static_cast<float*>(*buf);
+            float* l = h + count;
+            split_hi_lo<<<static_cast<unsigned>((count + 255) / 256), 256, 0, be->stream>>>(o.ptr, h, l, nb, outer, inner, o.batch_stride,
+                                                                                          o.ld, inner_p);
+            WB_LAUNCH_OK(be);
+            oh = o; ol = o;
+            oh.ptr = h; ol.ptr = l;
+            oh.ld = ol.ld = inner_p;
+            oh.batch_stride = ol.batch_stride = (o.batch_stride != 0) ? outer * inner_p : 0;
+            return WB_OK;
+        };
+        WB_TRY(split(A, Ah, Al, &hi_a, &ka));
+        int s2 = split(B, Bh, Bl, &hi_b, &kb);
+        if (s2 != WB_OK) { wb_arena_free(be, hi_a, ka); return s2; }
+        args.num_segments = 3;
+        int s = make_map(st, Ah, batch, tc::BM, &args.seg[0].a);
+        if (s == WB_OK) s = make_map(st, Bh, batch, BN, &args.seg[0].b);
+        if (s == WB_OK) s = make_map(st, Ah, batch, tc::BM, &args.seg[1].a);
+        if (s == WB_OK) s = make_map(st, Bl, batch, BN, &args.seg[1].b);
+        if (s == WB_OK) s = make_map(st, Al, batch, tc::BM, &args.seg[2].a);
+        if (s == WB_OK) s = make_map(st, Bh, batch, BN, &args.seg[2].b);
+        if (s != WB_OK) { wb_arena_free(be, hi_a, ka); wb_arena_free(be, hi_b, kb); return s; }
+    } else {
+        args.num_segments = 1;
+        WB_TRY(make_map(st, A, batch, tc::BM, &args.seg[0].a));
+        WB_TRY(make_map(st, B, batch, BN, &args.seg[0].b));
+    }
+    args.m = m;
+    args.n = n;
+    args.k_blocks = (k + tc::BK - 1) / tc::BK;
+    args.batched_a = A.batch_stride != 0;
+    args.batched_b = B.batch_stride != 0;
+    args.error_flag = st->error_flag;
+    const int tiles_m = (m + tc::BM - 1) / tc::BM, tiles_n = (n + BN - 1) / BN;
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * batch;
+    int splits = 1;
+    if (force_splits > 0) splits = force_splits;
+    else if (tiles * 2 <= be->sm_count && args.k_blocks >= 16) {
+        splits = static_cast<int>(std::min<int64_t>(be->sm_count / tiles, args.k_blocks / 8));
+    }
+    splits = std::max(1, std::min(splits, args.k_blocks));
+    // Make every split non-empty.
+    int per = (args.k_blocks + splits - 1) / splits;
+    splits = (args.k_blocks + per - 1) / per;
+    args.splits = splits;
+    int status = WB_OK;
+    void* part = nullptr;
+    size_t kp = 0;
+    if (splits > 1) {
+        const int64_t per_split = batch * static_cast<int64_t>(m) * n;
+        status = wb_arena_alloc(be, static_cast<size_t>(per_split) * splits * sizeof(float), &part, &kp);
+        if (status == WB_OK) {
+            args.ep = tc::Epilogue{static_cast<float*>(part), n, static_cast<int64_t>(m) * n, nullptr, nullptr, 0, 0};
+            args.split_stride_d = per_split;
+        }
+    } else {
+        args.ep = ep;
+        args.split_stride_d = 0;
+    }
+    if (status == WB_OK) {
+        WB_REQUIRE(batch * splits <= 65535, WB_ERR_UNSUPPORTED, "gemm: batch x split-K exceeds the grid limit");
+        dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m), static_cast<unsigned>(batch * splits));
+        const bool amn = A.mn_major, bmn = B.mn_major;
+        constexpr int STG = 6;
+        if (!amn && !bmn) status = launch_tc<BN, STG, false, false>(be, st, args, grid);
+        else if (!amn && bmn) status = launch_tc<BN, STG, false, true>(be, st, args, grid);
+        else if (amn && !bmn) status = launch_tc<BN, STG, true, false>(be, st, args, grid);
+        else status = launch_tc<BN, STG, true, true>(be, st, args, grid);
+    }
+    if (status == WB_OK && splits > 1) {
+        const int64_t total = batch * static_cast<int64_t>(m) * n;
+        splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
+                                                                                        total, m, n, ep);
+        cudaError_t e = cudaPeekAtLastError();
+        if (e != cudaSuccess) { wb_set_error("split-K reduce launch failed: %s", cudaGetErrorString(e)); status = WB_ERR_CUDA; }
+        else be->launches++;
+    }
+    if (part) wb_arena_free(be, part, kp);
+    if (hi_a) wb_arena_free(be, hi_a, ka);
+    if (hi_b) wb_arena_free(be, hi_b, kb);
+    return status;
+}
+
+// Reads the device-side error flag the GEMM kernels raise when a bounded wait runs out.
+// Synchronises the stream; meant for tests and for wb_synchronize-style checkpoints.
+extern "C" int wb_gemm_check(WbBackend* b) {
+    if (!b->gemm_state) return WB_OK;
+    GemmState* st = static_cast<GemmState*>(b->gemm_state);
+    WB_CHECK_CUDA(cudaMemcpyAsync(st->error_host, st->error_flag, sizeof(int), cudaMemcpyDeviceToHost, b->stream));
+    WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));
+    if (*st->error_host != 0) {
+        cudaMemsetAsync(st->error_flag, 0, sizeof(int), b->stream);
+        wb_set_error("a tensor-core GEMM gave up waiting on a pipeline barrier");
+        return WB_ERR_TIMEOUT;
+    }
+    return WB_OK;
+}
 
 extern "C" int wb_matmul_into(WbBackend* b, const WbView* a, const WbView* bb, void* out) {
     WB_REQUIRE(b && a && bb && out, WB_ERR_INVALID, "wb_matmul: null pointer");
@@ -15,6 +276,27 @@ extern "C" int wb_matmul_into(WbBackend* b, const WbView* a, const WbView* bb, v
                "matmul: [%lld,%lld,%lld] x [%lld,%lld,%lld] do not contract", (long long)a->shape[0], (long long)a->shape[1],
                (long long)a->shape[2], (long long)bb->shape[0], (long long)bb->shape[1], (long long)bb->shape[2]);
     WbProfileScope ps(b, "matmul");
+    const int64_t bs = a->shape[0], m = a->shape[1], k = a->shape[2], n = bb->shape[2];
+    if (bs * m * n == 0) return WB_OK;
+    const bool big = m * n * k >= (int64_t(1) << 18) && k >= 16 && m < (int64_t(1) << 31) && n < (int64_t(1) << 31) && k < (int64_t(1) << 31);
+    if (a->dtype == WB_F32 && b->matmul_mode != WB_MM_FP32 && big) {
+        // Operand classification, as gemm_operand does for cuBLAS (crates/weta-cuda/src/lib.rs:331-349).
+        WbGemmOperand A{static_cast<const float*>(a->data) + a->offset, m, k, 0, a->stride[0], false};
+        WbGemmOperand B{static_cast<const float*>(bb->data) + bb->offset, n, k, 0, bb->stride[0], false};
+        bool ok = true;
+        if (a->stride[2] == 1 || k == 1) { A.mn_major = false; A.ld = a->stride[1]; }
+        else if (a->stride[1] == 1 || m == 1) { A.mn_major = true; A.ld = a->stride[2]; }
+        else ok = false;
+        if (bb->stride[1] == 1 || k == 1) { B.mn_major = false; B.ld = bb->stride[2]; }
+        else if (bb->stride[2] == 1 || n == 1) { B.mn_major = true; B.ld = bb->stride[1]; }
+        else ok = false;
+        if (bs == 1) { A.batch_stride = 0; B.batch_stride = 0; }
+        if (ok) {
+            tc::Epilogue ep{static_cast<float*>(out), n, m * n, nullptr, nullptr, 0, 0};
+            int s = wb_tc_gemm(b, A, B, bs, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ep, b->matmul_mode, 0);
+            if (s != WB_ERR_UNSUPPORTED) return s;
+        }
+    }
     return wb_matmul_simt(b, a, bb, out);
 }
 

@@ -1,0 +1,302 @@
+// TF32 tensor-core GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma
+// (kind::tf32, accumulator in TMEM) -> tcgen05.ld epilogue.
+//
+// One CTA computes one 128 x BN output tile.  Warp 0 (one elected lane) issues the TMA loads,
+// warp 1 (one lane) issues the MMAs, then all four warps read the accumulator back (warp w owns
+// TMEM lanes 32w..32w+31, i.e. tile rows 32w..32w+31) and store it.  Operands may be K-major
+// (contraction index contiguous) or MN-major (row/column index contiguous); both are described to
+// the tensor core through the shared-memory matrix descriptor, so no operand is ever transposed
+// in memory.  A "segment" is one (A map, B map, K extent) triple; up to three segments accumulate
+// into the same TMEM tile, which is how the 3xTF32 mode runs hi*hi + hi*lo + lo*hi in one launch.
+//
+// Every wait on an mbarrier is bounded: after SPIN_LIMIT polls the waiter raises the error flag
+// in global memory and leaves; the other roles then run out as well, TMEM is released, and the
+// host reports WB_ERR_TIMEOUT.  No loads here use cluster-wide delivery; each CTA fetches its own
+// tiles.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.h"
+
+namespace tc {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                 // 32 tf32 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 8;              // K per tcgen05.mma for tf32
+constexpr int THREADS = 128;
+constexpr uint32_t SPIN_LIMIT = 1u << 26;
+
+struct Segment {
+    CUtensorMap a;
+    CUtensorMap b;
+};
+
+struct Epilogue {
+    float* out;            // row-major [M, ldd] (+ batch * batch_stride_d)
+    int64_t ldd;
+    int64_t batch_stride_d;
+    const float* bias_n;   // per output column, may be null
+    const float* bias_m;   // per output row, may be null
+    int relu;
+    int accumulate;        // out += result instead of out = result
+};
+
+struct Args {
+    Segment seg[3];
+    int num_segments;
+    int m, n;
+    int k_blocks;          // BK-blocks of the contraction, per segment
+    int splits;            // split-K factor: blockIdx.z = batch * splits + split
+    int batched_a, batched_b;  // 0: operand shared by every batch (TMA coordinate 0)
+    Epilogue ep;
+    int64_t split_stride_d;    // distance between split-K partial outputs
+    int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded wait.  Returns false if the phase never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1 (sm_100).
+//   bits [0,14)  start address >> 4      bits [16,30) leading-dim byte offset >> 4
+//   bits [32,46) stride-dim byte offset >> 4   bits [46,48) version = 1   bits [61,64) layout = 2 (128B swizzle)
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::tf32 with an f32 accumulator:
+//   [4,6) D format = 1 (f32)   [7,10) A format = 2 (tf32)   [10,13) B format = 2 (tf32)
+//   [15] A major (0 = K, 1 = MN)   [16] B major   [17,23) N >> 3   [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn, int b_mn) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn) << 15) | (static_cast<uint32_t>(b_mn) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on `bar` once every MMA issued so far by this thread has finished reading shared memory.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int STAGES>
+struct SharedStorage {
+    // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
+    alignas(1024) float a[STAGES][BM * BK];
+    alignas(1024) float b[STAGES][BN * BK];
+    alignas(8) uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+};
+
+// A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    using SS = SharedStorage<BN, STAGES>;
+    SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int batch = blockIdx.z / args.splits, split = blockIdx.z % args.splits;
+    // This CTA's share of the K blocks (split-K).
+    const int kb_per = (args.k_blocks + args.splits - 1) / args.splits;
+    const int kb_begin = split * kb_per;
+    const int kb_end = min(args.k_blocks, kb_begin + kb_per);
+    const int total_iters = max(0, kb_end - kb_begin) * args.num_segments;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ss.full[s], 1);
+            mbar_init(&ss.empty[s], 1);
+        }
+        mbar_init(&ss.tmem_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        // BN fp32 accumulator columns (a power of two >= 32).
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = ss.tmem_base;
+    bool ok = true;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer -------------------------------------------------------------------
+        constexpr uint32_t stage_bytes = (BM * BK + BN * BK) * sizeof(float);
+        int it = 0;
+        for (int sg = 0; sg < args.num_segments && ok; ++sg) {
+            const CUtensorMap* ma = &args.seg[sg].a;
+            const CUtensorMap* mb = &args.seg[sg].b;
+            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&ss.full[s], stage_bytes);
+                const int k0 = kb * BK;
+                const int za = args.batched_a ? batch : 0, zb = args.batched_b ? batch : 0;
+                if constexpr (A_MN) {
+#pragma unroll
+                    for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
+                } else {
+                    tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
+                }
+                if constexpr (B_MN) {
+#pragma unroll
+                    for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
+                } else {
+                    tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------
+        constexpr uint32_t idesc = make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        for (int it = 0; it < total_iters; ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            if (!mbar_wait(&ss.full[s], ph)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_base = smem_u32(&ss.a[s][0]), b_base = smem_u32(&ss.b[s][0]);
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                // K-major: rows of 128 B, 8-row groups 1024 B apart; a K step of 8 elements is +32 B
+                //          inside the swizzle row.
+                // MN-major: 32-element column blocks 32*BK*4 B apart (LBO), 8-row K groups 1024 B apart.
+                uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 1024) : make_smem_desc(a_base + ks * 32, 16, 1024);
+                uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 1024) : make_smem_desc(b_base + ks * 32, 16, 1024);
+                umma_tf32(tmem_d, ad, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+            }
+            umma_commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
+        }
+        umma_commit(&ss.tmem_full);
+    }
+    if (!ok) {
+        atomicExch(args.error_flag, 1);
+        // Give copies and MMAs that are still in flight time to finish before the CTA retires.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000) {}
+    }
+    __syncwarp();
+
+    // ---- epilogue: TMEM -> registers -> global ----------------------------------------------
+    bool ready = total_iters == 0 ? true : mbar_wait(&ss.tmem_full, 0);
+    if (!ready && lane == 0) atomicExch(args.error_flag, 1);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ready) {
+        const int row = m0 + warp * 32 + lane;
+        float* dst = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d +
+                     static_cast<int64_t>(row) * args.ep.ldd;
+        const float bm = (args.ep.bias_m && row < args.m) ? args.ep.bias_m[row] : 0.f;
+        const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
+                            (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+            float v[32];
+            if (total_iters == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            } else {
+                tmem_ld32(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
+            }
+            if (row < args.m) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const int col = n0 + c + i;
+                    if (col >= args.n) break;
+                    float r[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float x = v[i + j] + bm;
+                        if (args.ep.bias_n && col + j < args.n) x += args.ep.bias_n[col + j];
+                        if (args.ep.relu) x = fmaxf(x, 0.f);
+                        r[j] = x;
+                    }
+                    if (vec_ok && col + 4 <= args.n) {
+                        float4* p = reinterpret_cast<float4*>(dst + col);
+                        if (args.ep.accumulate) {
+                            float4 o = *p;
+                            r[0] += o.x; r[1] += o.y; r[2] += o.z; r[3] += o.w;
+                        }
+                        *p = make_float4(r[0], r[1], r[2], r[3]);
+                    } else {
+                        for (int j = 0; j < 4 && col + j < args.n; ++j) dst[col + j] = args.ep.accumulate ? dst[col + j] + r[j] : r[j];
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(BN) : "memory");
+    }
+}
+
+}  // namespace tc
