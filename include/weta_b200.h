@@ -182,6 +182,95 @@ uint64_t wb_splitmix64(uint64_t seed, uint64_t i); /* crates/weta-core/src/ops.r
  * counterpart: cuBLAS reports its own failures through the call's status (lib.rs:387). */
 int wb_gemm_check(WbBackend* b);
 
+/* ---- fused layer ops ------------------------------------------------------------------------
+ * Each stands for the chain of trait calls the reference issues for one layer; pointers are f32
+ * device memory, tensors are contiguous NCHW / row-major. */
+
+/* F::dropout in training mode (crates/weta-nn/src/functional.rs:64-74): y = x * mask with
+ * mask_i = (rand_f32(seed)_i > p) / (1 - p), the mask regenerated from the seed (never stored);
+ * values are bit-identical to the four-call chain random -> gt_scalar -> mul_scalar -> mul. */
+int wb_dropout_fwd(WbBackend* b, const float* x, float* y, int64_t n, double p, uint64_t seed);
+/* Its backward, dx = dy * mask, optionally times step(relu_out) (ReLU backward, autograd ops.rs:85). */
+int wb_dropout_relu_bwd(WbBackend* b, const float* dy, const float* relu_out, float* dx, int64_t n, double p, uint64_t seed);
+/* Just the mask values (0 or f32(1/(1-p))). */
+int wb_dropout_mask(WbBackend* b, float* mask, int64_t n, double p, uint64_t seed);
+/* Tensor::cross_entropy forward and CrossEntropyBw (crates/weta-autograd/src/ops.rs:444-519), mean
+ * reduction: logits [rows, cols], labels i64 [rows].  Any of probs / dlogits / row_loss / mean_loss may
+ * be null.  dlogits = (softmax - onehot) * upstream / rows. */
+int wb_softmax_ce(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs,
+                  float* dlogits, float* row_loss, float* mean_loss, double upstream);
+/* F::batch_norm in training mode (crates/weta-nn/src/functional.rs:144-180) on [n, c, hw]: batch mean,
+ * biased variance -> rstd = 1/sqrt(var + eps); running stats updated with the unbiased variance. */
+int wb_bn2d_stats(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, double eps, double momentum, float* mean,
+                  float* rstd, float* running_mean, float* running_var);
+int wb_bn2d_apply(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* mean, const float* rstd,
+                  const float* gamma, const float* beta, int relu, float* y);
+int wb_bn2d_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* gamma, const float* beta,
+                float* running_mean, float* running_var, double momentum, double eps, float* y, float* save_mean, float* save_rstd);
+/* The gradient autograd derives through that chain: dx, dgamma = sum(dy*xhat), dbeta = sum(dy). */
+int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_t n, int64_t c, int64_t hw, const float* gamma,
+                const float* save_mean, const float* save_rstd, float* dx, float* dgamma, float* dbeta);
+/* BatchNorm2d -> ReLU -> MaxPool2d(2) of crates/weta/examples/mnist_cnn.rs:18-20 in one pass: x [n,c,h,w]
+ * -> y_pooled [n,c,h/2,w/2].  Backward recomputes the activations from x; max-pool ties share the
+ * gradient equally (crates/weta-autograd/src/ops.rs:305-314).  dbias_conv (optional) receives sum(dx)
+ * per channel, the gradient of the bias of the convolution that produced x. */
+int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma,
+                        const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
+                        float* save_mean, float* save_rstd);
+int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
+                        const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
+                        float* dgamma, float* dbeta, float* dbias_conv);
+/* Adam::step / AdamW for one flat parameter range at step t >= 1 (crates/weta-optim/src/lib.rs:210-239,
+ * 276-283), every f32 rounding of the 13-call chain kept.  grad_scale multiplies the gradient first
+ * (1/world after a summing all-reduce); 1.0 leaves the chain untouched. */
+int wb_adam_step(WbBackend* b, float* theta, const float* grad, float* m, float* v, int64_t n, int64_t t, double lr, double beta1,
+                 double beta2, double eps, double weight_decay, int decoupled, double grad_scale);
+
+/* ---- fused training step ---------------------------------------------------------------------
+ * The step of crates/weta/examples/mnist_cnn.rs:63-73 / mnist_mlp.rs (forward, cross-entropy,
+ * backward, Adam) for a sequential model made of the three layer kinds below, run as a fixed
+ * sequence of fused kernels instead of ~400 trait calls.  Parameters, gradients and Adam state live
+ * in one flat f32 arena, layers in reverse order; wb_trainer_tensor_range maps the reference's
+ * parameter order (layer by layer: weight, bias, then BatchNorm weight, bias) onto it. */
+typedef enum WbLayerKind {
+    WB_LAYER_CONV_BN_RELU_POOL = 0, /* Conv2d(a -> b, 3x3, padding 1) + BatchNorm2d + ReLU + MaxPool2d(2) */
+    WB_LAYER_LINEAR = 1,            /* Linear(a -> b), followed by ReLU when c != 0 */
+    WB_LAYER_DROPOUT = 2            /* Dropout(p), training mode */
+} WbLayerKind;
+typedef struct WbLayerSpec { int32_t kind, a, b, c; double p; } WbLayerSpec;
+/* Adam / AdamW hyper-parameters (crates/weta-optim/src/lib.rs:178-207, 276-283). */
+typedef struct WbAdamConfig { double lr, beta1, beta2, eps, weight_decay; int32_t decoupled; } WbAdamConfig;
+typedef struct WbTrainer WbTrainer;
+/* Called during backward each time one layer's gradients are final: a contiguous arena range. */
+typedef void (*wb_bucket_callback)(void* user, float* grad_range, int64_t len);
+
+/* Input is [batch, in_c, in_h, in_w] (NCHW; use in_h = in_w = 1 for flat features). */
+int wb_trainer_create(WbBackend* b, const WbLayerSpec* layers, int n_layers, int64_t batch, int64_t in_c, int64_t in_h,
+                      int64_t in_w, const WbAdamConfig* adam, int matmul_mode, WbTrainer** out);
+int wb_trainer_destroy(WbTrainer* t);
+/* Default init of crates/weta-nn/src/layers.rs:19-26 from one RNG seed per weight / bias tensor, in creation order. */
+int wb_trainer_init(WbTrainer* t, const uint64_t* seeds, int n_seeds);
+int64_t wb_trainer_arena_len(const WbTrainer* t);
+float* wb_trainer_params(WbTrainer* t);      /* device pointers into the flat arenas */
+float* wb_trainer_grads(WbTrainer* t);
+float* wb_trainer_exp_avg(WbTrainer* t);
+float* wb_trainer_exp_avg_sq(WbTrainer* t);
+float* wb_trainer_input(WbTrainer* t);       /* staged batch: f32 [batch, in_c*in_h*in_w] */
+int64_t* wb_trainer_labels(WbTrainer* t);    /* staged labels: i64 [batch] */
+float* wb_trainer_loss_ptr(WbTrainer* t);    /* device scalar written by forward_backward */
+int wb_trainer_num_tensors(const WbTrainer* t);
+int wb_trainer_tensor_range(const WbTrainer* t, int index, int64_t* offset, int64_t* len);
+int wb_trainer_bn_buffers(WbTrainer* t, int conv_index, float** running_mean, float** running_var, int64_t* channels);
+int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* user);
+/* Forward, mean cross-entropy and backward on the staged batch; one seed per dropout layer in forward order. */
+int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds);
+/* Adam over the whole arena; grad_scale = 1/world after a summing all-reduce, else 1. */
+int wb_trainer_adam_step(WbTrainer* t, double grad_scale);
+/* One whole step from host memory: upload batch, forward/backward/Adam, download the loss, wait. */
+int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,
+                         float* host_loss);
+int wb_trainer_read_loss(WbTrainer* t, float* host_loss);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,270 @@
+"""Fused extension ops and the fused training step against the CPU oracle running the reference's
+primitive sequences (the op-by-op definitions in crates/weta-nn/src/functional.rs,
+crates/weta-autograd/src/ops.rs and crates/weta-optim/src/lib.rs)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+from weta_b200 import core, nn
+from weta_b200.autograd import Var
+from weta_b200.core import Distribution, DType, manual_seed
+from weta_b200.tensor import Tensor, allclose
+from weta_b200.trainer import FusedTrainer, _declare, cnn_specs, mlp_specs
+from weta_b200.workloads import MNIST_CNN, CnnConfig, build_cnn, mlp_batch, primitive_train_step, synthetic_batch
+
+pytestmark = pytest.mark.gpu
+RNG = np.random.default_rng(7)
+FP32, TF32, TF32X3 = 2, 1, 0
+
+
+def dev(gpu, arr):
+    t = Tensor.from_numpy(np.ascontiguousarray(arr), gpu)
+    return t, t.storage.ptr
+
+
+def empty(gpu, n, dt=DType.F32):
+    s = gpu.alloc(int(n), dt)
+    return s, s.ptr
+
+
+def fetch(gpu, storage, shape, dt=DType.F32):
+    from weta_b200.core import Layout
+    return gpu.to_host(storage, Layout.contiguous(shape), dt).reshape(shape)
+
+
+def test_dropout_is_bit_identical_to_the_primitive_chain(oracle, gpu):
+    _declare(gpu.lib)
+    n, p, seed = (1 << 20) + 3, 0.1, 42
+    x = RNG.standard_normal(n).astype(np.float32)
+    xo = Tensor.from_numpy(x, oracle)
+    mask_o = Tensor.random_seeded([n], Distribution.uniform(0.0, 1.0), DType.F32, oracle, seed).gt_scalar(p).mul_scalar(1.0 / (1.0 - p))
+    want = xo.mul(mask_o).numpy()
+    (xt, xp), (ys, yp), (ms, mp) = dev(gpu, x), empty(gpu, n), empty(gpu, n)
+    gpu.check(gpu.lib.wb_dropout_fwd(gpu.handle, xp, yp, n, p, seed))
+    gpu.check(gpu.lib.wb_dropout_mask(gpu.handle, mp, n, p, seed))
+    assert np.array_equal(fetch(gpu, ys, (n,)), want)
+    mask = fetch(gpu, ms, (n,))
+    assert np.array_equal(mask, mask_o.numpy())
+    assert set(np.unique(mask).tolist()) == {0.0, float(np.float32(1.0 / 0.9))}
+    # the same mask through the trait ops on the GPU
+    mask_g = Tensor.random_seeded([n], Distribution.uniform(0.0, 1.0), DType.F32, gpu, seed).gt_scalar(p).mul_scalar(1.0 / (1.0 - p))
+    assert np.array_equal(mask_g.numpy(), mask)
+
+
+def test_dropout_mask_2_pow_28_seed_42(oracle, gpu):
+    """The full-size mask fill: 2^28 elements, p = 0.1, seed 42, compared element for element."""
+    _declare(gpu.lib)
+    n, p = 1 << 28, 0.1
+    ms, mp = empty(gpu, n)
+    gpu.check(gpu.lib.wb_dropout_mask(gpu.handle, mp, n, p, 42))
+    got = fetch(gpu, ms, (n,))
+    want = Tensor.random_seeded([n], Distribution.uniform(0.0, 1.0), DType.F32, oracle, 42).gt_scalar(p).mul_scalar(1.0 / (1.0 - p)).numpy()
+    assert int((got != want).sum()) == 0
+
+
+def test_softmax_cross_entropy(oracle, gpu):
+    _declare(gpu.lib)
+    for rows, cols in [(128, 10), (257, 1000), (64, 33)]:
+        z = (RNG.standard_normal((rows, cols)) * 3).astype(np.float32)
+        y = RNG.integers(0, cols, rows).astype(np.int64)
+        zv = Var(Tensor.from_numpy(z, oracle), requires_grad=True)
+        loss = zv.cross_entropy(Tensor.from_numpy(y, oracle))
+        loss.backward()
+        (zt, zp), (yt, yp) = dev(gpu, z), dev(gpu, y)
+        (ps, pp), (ds, dp), (ls, lp) = empty(gpu, rows * cols), empty(gpu, rows * cols), empty(gpu, 1)
+        gpu.check(gpu.lib.wb_softmax_ce(gpu.handle, zp, yp, rows, cols, pp, dp, None, lp, 1.0))
+        assert abs(fetch(gpu, ls, (1,))[0] - loss.item()) <= 1e-5 * max(1.0, abs(loss.item()))
+        assert allclose(fetch(gpu, ds, (rows, cols)), zv.grad.numpy(), 1e-4, 1e-7)
+        assert allclose(fetch(gpu, ps, (rows, cols)), Tensor.from_numpy(z, oracle).softmax(1).numpy(), 1e-4, 1e-7)
+
+
+def _oracle_bn(oracle, x, gamma, beta, upstream=None, pool=False):
+    xv = Var(Tensor.from_numpy(x, oracle), requires_grad=True)
+    gv = Var(Tensor.from_numpy(gamma, oracle), requires_grad=True)
+    bv = Var(Tensor.from_numpy(beta, oracle), requires_grad=True)
+    c = x.shape[1]
+    rm, rv = Tensor.zeros([c], DType.F32, oracle), Tensor.ones([c], DType.F32, oracle)
+    y = nn.batch_norm(xv, rm, rv, gv, bv, True, 0.1, 1e-5)
+    if pool:
+        y = nn.max_pool2d(y.relu(), 2, 2)
+    if upstream is not None:
+        y.mul(Var(Tensor.from_numpy(upstream, oracle))).sum().backward()
+    return y.numpy(), rm.numpy(), rv.numpy(), xv.grad, gv.grad, bv.grad
+
+
+def test_batch_norm_2d(oracle, gpu):
+    _declare(gpu.lib)
+    n, c, h, w = 6, 5, 7, 9
+    x = (RNG.standard_normal((n, c, h, w)) * 2 + 3).astype(np.float32)
+    gamma, beta = RNG.standard_normal(c).astype(np.float32), RNG.standard_normal(c).astype(np.float32)
+    up = RNG.standard_normal((n, c, h, w)).astype(np.float32)
+    y_o, rm_o, rv_o, dx_o, dg_o, db_o = _oracle_bn(oracle, x, gamma, beta, up)
+    (xt, xp), (gt, gp), (bt, bp), (ut, upp) = dev(gpu, x), dev(gpu, gamma), dev(gpu, beta), dev(gpu, up)
+    (rmt, rmp), (rvt, rvp) = dev(gpu, np.zeros(c, np.float32)), dev(gpu, np.ones(c, np.float32))
+    (ys, yp), (ms, mp), (rs, rp) = empty(gpu, x.size), empty(gpu, c), empty(gpu, c)
+    gpu.check(gpu.lib.wb_bn2d_fwd(gpu.handle, xp, n, c, h * w, gp, bp, rmp, rvp, 0.1, 1e-5, yp, mp, rp))
+    assert allclose(fetch(gpu, ys, x.shape), y_o, 1e-5, 1e-5)
+    assert allclose(rmt.numpy(), rm_o, 1e-6, 1e-6) and allclose(rvt.numpy(), rv_o, 1e-5, 1e-6)
+    (dxs, dxp), (dgs, dgp), (dbs, dbp) = empty(gpu, x.size), empty(gpu, c), empty(gpu, c)
+    gpu.check(gpu.lib.wb_bn2d_bwd(gpu.handle, xp, upp, n, c, h * w, gp, mp, rp, dxp, dgp, dbp))
+    assert allclose(fetch(gpu, dxs, x.shape), dx_o.numpy(), 1e-4, 2e-5)
+    assert allclose(fetch(gpu, dgs, (c,)), dg_o.numpy(), 1e-4, 1e-4)
+    assert allclose(fetch(gpu, dbs, (c,)), db_o.numpy(), 1e-4, 1e-4)
+
+
+def test_bn_relu_pool_block_with_ties(oracle, gpu):
+    _declare(gpu.lib)
+    n, c, h, w = 5, 4, 8, 12
+    x = RNG.standard_normal((n, c, h, w)).astype(np.float32)
+    x[0, 0, 0:2, 0:2] = 1.5          # a window of four equal positives: the gradient splits four ways
+    x[1, 2, 2:4, 4:6] = [[0.7, 0.7], [-1.0, 0.1]]  # two-way tie
+    gamma = (np.abs(RNG.standard_normal(c)) + 0.5).astype(np.float32)
+    beta = (RNG.standard_normal(c) * 0.1).astype(np.float32)
+    up = RNG.standard_normal((n, c, h // 2, w // 2)).astype(np.float32)
+    y_o, rm_o, rv_o, dx_o, dg_o, db_o = _oracle_bn(oracle, x, gamma, beta, up, pool=True)
+    (xt, xp), (gt, gp), (bt, bp), (ut, upp) = dev(gpu, x), dev(gpu, gamma), dev(gpu, beta), dev(gpu, up)
+    (rmt, rmp), (rvt, rvp) = dev(gpu, np.zeros(c, np.float32)), dev(gpu, np.ones(c, np.float32))
+    (ys, yp), (ms, mp), (rs, rp) = empty(gpu, up.size), empty(gpu, c), empty(gpu, c)
+    gpu.check(gpu.lib.wb_bn_relu_pool_fwd(gpu.handle, xp, n, c, h, w, gp, bp, rmp, rvp, 0.1, 1e-5, yp, mp, rp))
+    assert allclose(fetch(gpu, ys, up.shape), y_o, 1e-5, 1e-5)
+    assert allclose(rvt.numpy(), rv_o, 1e-5, 1e-6)
+    (dxs, dxp), (dgs, dgp), (dbs, dbp), (dcs, dcp) = empty(gpu, x.size), empty(gpu, c), empty(gpu, c), empty(gpu, c)
+    gpu.check(gpu.lib.wb_bn_relu_pool_bwd(gpu.handle, xp, upp, n, c, h, w, gp, bp, mp, rp, dxp, dgp, dbp, dcp))
+    dx = fetch(gpu, dxs, x.shape)
+    assert allclose(dx, dx_o.numpy(), 1e-4, 2e-5)
+    assert allclose(fetch(gpu, dgs, (c,)), dg_o.numpy(), 1e-4, 1e-4)
+    assert allclose(fetch(gpu, dbs, (c,)), db_o.numpy(), 1e-4, 1e-4)
+    assert allclose(fetch(gpu, dcs, (c,)), dx.sum(axis=(0, 2, 3)), 1e-3, 1e-4)
+
+
+@pytest.mark.parametrize("wd,decoupled", [(0.0, False), (0.1, False), (0.1, True)])
+def test_adam_is_bit_identical_to_the_primitive_chain(oracle, gpu, wd, decoupled):
+    _declare(gpu.lib)
+    n = 10007
+    p0 = RNG.standard_normal(n).astype(np.float32)
+    grads = [RNG.standard_normal(n).astype(np.float32) * s for s in (1.0, 1e-3, 10.0)]
+    pv = Var(Tensor.from_numpy(p0.copy(), oracle), requires_grad=True)
+    opt = nn.Adam([pv], 1e-3, weight_decay=wd, decoupled=decoupled)
+    (tt, tp) = dev(gpu, p0)
+    (mt, mp), (vt, vp) = dev(gpu, np.zeros(n, np.float32)), dev(gpu, np.zeros(n, np.float32))
+    for step, g in enumerate(grads, 1):
+        pv.grad = Tensor.from_numpy(g, oracle)
+        opt.step()
+        gt, gp = dev(gpu, g)
+        gpu.check(gpu.lib.wb_adam_step(gpu.handle, tp, gp, mp, vp, n, step, 1e-3, 0.9, 0.999, 1e-8, wd, int(decoupled), 1.0))
+        assert np.array_equal(tt.numpy(), pv.numpy()), f"step {step}"
+        assert np.array_equal(mt.numpy(), opt.m[0].numpy()) and np.array_equal(vt.numpy(), opt.v[0].numpy())
+
+
+def _adam_params_close(name, got, want, steps, lr, frac_allowed=2e-3):
+    d = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert d.max() <= 2 * steps * lr * 1.01, f"{name}: max |diff| {d.max()}"
+    frac = float((d > 1e-5 + 1e-4 * np.abs(want)).mean())
+    assert frac < frac_allowed, f"{name}: {frac:.2%} of elements differ by more than 1e-5"
+
+
+@pytest.mark.parametrize("mode", [FP32, TF32X3])
+def test_fused_mlp_matches_the_primitive_step(oracle, gpu, mode):
+    """784-512-256-10, ReLU + Dropout(0.1), batch 128, Adam 1e-3, seed 42, 10 steps."""
+    manual_seed(42)
+    ref = nn.mlp(oracle, 0.1)
+    opt = nn.Adam(ref.parameters(), 1e-3)
+    manual_seed(42)
+    tr = FusedTrainer(gpu, mlp_specs(), 128, (784, 1, 1), lr=1e-3, matmul_mode=mode)
+    tr.init_from_global_rng()
+    for i, p in enumerate(ref.parameters()):
+        assert np.array_equal(tr.get_param(i), p.numpy().reshape(-1)), f"initial parameter {i}"
+    state_after_init = (core.global_rng().state,)
+    losses = []
+    for be_name in ("oracle", "fused"):
+        core.global_rng().state = state_after_init[0]
+        for step in range(10):
+            x, y = mlp_batch(128, step, oracle)
+            if be_name == "oracle":
+                l = primitive_train_step(ref, opt, x, y)
+                if step == 0:
+                    g0 = [p.grad.numpy().reshape(-1) for p in ref.parameters()]
+            else:
+                tr.stage(x.numpy(), y.numpy())
+                tr.forward_backward()
+                if step == 0:
+                    for i, g in enumerate(g0):
+                        got = tr.get_grad(i)
+                        assert np.abs(got - g).max() <= 2e-4 * max(np.abs(g).max(), 1e-6), f"grad {i}"
+                tr.adam_step()
+                l = tr.loss()
+            losses.append(l)
+    for a, b in zip(losses[:10], losses[10:]):
+        assert abs(a - b) < 2e-4, (losses[:10], losses[10:])
+    for i, (n, p) in enumerate(ref.named_parameters()):
+        _adam_params_close(n, tr.get_param(i), p.numpy().reshape(-1), 10, 1e-3, 5e-3)
+    gpu.gemm_check()
+    tr.close()
+
+
+@pytest.mark.parametrize("mode", [FP32, TF32X3, TF32])
+def test_fused_cnn_matches_the_primitive_step(oracle, gpu, mode):
+    """The 422k-parameter CNN (conv-BN-ReLU-pool x2, dropout, fc 128, dropout, fc 10), batch 64, 3 Adam steps."""
+    cfg = MNIST_CNN
+    ref = build_cnn(cfg, oracle, 42)
+    opt = nn.Adam(ref.parameters(), 1e-3)
+    manual_seed(42)
+    tr = FusedTrainer(gpu, cnn_specs(cfg), 64, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=mode)
+    tr.init_from_global_rng()
+    names = [n for n, _ in ref.named_parameters()]
+    for i, p in enumerate(ref.parameters()):
+        assert np.array_equal(tr.get_param(i), p.numpy().reshape(-1)), f"initial {names[i]}"
+    rng_state = core.global_rng().state
+    tol_loss, tol_grad = {FP32: (2e-4, 2e-3), TF32X3: (2e-4, 2e-3), TF32: (3e-3, 3e-2)}[mode]
+    ref_losses, ref_g0 = [], None
+    for step in range(3):
+        x, y = synthetic_batch(cfg, 64, step, 0, oracle)
+        ref_losses.append(primitive_train_step(ref, opt, x, y))
+        if step == 0:
+            ref_g0 = [p.grad.numpy().reshape(-1) for p in ref.parameters()]
+    core.global_rng().state = rng_state
+    for step in range(3):
+        x, y = synthetic_batch(cfg, 64, step, 0, oracle)
+        tr.stage(x.numpy(), y.numpy())
+        tr.forward_backward()
+        if step == 0:
+            for i, g in enumerate(ref_g0):
+                if names[i] in ("0.bias", "4.bias"):
+                    continue  # conv bias before BatchNorm: the true gradient is zero, both sides hold rounding noise
+                got = tr.get_grad(i)
+                assert np.abs(got - g).max() <= tol_grad * max(np.abs(g).max(), 1e-6), f"grad {names[i]}"
+        tr.adam_step()
+        assert abs(tr.loss() - ref_losses[step]) < tol_loss, (step, tr.loss(), ref_losses)
+    if mode != TF32:
+        for i, (n, p) in enumerate(ref.named_parameters()):
+            if n in ("0.bias", "4.bias"):
+                assert np.abs(tr.get_param(i) - p.numpy().reshape(-1)).max() <= 2 * 3 * 1e-3 * 1.01
+            else:
+                _adam_params_close(n, tr.get_param(i), p.numpy().reshape(-1), 3, 1e-3, 2e-2)
+        bufs = dict(ref.buffers())
+        for k, idx in ((0, "1"), (1, "5")):
+            rm, rv = tr.bn_buffers(k)
+            assert allclose(rm, bufs[f"{idx}.running_mean"].numpy(), 0.0, 3e-3)
+            assert allclose(rv, bufs[f"{idx}.running_var"].numpy(), 1e-3, 1e-5)
+    gpu.gemm_check()
+    tr.close()
+
+
+def test_bucket_callback_covers_the_arena(gpu):
+    cfg = CnnConfig("tiny", 3, 8, 8, 16, 32)
+    manual_seed(1)
+    tr = FusedTrainer(gpu, cnn_specs(cfg), 16, (3, 8, 8), matmul_mode=FP32)
+    tr.init_from_global_rng()
+    seen = []
+    base = tr.grads_ptr()
+    tr.set_bucket_callback(lambda ptr, n: seen.append(((ptr - base) // 4, n)))
+    x = RNG.random((16, 3, 8, 8)).astype(np.float32)
+    y = RNG.integers(0, 10, 16)
+    tr.stage(x, y)
+    tr.forward_backward()
+    gpu.synchronize()
+    assert seen[0][0] == 0 and [o for o, _ in seen] == sorted(o for o, _ in seen)  # last layer first, front of the arena
+    assert sum(n for _, n in seen) == tr.arena_len
+    assert all(seen[i][0] + seen[i][1] == seen[i + 1][0] for i in range(len(seen) - 1))
+    tr.close()

@@ -9,6 +9,7 @@
 #include <cuda.h>
 
 #include "tc_gemm.cuh"
+#include "gemm.h"
 
 int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);
 
@@ -59,13 +60,6 @@ void wb_gemm_state_destroy(WbBackend* b) {
     b->gemm_state = nullptr;
 }
 
-// One GEMM operand as the tensor core sees it: `rows` x `k` elements, either K-major (element
-// (r, kk) at ptr + r*ld + kk) or MN-major (element (r, kk) at ptr + kk*ld + r).
-struct WbGemmOperand {
-    const float* ptr;
-    int64_t rows, k, ld, batch_stride;  // batch_stride 0 = shared by every batch
-    bool mn_major;
-};
 
 namespace {
 
@@ -92,7 +86,8 @@ int make_map(GemmState* st, const WbGemmOperand& o, int64_t batch, int box_rows,
     cuuint32_t box[3] = {32u, static_cast<cuuint32_t>(o.mn_major ? tc::BK : box_rows), 1u};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(o.ptr), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, o.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         wb_set_error("cuTensorMapEncodeTiled failed with %d (inner %lld, outer %lld, ld %lld, batch %lld)", static_cast<int>(r),
@@ -152,8 +147,13 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
 
 // Runs D = A x B (+ epilogue) on the tensor cores.  mode: WB_MM_TF32 or WB_MM_TF32X3.
 // Returns WB_ERR_UNSUPPORTED (without setting an error message) if an operand cannot be read by TMA.
-int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int mode,
-               int force_splits) {
+// span_batch > 0: A and B are batched K-major operands of `span_batch` images and the contraction
+// runs over (image, k) pairs, giving one un-batched [m, n] result (a convolution's weight gradient).
+int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in, int m, int n, int k, tc::Epilogue ep, int mode,
+               int force_splits, int64_t span_batch) {
+    const int64_t batch = span_batch > 0 ? span_batch : batch_in;  // images the tensor maps cover
+    const int64_t grid_batch = span_batch > 0 ? 1 : batch_in;      // independent outputs
+    if (span_batch > 0 && (A.mn_major || B.mn_major || A.batch_stride == 0 || B.batch_stride == 0)) return WB_ERR_UNSUPPORTED;
     if (!operand_ok(A, batch) || !operand_ok(B, batch)) return WB_ERR_UNSUPPORTED;
     GemmState* st = nullptr;
     WB_TRY(get_state(be, &st));
@@ -199,11 +199,17 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, i
     args.m = m;
     args.n = n;
     args.k_blocks = (k + tc::BK - 1) / tc::BK;
+    args.kpb = 0;
+    if (span_batch > 0) {
+        args.kpb = args.k_blocks;
+        WB_REQUIRE(span_batch * args.kpb < (int64_t(1) << 31), WB_ERR_UNSUPPORTED, "gemm: contraction too long");
+        args.k_blocks = static_cast<int>(span_batch * args.kpb);
+    }
     args.batched_a = A.batch_stride != 0;
     args.batched_b = B.batch_stride != 0;
     args.error_flag = st->error_flag;
     const int tiles_m = (m + tc::BM - 1) / tc::BM, tiles_n = (n + BN - 1) / BN;
-    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * batch;
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
     int splits = 1;
     if (force_splits > 0) splits = force_splits;
     else if (tiles * 2 <= be->sm_count && args.k_blocks >= 16) {
@@ -218,7 +224,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, i
     void* part = nullptr;
     size_t kp = 0;
     if (splits > 1) {
-        const int64_t per_split = batch * static_cast<int64_t>(m) * n;
+        const int64_t per_split = grid_batch * static_cast<int64_t>(m) * n;
         status = wb_arena_alloc(be, static_cast<size_t>(per_split) * splits * sizeof(float), &part, &kp);
         if (status == WB_OK) {
             args.ep = tc::Epilogue{static_cast<float*>(part), n, static_cast<int64_t>(m) * n, nullptr, nullptr, 0, 0};
@@ -229,8 +235,8 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, i
         args.split_stride_d = 0;
     }
     if (status == WB_OK) {
-        WB_REQUIRE(batch * splits <= 65535, WB_ERR_UNSUPPORTED, "gemm: batch x split-K exceeds the grid limit");
-        dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m), static_cast<unsigned>(batch * splits));
+        WB_REQUIRE(grid_batch * splits <= 65535, WB_ERR_UNSUPPORTED, "gemm: batch x split-K exceeds the grid limit");
+        dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m), static_cast<unsigned>(grid_batch * splits));
         const bool amn = A.mn_major, bmn = B.mn_major;
         constexpr int STG = 6;
         if (!amn && !bmn) status = launch_tc<BN, STG, false, false>(be, st, args, grid);
@@ -239,7 +245,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, i
         else status = launch_tc<BN, STG, true, true>(be, st, args, grid);
     }
     if (status == WB_OK && splits > 1) {
-        const int64_t total = batch * static_cast<int64_t>(m) * n;
+        const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
         splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
                                                                                         total, m, n, ep);
         cudaError_t e = cudaPeekAtLastError();
@@ -293,7 +299,7 @@ extern "C" int wb_matmul_into(WbBackend* b, const WbView* a, const WbView* bb, v
         if (bs == 1) { A.batch_stride = 0; B.batch_stride = 0; }
         if (ok) {
             tc::Epilogue ep{static_cast<float*>(out), n, m * n, nullptr, nullptr, 0, 0};
-            int s = wb_tc_gemm(b, A, B, bs, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ep, b->matmul_mode, 0);
+            int s = wb_tc_gemm(b, A, B, bs, static_cast<int>(m), static_cast<int>(n), static_cast<int>(k), ep, b->matmul_mode, 0, 0);
             if (s != WB_ERR_UNSUPPORTED) return s;
         }
     }

@@ -49,6 +49,7 @@ struct Args {
     int k_blocks;          // BK-blocks of the contraction, per segment
     int splits;            // split-K factor: blockIdx.z = batch * splits + split
     int batched_a, batched_b;  // 0: operand shared by every batch (TMA coordinate 0)
+    int kpb;                   // K blocks per image when the contraction spans the batch, else 0
     Epilogue ep;
     int64_t split_stride_d;    // distance between split-K partial outputs
     int* error_flag;
@@ -92,13 +93,15 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 // Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1 (sm_100).
 //   bits [0,14)  start address >> 4      bits [16,30) leading-dim byte offset >> 4
 //   bits [32,46) stride-dim byte offset >> 4   bits [46,48) version = 1   bits [61,64) layout = 2 (128B swizzle)
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//   layout 2 = 128B swizzle of 16-byte chunks (K-major operands); layout 1 = 128B swizzle of 32-byte chunks,
+//   the only swizzled layout the tensor core accepts for MN-major 32-bit operands.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(layout) << 61;
     return d;
 }
 
@@ -199,8 +202,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
                 mbar_expect_tx(&ss.full[s], stage_bytes);
-                const int k0 = kb * BK;
-                const int za = args.batched_a ? batch : 0, zb = args.batched_b ? batch : 0;
+                // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
+                // operand pair, kpb blocks per image (a convolution's weight gradient); the image
+                // index becomes the third TMA coordinate and each image's tail is zero-filled.
+                const int k0 = (args.kpb > 0 ? kb % args.kpb : kb) * BK;
+                const int kz = args.kpb > 0 ? kb / args.kpb : 0;
+                const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
+                const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
                 if constexpr (A_MN) {
 #pragma unroll
                     for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
@@ -226,11 +234,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             const uint32_t a_base = smem_u32(&ss.a[s][0]), b_base = smem_u32(&ss.b[s][0]);
 #pragma unroll
             for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                // K-major: rows of 128 B, 8-row groups 1024 B apart; a K step of 8 elements is +32 B
+                // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8 elements is +32 B
                 //          inside the swizzle row.
-                // MN-major: 32-element column blocks 32*BK*4 B apart (LBO), 8-row K groups 1024 B apart.
-                uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 1024) : make_smem_desc(a_base + ks * 32, 16, 1024);
-                uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 1024) : make_smem_desc(b_base + ks * 32, 16, 1024);
+                // MN-major: each K index is a 128 B row of 32 consecutive M/N elements; rows come in
+                //          groups of 4 (512 B apart, SBO), 32-element M/N blocks are 32*BK*4 B apart (LBO);
+                //          a K step of 8 is two groups = +1024 B.
+                uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
+                uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
                 umma_tf32(tmem_d, ad, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
             }
             umma_commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it

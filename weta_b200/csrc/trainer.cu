@@ -1,1 +1,528 @@
-// Fused training-step runner.
+// Fused training-step runner for the named models (the MLP of crates/weta/examples/mnist_mlp.rs and
+// the conv-BN CNN of crates/weta/examples/mnist_cnn.rs, at any width).
+//
+// Where the reference's step is ~400 primitive calls driven by its autograd graph
+// (crates/weta-autograd/src/graph.rs:227-276), this runner issues a few dozen kernels in a fixed
+// order: for each layer the forward op, then the hand-ordered backward, then one Adam pass over a
+// flat parameter arena.  Arithmetic follows the reference's definitions (functional.rs, ops.rs,
+// optim lib.rs as cited at each step); parameters, gradients and optimizer state keep the
+// reference's tensor shapes and [out, in] / [O, C, kh, kw] element order.
+//
+// The arena holds the layers in REVERSE order, so the ranges whose gradients are finished first
+// in backward are contiguous at the front; after each layer's gradients are written the optional
+// callback fires with that range, which is where a data-parallel caller starts its all-reduce
+// while earlier layers are still being differentiated.
+#include <algorithm>
+#include <cmath>
+#include <vector>
+
+#include "common.h"
+#include "gemm.h"
+
+namespace {
+
+enum { L_CONV = 0, L_LINEAR = 1, L_DROPOUT = 2 };
+
+struct Layer {
+    int kind;
+    // conv block: conv3x3(pad 1) -> BatchNorm2d -> ReLU -> MaxPool2d(2)
+    int cin = 0, cout = 0, h = 0, w = 0;
+    // linear
+    int in = 0, out = 0, relu = 0;
+    // dropout
+    double p = 0.0;
+    // offsets into the flat arena (elements); -1 when absent
+    int64_t off_w = -1, off_b = -1, off_gamma = -1, off_beta = -1;
+    int64_t range_begin = 0, range_len = 0;
+    // buffers
+    float* running_mean = nullptr;
+    float* running_var = nullptr;
+    float* save_mean = nullptr;
+    float* save_rstd = nullptr;
+    float* cols = nullptr;      // [B, cin*9, h*w]
+    float* conv_out = nullptr;  // [B, cout, h, w]
+    float* out_act = nullptr;   // layer output
+    int64_t out_elems = 0;      // per-sample size of the layer output
+    bool relu_bwd_done = false;
+};
+
+}  // namespace
+
+struct WbTrainer {
+    WbBackend* be = nullptr;
+    int64_t batch = 0;
+    int64_t in_elems = 0;  // per-sample input size
+    std::vector<Layer> layers;
+    int64_t n_params = 0;
+    float *theta = nullptr, *grad = nullptr, *m = nullptr, *v = nullptr;
+    float* x_in = nullptr;       // staged input  [B, in_elems]
+    int64_t* y_in = nullptr;     // staged labels [B]
+    float* dlogits = nullptr;
+    float* loss_dev = nullptr;
+    float* loss_pinned = nullptr;
+    float* gbuf[2] = {nullptr, nullptr};  // ping-pong gradient-of-activation buffers
+    float* dcols = nullptr;
+    int64_t max_act = 0;
+    int64_t t = 0;
+    WbAdamConfig adam{};
+    int matmul_mode = WB_MM_TF32;
+    int classes = 0;
+    wb_bucket_callback cb = nullptr;
+    void* cb_user = nullptr;
+    std::vector<void*> owned;
+    // reference-order parameter table: (offset, len)
+    std::vector<std::pair<int64_t, int64_t>> param_table;
+};
+
+namespace {
+
+int dev_alloc(WbTrainer* t, size_t bytes, void** out) {
+    cudaError_t e = cudaMalloc(out, bytes ? bytes : 4);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        wb_set_error("trainer: allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? WB_ERR_OOM : WB_ERR_CUDA;
+    }
+    t->owned.push_back(*out);
+    return WB_OK;
+}
+
+template <class T>
+int dev_alloc_t(WbTrainer* t, int64_t n, T** out) {
+    void* p = nullptr;
+    WB_TRY(dev_alloc(t, static_cast<size_t>(n) * sizeof(T), &p));
+    *out = static_cast<T*>(p);
+    return WB_OK;
+}
+
+// D[batch][m][n] = A x B through the tensor cores, or the CUDA-core tiles when TMA cannot read an operand.
+int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int64_t span_batch = 0) {
+    const int mode = t->matmul_mode;
+    if (mode != WB_MM_FP32 && static_cast<int64_t>(m) * n * k >= (1 << 15)) {
+        int s = wb_tc_gemm(t->be, A, B, batch, m, n, k, ep, mode, 0, span_batch);
+        if (s != WB_ERR_UNSUPPORTED) return s;
+    }
+    WB_REQUIRE(span_batch == 0 && !ep.accumulate, WB_ERR_UNSUPPORTED, "trainer: no CUDA-core path for this contraction");
+    // CUDA-core path: describe the operands as [B, M, K] x [B, K, N] views.
+    WbView a{}, b{};
+    a.data = const_cast<float*>(A.ptr); a.dtype = WB_F32; a.ndim = 3; a.offset = 0;
+    a.shape[0] = batch; a.shape[1] = m; a.shape[2] = k;
+    a.stride[0] = A.batch_stride; a.stride[1] = A.mn_major ? 1 : A.ld; a.stride[2] = A.mn_major ? A.ld : 1;
+    b.data = const_cast<float*>(B.ptr); b.dtype = WB_F32; b.ndim = 3; b.offset = 0;
+    b.shape[0] = batch; b.shape[1] = k; b.shape[2] = n;
+    b.stride[0] = B.batch_stride; b.stride[1] = B.mn_major ? B.ld : 1; b.stride[2] = B.mn_major ? 1 : B.ld;
+    WB_REQUIRE(ep.ldd == n && (batch == 1 || ep.batch_stride_d == static_cast<int64_t>(m) * n), WB_ERR_UNSUPPORTED,
+               "trainer: CUDA-core path needs a dense output");
+    WB_TRY(wb_matmul_simt(t->be, &a, &b, ep.out));
+    if (ep.bias_n || ep.bias_m || ep.relu) {
+        // bias / ReLU as one broadcast add (+ relu) over the dense result
+        WbView o{}, bias{};
+        o.data = ep.out; o.dtype = WB_F32; o.ndim = 3; o.shape[0] = batch; o.shape[1] = m; o.shape[2] = n;
+        o.stride[0] = static_cast<int64_t>(m) * n; o.stride[1] = n; o.stride[2] = 1;
+        if (ep.bias_n || ep.bias_m) {
+            bias = o;
+            bias.data = const_cast<float*>(ep.bias_n ? ep.bias_n : ep.bias_m);
+            bias.stride[0] = 0; bias.stride[1] = ep.bias_m ? 1 : 0; bias.stride[2] = ep.bias_n ? 1 : 0;
+            WB_TRY(wb_binary_into(t->be, WB_ADD, &o, &bias, ep.out));
+        }
+        if (ep.relu) WB_TRY(wb_unary_into(t->be, WB_RELU, 0.0, 0.0, &o, ep.out));
+    }
+    return WB_OK;
+}
+
+// dst[j] = sum_i src[i][j] over a dense [rows, cols] matrix (a bias gradient, crates/weta-autograd/src/ops.rs:46-58).
+int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, float* dst) {
+    WbView v{};
+    v.data = const_cast<float*>(src); v.dtype = WB_F32; v.ndim = 2;
+    v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = cols; v.stride[1] = 1;
+    return wb_reduce_into(t->be, WB_SUM, &v, 0, dst);
+}
+
+int relu_bwd_inplace(WbTrainer* t, float* g, const float* y, int64_t n) {
+    // g *= step(y): UnaryBw for ReLU (crates/weta-autograd/src/ops.rs:85), p = 0 dropout = identity mask
+    return wb_dropout_relu_bwd(t->be, g, y, g, n, 0.0, 0);
+}
+
+}  // namespace
+
+extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_layers, int64_t batch, int64_t in_c, int64_t in_h,
+                                 int64_t in_w, const WbAdamConfig* adam, int matmul_mode, WbTrainer** out) {
+    WB_REQUIRE(b && specs && out && adam && n_layers > 0 && batch > 0, WB_ERR_INVALID, "wb_trainer_create: bad arguments");
+    WB_CHECK_CUDA(cudaSetDevice(b->ordinal));
+    WbTrainer* t = new WbTrainer();
+    t->be = b;
+    t->batch = batch;
+    t->adam = *adam;
+    t->matmul_mode = matmul_mode;
+    t->in_elems = in_c * in_h * in_w;
+    int64_t c = in_c, h = in_h, w = in_w, flat = t->in_elems;
+    bool spatial = in_h > 0 && in_w > 0 && !(in_h == 1 && in_w == 1 && false);
+    for (int i = 0; i < n_layers; ++i) {
+        Layer L;
+        L.kind = specs[i].kind;
+        if (L.kind == L_CONV) {
+            if (!spatial || specs[i].a != c || h % 2 || w % 2) {
+                delete t;
+                wb_set_error("trainer: conv block %d expects %d input channels on an even-sized image, got %lld x %lld x %lld", i, specs[i].a,
+                             (long long)c, (long long)h, (long long)w);
+                return WB_ERR_INVALID;
+            }
+            L.cin = static_cast<int>(c); L.cout = specs[i].b; L.h = static_cast<int>(h); L.w = static_cast<int>(w);
+            c = L.cout; h /= 2; w /= 2;
+            flat = c * h * w;
+            L.out_elems = flat;
+        } else if (L.kind == L_LINEAR) {
+            if (specs[i].a != flat) {
+                delete t;
+                wb_set_error("trainer: linear layer %d expects %d inputs, the previous layer gives %lld", i, specs[i].a, (long long)flat);
+                return WB_ERR_INVALID;
+            }
+            spatial = false;
+            L.in = specs[i].a; L.out = specs[i].b; L.relu = specs[i].c;
+            flat = L.out;
+            L.out_elems = flat;
+        } else if (L.kind == L_DROPOUT) {
+            L.p = specs[i].p;
+            L.out_elems = flat;
+            if (!(L.p >= 0.0 && L.p < 1.0)) { delete t; wb_set_error("trainer: dropout probability must be in [0, 1)"); return WB_ERR_INVALID; }
+        } else {
+            delete t;
+            wb_set_error("trainer: unknown layer kind %d", L.kind);
+            return WB_ERR_INVALID;
+        }
+        t->layers.push_back(L);
+    }
+    WB_REQUIRE(t->layers.back().kind == L_LINEAR, WB_ERR_INVALID, "trainer: the last layer must be linear (the logits)");
+    t->classes = t->layers.back().out;
+    // Arena layout: last layer first.  Each range is padded to 4 elements so every tensor starts
+    // on a 16-byte boundary (TMA operands).
+    auto pad4 = [](int64_t n) { return (n + 3) / 4 * 4; };
+    int64_t off = 0;
+    for (int i = n_layers - 1; i >= 0; --i) {
+        Layer& L = t->layers[i];
+        L.range_begin = off;
+        if (L.kind == L_CONV) {
+            L.off_w = off; off += pad4(static_cast<int64_t>(L.cout) * L.cin * 9);
+            L.off_b = off; off += pad4(L.cout);
+            L.off_gamma = off; off += pad4(L.cout);
+            L.off_beta = off; off += pad4(L.cout);
+        } else if (L.kind == L_LINEAR) {
+            L.off_w = off; off += pad4(static_cast<int64_t>(L.out) * L.in);
+            L.off_b = off; off += pad4(L.out);
+        }
+        L.range_len = off - L.range_begin;
+    }
+    t->n_params = off;
+    for (const Layer& L : t->layers) {  // reference order: layer by layer, weight, bias, (bn weight, bn bias)
+        if (L.kind == L_CONV) {
+            t->param_table.push_back({L.off_w, static_cast<int64_t>(L.cout) * L.cin * 9});
+            t->param_table.push_back({L.off_b, L.cout});
+            t->param_table.push_back({L.off_gamma, L.cout});
+            t->param_table.push_back({L.off_beta, L.cout});
+        } else if (L.kind == L_LINEAR) {
+            t->param_table.push_back({L.off_w, static_cast<int64_t>(L.out) * L.in});
+            t->param_table.push_back({L.off_b, L.out});
+        }
+    }
+    int s = WB_OK;
+    auto A = [&](int st) { if (s == WB_OK) s = st; };
+    A(dev_alloc_t(t, t->n_params, &t->theta));
+    A(dev_alloc_t(t, t->n_params, &t->grad));
+    A(dev_alloc_t(t, t->n_params, &t->m));
+    A(dev_alloc_t(t, t->n_params, &t->v));
+    A(dev_alloc_t(t, batch * t->in_elems, &t->x_in));
+    A(dev_alloc_t(t, batch, &t->y_in));
+    A(dev_alloc_t(t, batch * t->classes, &t->dlogits));
+    A(dev_alloc_t(t, 4, &t->loss_dev));
+    int64_t max_act = batch * t->in_elems, max_dcols = 0;
+    bool first_conv = true;
+    for (Layer& L : t->layers) {
+        if (L.kind == L_CONV) {
+            int64_t hw = static_cast<int64_t>(L.h) * L.w;
+            A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
+            A(dev_alloc_t(t, batch * L.cout * hw, &L.conv_out));
+            A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
+            A(dev_alloc_t(t, L.cout, &L.running_mean));
+            A(dev_alloc_t(t, L.cout, &L.running_var));
+            A(dev_alloc_t(t, L.cout, &L.save_mean));
+            A(dev_alloc_t(t, L.cout, &L.save_rstd));
+            max_act = std::max(max_act, batch * L.cout * hw);
+            if (!first_conv) max_dcols = std::max(max_dcols, batch * L.cin * 9 * hw);
+            first_conv = false;
+        } else {
+            A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
+            max_act = std::max(max_act, batch * L.out_elems);
+        }
+    }
+    t->max_act = max_act;
+    A(dev_alloc_t(t, max_act, &t->gbuf[0]));
+    A(dev_alloc_t(t, max_act, &t->gbuf[1]));
+    if (max_dcols > 0) A(dev_alloc_t(t, max_dcols, &t->dcols));
+    if (s == WB_OK) {
+        cudaError_t e = cudaMallocHost(&t->loss_pinned, 16);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); wb_set_error("trainer: pinned allocation failed"); s = WB_ERR_CUDA; }
+    }
+    if (s == WB_OK) {
+        cudaMemsetAsync(t->theta, 0, t->n_params * sizeof(float), b->stream);
+        cudaMemsetAsync(t->grad, 0, t->n_params * sizeof(float), b->stream);
+        cudaMemsetAsync(t->m, 0, t->n_params * sizeof(float), b->stream);
+        cudaMemsetAsync(t->v, 0, t->n_params * sizeof(float), b->stream);
+    }
+    if (s != WB_OK) {
+        for (void* p : t->owned) cudaFree(p);
+        delete t;
+        return s;
+    }
+    *out = t;
+    return WB_OK;
+}
+
+extern "C" int wb_trainer_destroy(WbTrainer* t) {
+    if (!t) return WB_OK;
+    cudaStreamSynchronize(t->be->stream);
+    for (void* p : t->owned) cudaFree(p);
+    if (t->loss_pinned) cudaFreeHost(t->loss_pinned);
+    delete t;
+    return WB_OK;
+}
+
+// Default initialisation (crates/weta-nn/src/layers.rs:19-26): weight then bias of every Linear /
+// Conv2d from U(-1/sqrt(fan_in), 1/sqrt(fan_in)), one seed each in creation order; BatchNorm
+// weight 1, bias 0, running mean 0, running variance 1 (layers.rs:235-247).
+extern "C" int wb_trainer_init(WbTrainer* t, const uint64_t* seeds, int n_seeds) {
+    WB_REQUIRE(t && seeds, WB_ERR_INVALID, "wb_trainer_init: null pointer");
+    int need = 0;
+    for (const Layer& L : t->layers) need += (L.kind == L_CONV || L.kind == L_LINEAR) ? 2 : 0;
+    WB_REQUIRE(n_seeds == need, WB_ERR_INVALID, "wb_trainer_init: expected %d seeds, got %d", need, n_seeds);
+    WbBackend* b = t->be;
+    WB_CHECK_CUDA(cudaMemsetAsync(t->theta, 0, t->n_params * sizeof(float), b->stream));
+    WB_CHECK_CUDA(cudaMemsetAsync(t->m, 0, t->n_params * sizeof(float), b->stream));
+    WB_CHECK_CUDA(cudaMemsetAsync(t->v, 0, t->n_params * sizeof(float), b->stream));
+    t->t = 0;
+    int si = 0;
+    std::vector<float> ones;
+    for (Layer& L : t->layers) {
+        if (L.kind == L_DROPOUT) continue;
+        int64_t fan_in = L.kind == L_CONV ? static_cast<int64_t>(L.cin) * 9 : L.in;
+        int64_t wn = L.kind == L_CONV ? static_cast<int64_t>(L.cout) * L.cin * 9 : static_cast<int64_t>(L.out) * L.in;
+        int64_t bn = L.kind == L_CONV ? L.cout : L.out;
+        double bound = 1.0 / std::sqrt(static_cast<double>(fan_in));
+        WB_TRY(wb_random_into(b, wn, WB_F32, WB_UNIFORM, -bound, bound, seeds[si++], t->theta + L.off_w));
+        WB_TRY(wb_random_into(b, bn, WB_F32, WB_UNIFORM, -bound, bound, seeds[si++], t->theta + L.off_b));
+        if (L.kind == L_CONV) {
+            ones.assign(L.cout, 1.0f);
+            WB_CHECK_CUDA(cudaMemcpyAsync(t->theta + L.off_gamma, ones.data(), L.cout * sizeof(float), cudaMemcpyHostToDevice, b->stream));
+            WB_CHECK_CUDA(cudaMemcpyAsync(L.running_var, ones.data(), L.cout * sizeof(float), cudaMemcpyHostToDevice, b->stream));
+            WB_CHECK_CUDA(cudaMemsetAsync(L.running_mean, 0, L.cout * sizeof(float), b->stream));
+            WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));  // `ones` is pageable host memory
+        }
+    }
+    return WB_OK;
+}
+
+extern "C" int64_t wb_trainer_arena_len(const WbTrainer* t) { return t->n_params; }
+extern "C" float* wb_trainer_params(WbTrainer* t) { return t->theta; }
+extern "C" float* wb_trainer_grads(WbTrainer* t) { return t->grad; }
+extern "C" float* wb_trainer_exp_avg(WbTrainer* t) { return t->m; }
+extern "C" float* wb_trainer_exp_avg_sq(WbTrainer* t) { return t->v; }
+extern "C" float* wb_trainer_input(WbTrainer* t) { return t->x_in; }
+extern "C" int64_t* wb_trainer_labels(WbTrainer* t) { return t->y_in; }
+extern "C" float* wb_trainer_loss_ptr(WbTrainer* t) { return t->loss_dev; }
+extern "C" int wb_trainer_num_tensors(const WbTrainer* t) { return static_cast<int>(t->param_table.size()); }
+
+extern "C" int wb_trainer_tensor_range(const WbTrainer* t, int index, int64_t* offset, int64_t* len) {
+    WB_REQUIRE(t && index >= 0 && index < static_cast<int>(t->param_table.size()), WB_ERR_INVALID, "trainer: no parameter tensor %d", index);
+    *offset = t->param_table[index].first;
+    *len = t->param_table[index].second;
+    return WB_OK;
+}
+
+extern "C" int wb_trainer_bn_buffers(WbTrainer* t, int conv_index, float** running_mean, float** running_var, int64_t* channels) {
+    int k = 0;
+    for (Layer& L : t->layers) {
+        if (L.kind != L_CONV) continue;
+        if (k++ == conv_index) {
+            *running_mean = L.running_mean;
+            *running_var = L.running_var;
+            *channels = L.cout;
+            return WB_OK;
+        }
+    }
+    wb_set_error("trainer: no conv block %d", conv_index);
+    return WB_ERR_INVALID;
+}
+
+extern "C" int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* user) {
+    t->cb = cb;
+    t->cb_user = user;
+    return WB_OK;
+}
+
+// Forward + loss + backward over the staged batch (wb_trainer_input / wb_trainer_labels).
+// dropout_seeds: one per dropout layer, in forward order (the reference draws them from the global
+// generator in that order, crates/weta-tensor/src/random.rs:95-98).
+extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds) {
+    WB_REQUIRE(t, WB_ERR_INVALID, "wb_trainer_forward_backward: null trainer");
+    WbBackend* b = t->be;
+    const int64_t B = t->batch;
+    int n_drop = 0;
+    for (const Layer& L : t->layers) n_drop += L.kind == L_DROPOUT;
+    WB_REQUIRE(n_seeds == n_drop && (n_drop == 0 || dropout_seeds), WB_ERR_INVALID, "trainer: expected %d dropout seeds, got %d", n_drop, n_seeds);
+    const int nl = static_cast<int>(t->layers.size());
+    // ---- forward ----------------------------------------------------------------------------
+    const float* act = t->x_in;
+    int di = 0;
+    std::vector<uint64_t> seed_of(nl, 0);
+    for (int i = 0; i < nl; ++i) {
+        Layer& L = t->layers[i];
+        L.relu_bwd_done = false;
+        if (L.kind == L_CONV) {
+            // F::conv2d_ext (crates/weta-nn/src/functional.rs:84-106): im2col, W[O, C*9] x cols[n], + bias[O,1]
+            const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
+            WbView xv{};
+            xv.data = const_cast<float*>(act); xv.dtype = WB_F32; xv.ndim = 4;
+            xv.shape[0] = B; xv.shape[1] = L.cin; xv.shape[2] = L.h; xv.shape[3] = L.w;
+            xv.stride[0] = L.cin * hw; xv.stride[1] = hw; xv.stride[2] = L.w; xv.stride[3] = 1;
+            WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
+            WB_TRY(wb_im2col_into(b, &xv, &cp, L.cols));
+            WbGemmOperand Aw{t->theta + L.off_w, L.cout, ck, ck, 0, false};
+            WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
+            tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
+            WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep));
+            // BatchNorm2d (train) -> ReLU -> MaxPool2d(2)
+            WB_TRY(wb_bn_relu_pool_fwd(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.running_mean,
+                                       L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd));
+            act = L.out_act;
+        } else if (L.kind == L_LINEAR) {
+            // F::linear (functional.rs:54-60): x W^T + b, ReLU folded into the epilogue
+            WbGemmOperand Ax{act, B, L.in, L.in, 0, false};
+            WbGemmOperand Bw{t->theta + L.off_w, L.out, L.in, L.in, 0, false};
+            tc::Epilogue ep{L.out_act, L.out, 0, t->theta + L.off_b, nullptr, L.relu, 0};
+            WB_TRY(gemm(t, Ax, Bw, 1, static_cast<int>(B), L.out, L.in, ep));
+            act = L.out_act;
+        } else {
+            seed_of[i] = dropout_seeds[di++];
+            WB_TRY(wb_dropout_fwd(b, act, L.out_act, B * L.out_elems, L.p, seed_of[i]));
+            act = L.out_act;
+        }
+    }
+    // ---- loss: cross-entropy, mean over the batch (crates/weta-autograd/src/ops.rs:499-519) ---
+    WB_TRY(wb_softmax_ce(b, act, t->y_in, B, t->classes, nullptr, t->dlogits, nullptr, t->loss_dev, 1.0));
+    // ---- backward ---------------------------------------------------------------------------
+    const float* g = t->dlogits;  // gradient w.r.t. the current layer's output
+    int pp = 0;
+    for (int i = nl - 1; i >= 0; --i) {
+        Layer& L = t->layers[i];
+        const float* in_act = i == 0 ? t->x_in : t->layers[i - 1].out_act;
+        const bool need_dx = i > 0;
+        if (L.kind == L_LINEAR) {
+            float* gz = const_cast<float*>(g);
+            if (L.relu && !L.relu_bwd_done) WB_TRY(relu_bwd_inplace(t, gz, L.out_act, B * L.out));
+            // MatmulBw (ops.rs:821-827): dW = dZ^T X, db = sum over the batch, dX = dZ W
+            WbGemmOperand Az{gz, L.out, B, L.out, 0, true};
+            WbGemmOperand Bx{in_act, L.in, B, L.in, 0, true};
+            tc::Epilogue epw{t->grad + L.off_w, L.in, 0, nullptr, nullptr, 0, 0};
+            WB_TRY(gemm(t, Az, Bx, 1, L.out, L.in, static_cast<int>(B), epw));
+            WB_TRY(column_sum(t, gz, B, L.out, t->grad + L.off_b));
+            if (need_dx) {
+                float* dx = t->gbuf[pp];
+                pp ^= 1;
+                WbGemmOperand Ad{gz, B, L.out, L.out, 0, false};
+                WbGemmOperand Bw{t->theta + L.off_w, L.in, L.out, L.in, 0, true};
+                tc::Epilogue epx{dx, L.in, 0, nullptr, nullptr, 0, 0};
+                WB_TRY(gemm(t, Ad, Bw, 1, static_cast<int>(B), L.in, L.out, epx));
+                g = dx;
+            }
+        } else if (L.kind == L_DROPOUT) {
+            // BinaryBw Mul (ops.rs:199): dx = dy * mask.  If a ReLU'd linear layer feeds this dropout, its
+            // step() factor is applied in the same pass.
+            float* dx = t->gbuf[pp];
+            pp ^= 1;
+            const float* relu_src = nullptr;
+            if (i > 0 && t->layers[i - 1].kind == L_LINEAR && t->layers[i - 1].relu) {
+                relu_src = t->layers[i - 1].out_act;
+                t->layers[i - 1].relu_bwd_done = true;
+            }
+            WB_TRY(wb_dropout_relu_bwd(b, g, relu_src, dx, B * L.out_elems, L.p, seed_of[i]));
+            g = dx;
+        } else {
+            const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
+            float* dconv = t->gbuf[pp];
+            pp ^= 1;
+            WB_TRY(wb_bn_relu_pool_bwd(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
+                                       L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_b));
+            // dW[O, C*9] = sum_n dY[n] cols[n]^T: one contraction over (n, position), not a batched
+            // product followed by a reduction over n (ops.rs:821-827 + sum_to_shape).
+            WbGemmOperand Ad{dconv, L.cout, hw, hw, L.cout * hw, false};
+            WbGemmOperand Bc{L.cols, ck, hw, hw, ck * hw, false};
+            tc::Epilogue epw{t->grad + L.off_w, ck, 0, nullptr, nullptr, 0, 0};
+            int s = WB_ERR_UNSUPPORTED;
+            if (t->matmul_mode != WB_MM_FP32) s = wb_tc_gemm(b, Ad, Bc, 1, L.cout, static_cast<int>(ck), static_cast<int>(hw), epw, t->matmul_mode, 0, B);
+            if (s == WB_ERR_UNSUPPORTED) {
+                // CUDA-core path: batched dY[n] cols[n]^T into scratch, then the sum over n.
+                void* tmp = nullptr;
+                size_t klass = 0;
+                WB_TRY(wb_arena_alloc(b, static_cast<size_t>(B) * L.cout * ck * sizeof(float), &tmp, &klass));
+                WbGemmOperand Bt{L.cols, ck, hw, hw, ck * hw, false};
+                tc::Epilogue ept{static_cast<float*>(tmp), ck, L.cout * ck, nullptr, nullptr, 0, 0};
+                int saved = t->matmul_mode;
+                t->matmul_mode = WB_MM_FP32;
+                s = gemm(t, Ad, Bt, B, L.cout, static_cast<int>(ck), static_cast<int>(hw), ept);
+                t->matmul_mode = saved;
+                if (s == WB_OK) s = column_sum(t, static_cast<float*>(tmp), B, L.cout * ck, t->grad + L.off_w);
+                wb_arena_free(b, tmp, klass);
+            }
+            WB_TRY(s);
+            if (need_dx) {
+                // dcols[n] = W^T dY[n], then col2im (Im2ColBw, ops.rs:865-868)
+                WbGemmOperand Aw{t->theta + L.off_w, ck, L.cout, ck, 0, true};
+                WbGemmOperand Bd{dconv, hw, L.cout, hw, L.cout * hw, true};
+                tc::Epilogue epc{t->dcols, hw, ck * hw, nullptr, nullptr, 0, 0};
+                WB_TRY(gemm(t, Aw, Bd, B, static_cast<int>(ck), static_cast<int>(hw), L.cout, epc));
+                float* dx = t->gbuf[pp];
+                pp ^= 1;
+                WbView cv{};
+                cv.data = t->dcols; cv.dtype = WB_F32; cv.ndim = 3;
+                cv.shape[0] = B; cv.shape[1] = ck; cv.shape[2] = hw;
+                cv.stride[0] = ck * hw; cv.stride[1] = hw; cv.stride[2] = 1;
+                WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
+                WB_TRY(wb_col2im_into(b, &cv, &cp, L.cin, L.h, L.w, dx));
+                g = dx;
+            }
+        }
+        if (t->cb && L.range_len > 0) t->cb(t->cb_user, t->grad + L.range_begin, L.range_len);
+    }
+    return WB_OK;
+}
+
+extern "C" int wb_trainer_adam_step(WbTrainer* t, double grad_scale) {
+    WB_REQUIRE(t, WB_ERR_INVALID, "wb_trainer_adam_step: null trainer");
+    t->t += 1;
+    const WbAdamConfig& a = t->adam;
+    return wb_adam_step(t->be, t->theta, t->grad, t->m, t->v, t->n_params, t->t, a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.decoupled,
+                        grad_scale);
+}
+
+// The call a user makes per step: host batch in, loss out.  Copies the batch from (pinned) host
+// memory, runs forward/backward/Adam and reads the loss back; waits for the stream.
+extern "C" int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,
+                                    float* host_loss) {
+    WB_REQUIRE(t && host_x && host_y, WB_ERR_INVALID, "wb_trainer_step_host: null pointer");
+    WbBackend* b = t->be;
+    WB_CHECK_CUDA(cudaMemcpyAsync(t->x_in, host_x, static_cast<size_t>(t->batch * t->in_elems) * sizeof(float), cudaMemcpyHostToDevice, b->stream));
+    WB_CHECK_CUDA(cudaMemcpyAsync(t->y_in, host_y, static_cast<size_t>(t->batch) * sizeof(int64_t), cudaMemcpyHostToDevice, b->stream));
+    WB_TRY(wb_trainer_forward_backward(t, dropout_seeds, n_seeds));
+    WB_TRY(wb_trainer_adam_step(t, 1.0));
+    WB_CHECK_CUDA(cudaMemcpyAsync(t->loss_pinned, t->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, b->stream));
+    WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));
+    if (host_loss) *host_loss = *t->loss_pinned;
+    return WB_OK;
+}
+
+extern "C" int wb_trainer_read_loss(WbTrainer* t, float* host_loss) {
+    WbBackend* b = t->be;
+    WB_CHECK_CUDA(cudaMemcpyAsync(t->loss_pinned, t->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, b->stream));
+    WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));
+    *host_loss = *t->loss_pinned;
+    return WB_OK;
+}
