@@ -1,0 +1,292 @@
+"""Benchmark of the hot path: CNN train samples/s on 1/2/4/8 B200, plus the roofline of its dominant kernel.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference --steps 2 --warmup 1      # the CPU path, on the host cores
+
+Workload: the data-parallel wide CNN (conv 3->128 + BN + ReLU + pool, conv 128->256 + BN + ReLU + pool,
+dropout, fc 16384->1024, ReLU, dropout, fc 1024->10; 17.1 M parameters), synthetic 3x32x32 images in
+[0,1) and uniform labels standing in for CIFAR-10 (no dataset is available offline), global batch 4096
+split evenly over the ranks, f32 storage with TF32 tensor-core contractions, Adam lr 1e-3, one model
+seed shared by all ranks.  A step is forward + cross-entropy + backward + gradient all-reduce + Adam.
+
+One JSON line is printed by rank 0.  `value` times the step with inputs already resident in HBM;
+`e2e` times the same step through the host-facing call with pinned host buffers (upload of the batch and
+read-back of the loss inside the timed region).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 4096
+METRIC = "cnn_train_samples_per_s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([f.strip() for f in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        mhz, mx, reasons = [], None, set()
+        for s in self.samples:
+            if len(s) < 6:
+                continue
+            try:
+                mhz.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def cpu_reference_run(steps: int, warmup: int, sample_batch: int):
+    """The reference's CPU path (the oracle restating weta-cpu, driven op by op like the reference's
+    own autograd would) on a bounded sample of the workload, with every host thread."""
+    from oracle.cpu_backend import OracleBackend
+    from weta_b200 import nn
+    from weta_b200.workloads import WIDE_CNN, build_cnn, primitive_train_step, synthetic_batch
+
+    be = OracleBackend()
+    model = build_cnn(WIDE_CNN, be, 42)
+    opt = nn.Adam(model.parameters(), 1e-3)
+    batches = [synthetic_batch(WIDE_CNN, sample_batch, s, 0, be) for s in range(2)]
+    for s in range(warmup):
+        primitive_train_step(model, opt, *batches[s % 2])
+    t0 = time.perf_counter()
+    for s in range(steps):
+        primitive_train_step(model, opt, *batches[s % 2])
+    dt = time.perf_counter() - t0
+    return {"value": sample_batch * steps / dt, "unit": "samples/s", "cores": be.num_threads(), "kind": "port",
+            "sample": f"{steps} step(s) of the same wide CNN at batch {sample_batch} (of 4096), primitive-call stream on the C++ "
+                      f"restatement of weta-cpu, OpenMP over {be.num_threads()} threads", "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warmup = max(1, min(args.steps, 3)), max(1, min(args.warmup, 1))
+    r = cpu_reference_run(steps, warmup, args.cpu_batch)
+    line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": "wide CNN 3x32x32 (conv128-conv256-fc1024), CPU sample", "global_batch": args.cpu_batch},
+            "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-batch", type=int, default=32, help="sample batch of the CPU baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from weta_b200.backend import B200Backend
+    from weta_b200.core import manual_seed
+    from weta_b200.trainer import DataParallelTrainer, FusedTrainer, cnn_specs
+    from weta_b200.workloads import WIDE_CNN, synthetic_batch
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}"
+    assert args.warmup >= 3, "at least 3 warm-up steps"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cfg = WIDE_CNN
+    gb = args.global_batch
+    assert gb % world == 0
+    batch = gb // world
+
+    stream = torch.cuda.Stream()
+    be = B200Backend(local, stream=stream.cuda_stream)
+    manual_seed(42)  # one model seed shared by all ranks
+    tr = FusedTrainer(be, cnn_specs(cfg), batch, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=1)
+    tr.init_from_global_rng()
+    dp = DataParallelTrainer(tr, stream, world)
+
+    # Synthetic batches: drawn on the device from the counter RNG, then copied to pinned host memory for
+    # the end-to-end leg.  Two distinct batches alternate.
+    n_in = batch * cfg.in_ch * cfg.hw * cfg.hw
+    dev_batches, host_batches = [], []
+    for s in range(2):
+        x, y = synthetic_batch(cfg, batch, s, rank, be)
+        dev_batches.append((x, y))
+        hx = torch.empty(n_in, dtype=torch.float32, pin_memory=True)
+        hy = torch.empty(batch, dtype=torch.int64, pin_memory=True)
+        hx.copy_(torch.from_numpy(x.numpy().reshape(-1)))
+        hy.copy_(torch.from_numpy(y.numpy().reshape(-1)))
+        host_batches.append((hx, hy))
+    import ctypes
+
+    def stage_from_device(i):
+        x, y = dev_batches[i % 2]
+        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(x.layout.view(x.storage.ptr, 0)), 0, ctypes.c_void_p(tr.input_ptr())))
+        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(y.layout.view(y.storage.ptr, 2)), 2, ctypes.c_void_p(tr.labels_ptr())))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            fn(i)
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def resident_step(i):
+        stage_from_device(i)       # device-to-device: the batch is already in HBM
+        dp.forward_backward_step()
+
+    losses = []
+
+    def e2e_step(i):
+        losses.append(dp.step_host(*host_batches[i % 2]))
+
+    # ---- warm-up ------------------------------------------------------------------------------
+    for i in range(args.warmup):
+        resident_step(i)
+    be.gemm_check()
+
+    # ---- value: inputs resident in HBM, per-op timing on for the roofline ------------------------
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    tr.set_timing(True)
+    tr.timing_report()
+    launches0 = be.launch_count()
+    total_ms = timed(resident_step, args.steps)
+    launches = be.launch_count() - launches0
+    op_times = tr.timing_report()
+    tr.set_timing(False)
+    clocks = sampler.stop() if rank == 0 else None
+    value = gb * args.steps / (total_ms / 1e3)
+
+    # ---- e2e: through the host-facing call ------------------------------------------------------
+    for i in range(2):
+        e2e_step(i)
+    e2e_ms = timed(e2e_step, args.steps)
+    e2e_value = gb * args.steps / (e2e_ms / 1e3)
+    be.gemm_check()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel --------------------------------------------------------
+    peaks = load_peaks()
+    hw1, hw2 = cfg.hw * cfg.hw, (cfg.hw // 2) ** 2
+    flops = {  # algorithmic 2*M*N*K per launch, per rank
+        "L0.conv_fwd_gemm": 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1, "L0.conv_wgrad_gemm": 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1,
+        "L1.conv_fwd_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2, "L1.conv_wgrad_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2,
+        "L1.conv_dgrad_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2,
+        "L3.linear_fwd_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4), "L3.linear_wgrad_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4),
+        "L3.linear_dgrad_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4),
+    }
+    top = max(op_times.items(), key=lambda kv: kv[1][1])
+    shares = {k: round(v[1] / total_ms, 4) for k, v in sorted(op_times.items(), key=lambda kv: -kv[1][1])}
+    top_name, (top_calls, top_ms) = top
+    tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
+    if top_name in flops:
+        achieved = flops[top_name] / (top_ms / top_calls * 1e-3) / 1e12
+        roofline = {"kernel": top_name, "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
+                    "traffic": None, "peak_note": f"{peaks['source']} sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate)",
+                    "avg_ms_per_launch": top_ms / top_calls, "launches": top_calls}
+    else:
+        roofline = {"kernel": top_name, "bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
+                    "avg_ms_per_launch": top_ms / top_calls, "launches": top_calls}
+    gemm_ms = sum(v[1] for k, v in op_times.items() if k in flops)
+    gemm_flops = sum(flops[k] * v[0] for k, v in op_times.items() if k in flops)
+    roofline["all_contractions_tflops"] = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_run(2, 1, args.cpu_batch)
+        cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (TF32 contractions)",
+        "data": "synthetic",
+        "config": {"workload": "data-parallel wide CNN train step (conv3-128, conv128-256, fc16384-1024-10; BN, ReLU, maxpool, dropout 0.25)",
+                   "global_batch": gb, "per_gpu_batch": batch, "image": "3x32x32", "params": cfg.num_params(), "optimizer": "Adam lr 1e-3",
+                   "parallelism": f"dp{world}", "l2": "per-step working set is several GB, far larger than the 126 MB L2; two batches alternate",
+                   "step": "upload/stage + forward + cross-entropy + backward + all-reduce + Adam"},
+        "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": n_in * 4 + batch * 8,
+                "d2h_bytes_per_step": 4, "last_loss": losses[-1]},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "op_time_shares": shares,
+        "train_tflops": cfg.train_flops_per_sample() * value / 1e12,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

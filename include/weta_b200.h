@@ -270,6 +270,11 @@ int wb_trainer_adam_step(WbTrainer* t, double grad_scale);
 int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,
                          float* host_loss);
 int wb_trainer_read_loss(WbTrainer* t, float* host_loss);
+/* Per-op device timing (the counterpart of WETA_CUDA_PROFILE, crates/weta-cuda/src/profile.rs, without
+ * its per-call synchronisation): event pairs are recorded around each op while timing is on;
+ * the report waits for the stream and returns lines "label calls total_ms". */
+int wb_trainer_set_timing(WbTrainer* t, int on);
+const char* wb_trainer_timing_report(WbTrainer* t);
 
 #ifdef __cplusplus
 }

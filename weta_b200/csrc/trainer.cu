@@ -14,6 +14,7 @@
 // while earlier layers are still being differentiated.
 #include <algorithm>
 #include <cmath>
+#include <string>
 #include <vector>
 
 #include "common.h"
@@ -72,6 +73,13 @@ struct WbTrainer {
     std::vector<void*> owned;
     // reference-order parameter table: (offset, len)
     std::vector<std::pair<int64_t, int64_t>> param_table;
+    // optional per-op device timing: event pairs recorded around each op, read after the fact
+    bool timing = false;
+    std::vector<std::string> labels;
+    struct TimeRec { int label; cudaEvent_t e0, e1; };
+    std::vector<TimeRec> recs;
+    std::vector<cudaEvent_t> event_pool;
+    std::string timing_text;
 };
 
 namespace {
@@ -94,6 +102,41 @@ int dev_alloc_t(WbTrainer* t, int64_t n, T** out) {
     *out = static_cast<T*>(p);
     return WB_OK;
 }
+
+cudaEvent_t get_event(WbTrainer* t) {
+    if (!t->event_pool.empty()) {
+        cudaEvent_t e = t->event_pool.back();
+        t->event_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    return e;
+}
+
+// Records an event pair around one op when timing is on; costs a branch otherwise.  No waits here:
+// the elapsed times are read by wb_trainer_timing_report after the stream has drained.
+struct OpTimer {
+    WbTrainer* t;
+    int label = -1;
+    cudaEvent_t e0 = nullptr;
+    OpTimer(WbTrainer* tr, int layer, const char* what) : t(tr) {
+        if (!t->timing) return;
+        char name[64];
+        snprintf(name, sizeof name, "L%d.%s", layer, what);
+        for (size_t i = 0; i < t->labels.size(); ++i)
+            if (t->labels[i] == name) label = static_cast<int>(i);
+        if (label < 0) { t->labels.push_back(name); label = static_cast<int>(t->labels.size()) - 1; }
+        e0 = get_event(t);
+        cudaEventRecord(e0, t->be->stream);
+    }
+    ~OpTimer() {
+        if (!e0) return;
+        cudaEvent_t e1 = get_event(t);
+        cudaEventRecord(e1, t->be->stream);
+        t->recs.push_back({label, e0, e1});
+    }
+};
 
 // D[batch][m][n] = A x B through the tensor cores, or the CUDA-core tiles when TMA cannot read an operand.
 int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int64_t span_batch = 0) {
@@ -384,30 +427,33 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             xv.shape[0] = B; xv.shape[1] = L.cin; xv.shape[2] = L.h; xv.shape[3] = L.w;
             xv.stride[0] = L.cin * hw; xv.stride[1] = hw; xv.stride[2] = L.w; xv.stride[3] = 1;
             WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
-            WB_TRY(wb_im2col_into(b, &xv, &cp, L.cols));
+            { OpTimer tm(t, i, "im2col"); WB_TRY(wb_im2col_into(b, &xv, &cp, L.cols)); }
             WbGemmOperand Aw{t->theta + L.off_w, L.cout, ck, ck, 0, false};
             WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
             tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
-            WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep));
+            { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep)); }
             // BatchNorm2d (train) -> ReLU -> MaxPool2d(2)
-            WB_TRY(wb_bn_relu_pool_fwd(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.running_mean,
-                                       L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd));
+            {
+                OpTimer tm(t, i, "bn_relu_pool_fwd");
+                WB_TRY(wb_bn_relu_pool_fwd(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.running_mean,
+                                           L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd));
+            }
             act = L.out_act;
         } else if (L.kind == L_LINEAR) {
             // F::linear (functional.rs:54-60): x W^T + b, ReLU folded into the epilogue
             WbGemmOperand Ax{act, B, L.in, L.in, 0, false};
             WbGemmOperand Bw{t->theta + L.off_w, L.out, L.in, L.in, 0, false};
             tc::Epilogue ep{L.out_act, L.out, 0, t->theta + L.off_b, nullptr, L.relu, 0};
-            WB_TRY(gemm(t, Ax, Bw, 1, static_cast<int>(B), L.out, L.in, ep));
+            { OpTimer tm(t, i, "linear_fwd_gemm"); WB_TRY(gemm(t, Ax, Bw, 1, static_cast<int>(B), L.out, L.in, ep)); }
             act = L.out_act;
         } else {
             seed_of[i] = dropout_seeds[di++];
-            WB_TRY(wb_dropout_fwd(b, act, L.out_act, B * L.out_elems, L.p, seed_of[i]));
+            { OpTimer tm(t, i, "dropout_fwd"); WB_TRY(wb_dropout_fwd(b, act, L.out_act, B * L.out_elems, L.p, seed_of[i])); }
             act = L.out_act;
         }
     }
     // ---- loss: cross-entropy, mean over the batch (crates/weta-autograd/src/ops.rs:499-519) ---
-    WB_TRY(wb_softmax_ce(b, act, t->y_in, B, t->classes, nullptr, t->dlogits, nullptr, t->loss_dev, 1.0));
+    { OpTimer tm(t, nl, "softmax_ce"); WB_TRY(wb_softmax_ce(b, act, t->y_in, B, t->classes, nullptr, t->dlogits, nullptr, t->loss_dev, 1.0)); }
     // ---- backward ---------------------------------------------------------------------------
     const float* g = t->dlogits;  // gradient w.r.t. the current layer's output
     int pp = 0;
@@ -422,15 +468,15 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             WbGemmOperand Az{gz, L.out, B, L.out, 0, true};
             WbGemmOperand Bx{in_act, L.in, B, L.in, 0, true};
             tc::Epilogue epw{t->grad + L.off_w, L.in, 0, nullptr, nullptr, 0, 0};
-            WB_TRY(gemm(t, Az, Bx, 1, L.out, L.in, static_cast<int>(B), epw));
-            WB_TRY(column_sum(t, gz, B, L.out, t->grad + L.off_b));
+            { OpTimer tm(t, i, "linear_wgrad_gemm"); WB_TRY(gemm(t, Az, Bx, 1, L.out, L.in, static_cast<int>(B), epw)); }
+            { OpTimer tm(t, i, "linear_bias_grad"); WB_TRY(column_sum(t, gz, B, L.out, t->grad + L.off_b)); }
             if (need_dx) {
                 float* dx = t->gbuf[pp];
                 pp ^= 1;
                 WbGemmOperand Ad{gz, B, L.out, L.out, 0, false};
                 WbGemmOperand Bw{t->theta + L.off_w, L.in, L.out, L.in, 0, true};
                 tc::Epilogue epx{dx, L.in, 0, nullptr, nullptr, 0, 0};
-                WB_TRY(gemm(t, Ad, Bw, 1, static_cast<int>(B), L.in, L.out, epx));
+                { OpTimer tm(t, i, "linear_dgrad_gemm"); WB_TRY(gemm(t, Ad, Bw, 1, static_cast<int>(B), L.in, L.out, epx)); }
                 g = dx;
             }
         } else if (L.kind == L_DROPOUT) {
@@ -443,14 +489,18 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 relu_src = t->layers[i - 1].out_act;
                 t->layers[i - 1].relu_bwd_done = true;
             }
-            WB_TRY(wb_dropout_relu_bwd(b, g, relu_src, dx, B * L.out_elems, L.p, seed_of[i]));
+            { OpTimer tm(t, i, "dropout_bwd"); WB_TRY(wb_dropout_relu_bwd(b, g, relu_src, dx, B * L.out_elems, L.p, seed_of[i])); }
             g = dx;
         } else {
             const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
             float* dconv = t->gbuf[pp];
             pp ^= 1;
-            WB_TRY(wb_bn_relu_pool_bwd(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
-                                       L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_b));
+            {
+                OpTimer tm(t, i, "bn_relu_pool_bwd");
+                WB_TRY(wb_bn_relu_pool_bwd(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
+                                           L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_b));
+            }
+            OpTimer* wt = new OpTimer(t, i, "conv_wgrad_gemm");
             // dW[O, C*9] = sum_n dY[n] cols[n]^T: one contraction over (n, position), not a batched
             // product followed by a reduction over n (ops.rs:821-827 + sum_to_shape).
             WbGemmOperand Ad{dconv, L.cout, hw, hw, L.cout * hw, false};
@@ -472,13 +522,14 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 if (s == WB_OK) s = column_sum(t, static_cast<float*>(tmp), B, L.cout * ck, t->grad + L.off_w);
                 wb_arena_free(b, tmp, klass);
             }
+            delete wt;
             WB_TRY(s);
             if (need_dx) {
                 // dcols[n] = W^T dY[n], then col2im (Im2ColBw, ops.rs:865-868)
                 WbGemmOperand Aw{t->theta + L.off_w, ck, L.cout, ck, 0, true};
                 WbGemmOperand Bd{dconv, hw, L.cout, hw, L.cout * hw, true};
                 tc::Epilogue epc{t->dcols, hw, ck * hw, nullptr, nullptr, 0, 0};
-                WB_TRY(gemm(t, Aw, Bd, B, static_cast<int>(ck), static_cast<int>(hw), L.cout, epc));
+                { OpTimer tm(t, i, "conv_dgrad_gemm"); WB_TRY(gemm(t, Aw, Bd, B, static_cast<int>(ck), static_cast<int>(hw), L.cout, epc)); }
                 float* dx = t->gbuf[pp];
                 pp ^= 1;
                 WbView cv{};
@@ -486,7 +537,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 cv.shape[0] = B; cv.shape[1] = ck; cv.shape[2] = hw;
                 cv.stride[0] = ck * hw; cv.stride[1] = hw; cv.stride[2] = 1;
                 WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
-                WB_TRY(wb_col2im_into(b, &cv, &cp, L.cin, L.h, L.w, dx));
+                { OpTimer tm(t, i, "col2im"); WB_TRY(wb_col2im_into(b, &cv, &cp, L.cin, L.h, L.w, dx)); }
                 g = dx;
             }
         }
@@ -499,6 +550,7 @@ extern "C" int wb_trainer_adam_step(WbTrainer* t, double grad_scale) {
     WB_REQUIRE(t, WB_ERR_INVALID, "wb_trainer_adam_step: null trainer");
     t->t += 1;
     const WbAdamConfig& a = t->adam;
+    OpTimer tm(t, static_cast<int>(t->layers.size()), "adam");
     return wb_adam_step(t->be, t->theta, t->grad, t->m, t->v, t->n_params, t->t, a.lr, a.beta1, a.beta2, a.eps, a.weight_decay, a.decoupled,
                         grad_scale);
 }
@@ -525,4 +577,32 @@ extern "C" int wb_trainer_read_loss(WbTrainer* t, float* host_loss) {
     WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));
     *host_loss = *t->loss_pinned;
     return WB_OK;
+}
+
+extern "C" int wb_trainer_set_timing(WbTrainer* t, int on) {
+    t->timing = on != 0;
+    return WB_OK;
+}
+
+// Waits for the stream, then returns one line per op label: "label calls total_ms" (device time
+// between the event pairs recorded since the last report).  The string stays valid until the next call.
+extern "C" const char* wb_trainer_timing_report(WbTrainer* t) {
+    cudaStreamSynchronize(t->be->stream);
+    std::vector<double> ms(t->labels.size(), 0.0);
+    std::vector<int64_t> calls(t->labels.size(), 0);
+    for (auto& r : t->recs) {
+        float e = 0.f;
+        if (cudaEventElapsedTime(&e, r.e0, r.e1) == cudaSuccess) { ms[r.label] += e; calls[r.label]++; }
+        t->event_pool.push_back(r.e0);
+        t->event_pool.push_back(r.e1);
+    }
+    t->recs.clear();
+    t->timing_text.clear();
+    char line[160];
+    for (size_t i = 0; i < t->labels.size(); ++i) {
+        if (!calls[i]) continue;
+        snprintf(line, sizeof line, "%s %lld %.6f\n", t->labels[i].c_str(), (long long)calls[i], ms[i]);
+        t->timing_text += line;
+    }
+    return t->timing_text.c_str();
 }

@@ -59,6 +59,8 @@ def _declare(lib):
         "wb_trainer_adam_step": ([P, f64], i32),
         "wb_trainer_step_host": ([P, P, P, U64P, i32, ctypes.POINTER(ctypes.c_float)], i32),
         "wb_trainer_read_loss": ([P, ctypes.POINTER(ctypes.c_float)], i32),
+        "wb_trainer_set_timing": ([P, i32], i32),
+        "wb_trainer_timing_report": ([P], ctypes.c_char_p),
         "wb_dropout_fwd": ([P, P, P, i64, f64, ctypes.c_uint64], i32),
         "wb_dropout_relu_bwd": ([P, P, P, P, i64, f64, ctypes.c_uint64], i32),
         "wb_dropout_mask": ([P, P, i64, f64, ctypes.c_uint64], i32),
@@ -195,6 +197,17 @@ class FusedTrainer:
                                                     ctypes.byref(out)))
         return out.value
 
+    def set_timing(self, on: bool):
+        self.be.check(self.lib.wb_trainer_set_timing(self.handle, int(on)))
+
+    def timing_report(self) -> dict:
+        """{label: (calls, total_ms)} of the ops timed since the last report; waits for the stream."""
+        out = {}
+        for line in self.lib.wb_trainer_timing_report(self.handle).decode().splitlines():
+            label, calls, ms = line.split()
+            out[label] = (int(calls), float(ms))
+        return out
+
     def set_bucket_callback(self, fn: Optional[Callable[[int, int], None]]):
         """fn(device_pointer, n_floats) fires during backward whenever one layer's gradients are final."""
         if fn is None:
@@ -202,3 +215,99 @@ class FusedTrainer:
         else:
             self._cb = BUCKET_CB(lambda user, ptr, n: fn(ptr, n))
         self.be.check(self.lib.wb_trainer_set_bucket_callback(self.handle, self._cb, None))
+
+
+class GradBucketer:
+    """Turns the trainer's per-layer "gradients final" notifications into a few large all-reduces.
+
+    Ranges arrive front to back over one flat arena (last layer first).  Adjacent ranges are merged
+    until `min_elems` have accumulated, then `reduce_fn(start, length)` is called for the merged
+    range; `flush()` sends whatever is left.  Pure host logic: the collective itself is injected.
+    """
+
+    def __init__(self, reduce_fn: Callable[[int, int], None], min_elems: int = 1 << 20):
+        self.reduce_fn = reduce_fn
+        self.min_elems = min_elems
+        self.start: Optional[int] = None
+        self.length = 0
+        self.issued: List[Tuple[int, int]] = []
+
+    def add(self, start: int, length: int):
+        if length <= 0:
+            return
+        if self.start is None:
+            self.start, self.length = start, length
+        elif start == self.start + self.length:
+            self.length += length
+        else:  # not adjacent: send what we have and start over
+            self.flush()
+            self.start, self.length = start, length
+        if self.length >= self.min_elems:
+            self.flush()
+
+    def flush(self):
+        if self.start is not None and self.length > 0:
+            self.reduce_fn(self.start, self.length)
+            self.issued.append((self.start, self.length))
+        self.start, self.length = None, 0
+
+
+class _DevicePtr:
+    """Exposes a raw device range to torch through __cuda_array_interface__ (no copy)."""
+
+    def __init__(self, ptr: int, n: int, typestr: str = "<f4"):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3, "strides": None}
+
+
+class DataParallelTrainer:
+    """Data-parallel wrapper: one process per GPU, every rank a full replica, the batch sharded.
+
+    The reference has no multi-GPU path; this adds the one exchange a data-parallel step needs.
+    Gradients are summed with NCCL (`torch.distributed`) on a side stream as soon as a bucket of the
+    arena is final, while backward continues on the compute stream; Adam then applies 1/world.
+    BatchNorm statistics stay per rank, as they would in the reference (it has no SyncBN).
+    """
+
+    def __init__(self, trainer: FusedTrainer, compute_stream, world_size: int, bucket_elems: int = 1 << 20):
+        import torch
+        import torch.distributed as dist
+
+        self.torch, self.dist = torch, dist
+        self.tr = trainer
+        self.world = world_size
+        self.stream = compute_stream
+        self.comm_stream = torch.cuda.Stream() if world_size > 1 else None
+        self.works = []
+        self.grad_view = torch.as_tensor(_DevicePtr(trainer.grads_ptr(), trainer.arena_len), device=f"cuda:{trainer.be.ordinal}")
+        self.bucketer = GradBucketer(self._all_reduce_range, bucket_elems)
+        base = trainer.grads_ptr()
+        if world_size > 1:
+            trainer.set_bucket_callback(lambda ptr, n: self.bucketer.add((ptr - base) // 4, n))
+
+    def _all_reduce_range(self, start: int, length: int):
+        torch = self.torch
+        ev = torch.cuda.Event()
+        ev.record(self.stream)                   # everything queued so far, i.e. this bucket's gradients
+        self.comm_stream.wait_event(ev)
+        with torch.cuda.stream(self.comm_stream):
+            self.works.append(self.dist.all_reduce(self.grad_view[start:start + length], op=self.dist.ReduceOp.SUM, async_op=True))
+
+    def forward_backward_step(self, seeds=None):
+        """forward, backward with overlapped all-reduce, Adam.  Inputs must already be staged."""
+        self.tr.forward_backward(seeds)
+        if self.world > 1:
+            self.bucketer.flush()
+            with self.torch.cuda.stream(self.comm_stream):
+                for w in self.works:
+                    w.wait()
+            self.works.clear()
+            self.stream.wait_stream(self.comm_stream)
+        self.tr.adam_step(1.0 / self.world)
+
+    def step_host(self, x_pinned, y_pinned, seeds=None) -> float:
+        """One step from pinned host tensors: upload, forward/backward (+ all-reduce), Adam, loss read-back."""
+        tr, be = self.tr, self.tr.be
+        be.check(be.lib.wb_upload_async(be.handle, x_pinned.data_ptr(), ctypes.c_void_p(tr.input_ptr()), x_pinned.numel() * 4))
+        be.check(be.lib.wb_upload_async(be.handle, y_pinned.data_ptr(), ctypes.c_void_p(tr.labels_ptr()), y_pinned.numel() * 8))
+        self.forward_backward_step(seeds)
+        return tr.loss()
