@@ -67,6 +67,67 @@ __global__ void __launch_bounds__(THREADS) col2im_kernel(T* __restrict__ out, co
     out[i] = acc;
 }
 
+// ---- 3x3, stride 1, padding 1, dilation 1 on contiguous f32 images (every convolution of the named models) ----
+// Same gather, four consecutive output columns per thread and 32-bit index arithmetic: one 128-bit
+// store per thread, the nine shifted reads of each pixel come from L1/L2.
+__global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ out, const float* __restrict__ x, int h, int w,
+                                                           uint32_t groups) {
+    uint32_t i = blockIdx.x * THREADS + threadIdx.x;
+    if (i >= groups) return;
+    const uint32_t wq = static_cast<uint32_t>(w) >> 2;
+    uint32_t xq = i % wq, t = i / wq;
+    uint32_t y = t % static_cast<uint32_t>(h);
+    t /= static_cast<uint32_t>(h);
+    uint32_t k9 = t % 9u, nc = t / 9u;
+    int ki = static_cast<int>(k9 / 3u), kj = static_cast<int>(k9 % 3u);
+    int iy = static_cast<int>(y) + ki - 1;
+    int ix0 = static_cast<int>(xq * 4u) + kj - 1;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (iy >= 0 && iy < h) {
+        const float* row = x + (static_cast<int64_t>(nc) * h + iy) * w;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            int ix = ix0 + k;
+            if (ix >= 0 && ix < w) v[k] = row[ix];
+        }
+    }
+    *reinterpret_cast<float4*>(out + static_cast<int64_t>(i) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+}
+
+// Adjoint: each thread owns four consecutive pixels of one (n, c) plane and adds its (up to) nine
+// column entries in (ki, kj) order, the order the CPU backend's scatter reaches them.
+__global__ void __launch_bounds__(THREADS) col2im3_kernel(float* __restrict__ out, const float* __restrict__ cols, int h, int w,
+                                                           uint32_t groups) {
+    uint32_t i = blockIdx.x * THREADS + threadIdx.x;
+    if (i >= groups) return;
+    const uint32_t wq = static_cast<uint32_t>(w) >> 2;
+    uint32_t xq = i % wq, t = i / wq;
+    uint32_t y = t % static_cast<uint32_t>(h), nc = t / static_cast<uint32_t>(h);
+    const int64_t l = static_cast<int64_t>(h) * w;
+    const float* base = cols + static_cast<int64_t>(nc) * 9 * l;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ki = 0; ki < 3; ++ki) {
+        int oy = static_cast<int>(y) + 1 - ki;
+        if (oy < 0 || oy >= h) continue;
+#pragma unroll
+        for (int kj = 0; kj < 3; ++kj) {
+            const float* row = base + (ki * 3 + kj) * l + static_cast<int64_t>(oy) * w;
+            int ox0 = static_cast<int>(xq * 4u) + 1 - kj;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                int ox = ox0 + k;
+                if (ox >= 0 && ox < w) acc[k] = acc[k] + row[ox];
+            }
+        }
+    }
+    *reinterpret_cast<float4*>(out + static_cast<int64_t>(i) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
+inline bool same_conv3(const WbConvParams& p) {
+    return p.kh == 3 && p.kw == 3 && p.sh == 1 && p.sw == 1 && p.ph == 1 && p.pw == 1 && p.dh == 1 && p.dw == 1;
+}
+
 inline int64_t out_size1(int64_t x, int64_t k, int64_t s, int64_t p, int64_t d) {  // crates/weta-core/src/ops.rs:136-149
     int64_t span = d * (k - 1) + 1;
     if (x + 2 * p < span) return 0;
@@ -95,6 +156,15 @@ extern "C" int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams*
     int64_t total = p.n * p.c * p.kh * p.kw * p.oh * p.ow;
     if (total == 0) return WB_OK;
     WbProfileScope ps(b, "im2col");
+    if (same_conv3(*cp) && x->dtype == WB_F32 && wb_is_contiguous(*x) && p.w % 4 == 0 && total / 4 < (int64_t(1) << 31) &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        int64_t groups = total / 4;
+        im2col3_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+            static_cast<float*>(out), static_cast<const float*>(x->data) + x->offset, static_cast<int>(p.h), static_cast<int>(p.w),
+            static_cast<uint32_t>(groups));
+        WB_LAUNCH_OK(b);
+        return WB_OK;
+    }
     unsigned grid = static_cast<unsigned>((total + THREADS - 1) / THREADS);
     switch (x->dtype) {
         case WB_F32: im2col_kernel<float><<<grid, THREADS, 0, b->stream>>>(static_cast<float*>(out), static_cast<const float*>(x->data), p, total); break;
@@ -128,6 +198,15 @@ extern "C" int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvPara
     int64_t total = p.n * c * h * w;
     if (total == 0) return WB_OK;
     WbProfileScope ps(b, "col2im");
+    if (same_conv3(*cp) && cols->dtype == WB_F32 && wb_is_contiguous(*cols) && w % 4 == 0 && total / 4 < (int64_t(1) << 31) &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        int64_t groups = total / 4;
+        col2im3_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+            static_cast<float*>(out), static_cast<const float*>(cols->data) + cols->offset, static_cast<int>(h), static_cast<int>(w),
+            static_cast<uint32_t>(groups));
+        WB_LAUNCH_OK(b);
+        return WB_OK;
+    }
     unsigned grid = static_cast<unsigned>((total + THREADS - 1) / THREADS);
     if (cols->dtype == WB_F32)
         col2im_kernel<float><<<grid, THREADS, 0, b->stream>>>(static_cast<float*>(out), static_cast<const float*>(cols->data), p,

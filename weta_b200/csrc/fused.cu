@@ -113,22 +113,36 @@ __global__ void __launch_bounds__(THREADS) bn_stats_kernel(const float* __restri
     const int c = blockIdx.x;
     const float pivot = x[static_cast<int64_t>(c) * hw];
     double s1 = 0.0, s2 = 0.0;
-    for (int64_t n = blockIdx.y; n < n_img; n += gridDim.y) {
-        const float* src = x + (n * c_total + c) * hw;
+    // This block's images [n0, n1); its threads walk the (image, position) pairs of that slab
+    // flattened, so every thread is busy whatever the plane size.
+    const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+    const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+    const int64_t plane_stride = static_cast<int64_t>(c_total) * hw;
+    const float* slab = x + (n0 * c_total + c) * hw;
+    if ((hw & 3) == 0) {
+        const uint32_t q = static_cast<uint32_t>(hw >> 2), items = static_cast<uint32_t>(n1 - n0) * q;  // host checks the range
         float a1 = 0.f, a2 = 0.f;
-        if ((hw & 3) == 0) {
-            for (int64_t i = threadIdx.x * 4; i < hw; i += THREADS * 4) {
-                float4 v = *reinterpret_cast<const float4*>(src + i);
-                float d0 = v.x - pivot, d1 = v.y - pivot, d2 = v.z - pivot, d3 = v.w - pivot;
-                a1 += (d0 + d1) + (d2 + d3);
-                a2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-            }
-        } else {
-            for (int64_t i = threadIdx.x; i < hw; i += THREADS) {
-                float d = src[i] - pivot;
-                a1 += d;
-                a2 += d * d;
-            }
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / q, p = j - n * q;
+            float4 v = *reinterpret_cast<const float4*>(slab + n * plane_stride + p * 4);
+            float d0 = v.x - pivot, d1 = v.y - pivot, d2 = v.z - pivot, d3 = v.w - pivot;
+            a1 += (d0 + d1) + (d2 + d3);
+            a2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+            if (++flushed == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }  // keep f32 partial sums short
+        }
+        s1 += a1;
+        s2 += a2;
+    } else {
+        const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / uhw, p = j - n * uhw;
+            float d = slab[n * plane_stride + p] - pivot;
+            a1 += d;
+            a2 += d * d;
+            if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
         }
         s1 += a1;
         s2 += a2;
@@ -208,14 +222,21 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __re
     const int c = blockIdx.x;
     const float m = mean[c], r = rstd[c];
     double s1 = 0.0, s2 = 0.0;
-    for (int64_t n = blockIdx.y; n < n_img; n += gridDim.y) {
-        const float* xs = x + (n * c_total + c) * hw;
-        const float* gs = dy + (n * c_total + c) * hw;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
+        const int64_t stride = static_cast<int64_t>(c_total) * hw;
+        const float* xslab = x + (n0 * c_total + c) * hw;
+        const float* gslab = dy + (n0 * c_total + c) * hw;
         float a1 = 0.f, a2 = 0.f;
-        for (int64_t i = threadIdx.x; i < hw; i += THREADS) {
-            float g = gs[i];
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / uhw, i = j - n * uhw;
+            float g = gslab[n * stride + i];
             a1 += g;
-            a2 += g * ((xs[i] - m) * r);
+            a2 += g * ((xslab[n * stride + i] - m) * r);
+            if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
         }
         s1 += a1;
         s2 += a2;
@@ -327,19 +348,26 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_stats_kernel(const f
     const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
     const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
     double s1 = 0.0, s2 = 0.0;
-    for (int64_t n = blockIdx.y; n < n_img; n += gridDim.y) {
-        const float* xs = x + (n * c_total + c) * h * w;
-        const float* gs = dyp + (n * c_total + c) * pooled;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
+        const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+        const float* xslab = x + (n0 * c_total + c) * h * w;
+        const float* gslab = dyp + (n0 * c_total + c) * pooled;
         float a1 = 0.f, a2 = 0.f;
-        for (int i = threadIdx.x; i < pooled; i += THREADS) {
-            int oy = i / ow, ox = i - oy * ow;
-            const float* src = xs + 2 * oy * w + 2 * ox;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / up, i = j - n * up;
+            const uint32_t oy = i / static_cast<uint32_t>(ow), ox = i - oy * ow;
+            const float* src = xslab + n * xstride + 2 * oy * w + 2 * ox;
             float2 r0 = *reinterpret_cast<const float2*>(src);
             float2 r1 = *reinterpret_cast<const float2*>(src + w);
             float v[4] = {r0.x, r0.y, r1.x, r1.y}, go[4], xh[4];
-            pool_window_grads(v, m, r, g, b, gs[i], go, xh);
+            pool_window_grads(v, m, r, g, b, gslab[n * gstride + i], go, xh);
 #pragma unroll
             for (int k = 0; k < 4; ++k) { a1 += go[k]; a2 += go[k] * xh[k]; }
+            if (++flushed == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
         }
         s1 += a1;
         s2 += a2;
@@ -371,22 +399,29 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
     const float k1 = dbeta[c] * inv_count, k2 = dgamma[c] * inv_count, gr = g * r;
     const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
     double sb = 0.0;
-    for (int64_t n = blockIdx.y; n < n_img; n += gridDim.y) {
-        const float* xs = x + (n * c_total + c) * h * w;
-        const float* gs = dyp + (n * c_total + c) * pooled;
-        float* ds = dx + (n * c_total + c) * h * w;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
+        const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+        const float* xslab = x + (n0 * c_total + c) * h * w;
+        const float* gslab = dyp + (n0 * c_total + c) * pooled;
+        float* dslab = dx + (n0 * c_total + c) * h * w;
         float a = 0.f;
-        for (int i = threadIdx.x; i < pooled; i += THREADS) {
-            int oy = i / ow, ox = i - oy * ow;
-            const int64_t o = static_cast<int64_t>(2 * oy) * w + 2 * ox;
-            float2 r0 = *reinterpret_cast<const float2*>(xs + o);
-            float2 r1 = *reinterpret_cast<const float2*>(xs + o + w);
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / up, i = j - n * up;
+            const uint32_t oy = i / static_cast<uint32_t>(ow), ox = i - oy * ow;
+            const int64_t o = n * xstride + static_cast<int64_t>(2 * oy) * w + 2 * ox;
+            float2 r0 = *reinterpret_cast<const float2*>(xslab + o);
+            float2 r1 = *reinterpret_cast<const float2*>(xslab + o + w);
             float v[4] = {r0.x, r0.y, r1.x, r1.y}, go[4], xh[4], d[4];
-            pool_window_grads(v, m, r, g, b, gs[i], go, xh);
+            pool_window_grads(v, m, r, g, b, gslab[n * gstride + i], go, xh);
 #pragma unroll
             for (int k = 0; k < 4; ++k) { d[k] = gr * (go[k] - k1 - xh[k] * k2); a += d[k]; }
-            *reinterpret_cast<float2*>(ds + o) = make_float2(d[0], d[1]);
-            *reinterpret_cast<float2*>(ds + o + w) = make_float2(d[2], d[3]);
+            *reinterpret_cast<float2*>(dslab + o) = make_float2(d[0], d[1]);
+            *reinterpret_cast<float2*>(dslab + o + w) = make_float2(d[2], d[3]);
+            if (++flushed == 64) { sb += a; a = 0.f; flushed = 0; }
         }
         sb += a;
     }
@@ -449,9 +484,12 @@ double powi(double a, int n) {  // f64::powi (compiler-rt __powidf2)
     return r;
 }
 
-int stat_splits(WbBackend* be, int c, int64_t n_img) {
-    int64_t want = (4LL * be->sm_count + c - 1) / c;
-    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(want, n_img)));
+// Number of image slabs per channel for the per-channel reductions: about 8 blocks per SM in total,
+// and few enough images per slab that the kernels' 32-bit item counters cannot overflow.
+int stat_splits(WbBackend* be, int c, int64_t n_img, int64_t items_per_image) {
+    int64_t want = (8LL * be->sm_count + c - 1) / c;
+    int64_t need = (n_img * items_per_image + (int64_t(1) << 30) - 1) / (int64_t(1) << 30);
+    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::max(want, need), n_img)));
 }
 
 }  // namespace
@@ -520,7 +558,7 @@ extern "C" int wb_bn2d_stats(WbBackend* b, const float* x, int64_t n, int64_t c,
     WB_REQUIRE(b && x && mean && rstd, WB_ERR_INVALID, "wb_bn2d_stats: null pointer");
     WB_REQUIRE(n > 0 && c > 0 && hw > 0, WB_ERR_INVALID, "wb_bn2d_stats: empty input");
     WbProfileScope ps(b, "bn2d_stats");
-    int splits = stat_splits(b, static_cast<int>(c), n);
+    int splits = stat_splits(b, static_cast<int>(c), n, hw);
     void* s = nullptr;
     WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 2 * sizeof(double), &s));
     bn_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, n, static_cast<int>(c), hw, static_cast<double*>(s));
@@ -560,7 +598,7 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
                            const float* save_mean, const float* save_rstd, float* dx, float* dgamma, float* dbeta) {
     WB_REQUIRE(b && x && dy && dx && dgamma && dbeta && save_mean && save_rstd, WB_ERR_INVALID, "wb_bn2d_bwd: null pointer");
     WbProfileScope ps(b, "bn2d_bwd");
-    int splits = stat_splits(b, static_cast<int>(c), n);
+    int splits = stat_splits(b, static_cast<int>(c), n, hw);
     void* s = nullptr;
     WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 2 * sizeof(double), &s));
     bn_bwd_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, dy, save_mean, save_rstd, n, static_cast<int>(c), hw,
@@ -599,7 +637,7 @@ extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy
     WB_REQUIRE(b && x && dy_pooled && dx && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
     WbProfileScope ps(b, "bn_relu_pool_bwd");
-    int splits = stat_splits(b, static_cast<int>(c), n);
+    int splits = stat_splits(b, static_cast<int>(c), n, h * w);
     void* s = nullptr;
     WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 3 * sizeof(double), &s));
     double* part = static_cast<double*>(s);

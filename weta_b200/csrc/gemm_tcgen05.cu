@@ -238,7 +238,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         WB_REQUIRE(grid_batch * splits <= 65535, WB_ERR_UNSUPPORTED, "gemm: batch x split-K exceeds the grid limit");
         dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m), static_cast<unsigned>(grid_batch * splits));
         const bool amn = A.mn_major, bmn = B.mn_major;
-        constexpr int STG = 6;
+        constexpr int STG = 3;  // 3 x 32 KB: two CTAs share an SM, so one tile's epilogue overlaps the other's main loop
         if (!amn && !bmn) status = launch_tc<BN, STG, false, false>(be, st, args, grid);
         else if (!amn && bmn) status = launch_tc<BN, STG, false, true>(be, st, args, grid);
         else if (amn && !bmn) status = launch_tc<BN, STG, true, false>(be, st, args, grid);

@@ -93,7 +93,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 // Shared-memory matrix descriptor, SWIZZLE_128B, descriptor version 1 (sm_100).
 //   bits [0,14)  start address >> 4      bits [16,30) leading-dim byte offset >> 4
 //   bits [32,46) stride-dim byte offset >> 4   bits [46,48) version = 1   bits [61,64) layout = 2 (128B swizzle)
-//   layout 2 = 128B swizzle of 16-byte chunks (K-major operands); layout 1 = 128B swizzle of 32-byte chunks,
+// Layout field: 2 = 128B swizzle of 16-byte chunks (K-major operands); layout 1 = 128B swizzle of 32-byte chunks,
 //   the only swizzled layout the tensor core accepts for MN-major 32-bit operands.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
     uint64_t d = 0;
@@ -156,7 +156,7 @@ struct SharedStorage {
 
 // A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
+__global__ void __launch_bounds__(THREADS, (STAGES <= 3 && BN <= 128) ? 2 : 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using SS = SharedStorage<BN, STAGES>;
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -260,14 +260,19 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     if (!ready && lane == 0) atomicExch(args.error_flag, 1);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ready) {
+        // Each thread holds one accumulator row (32 columns per tcgen05.ld).  The rows are staged through
+        // shared memory (the pipeline buffers are idle by now) so that every store instruction of a warp
+        // writes four 128-byte row segments instead of 32 scattered 16-byte pieces.
+        constexpr int PITCH = 36;  // floats; 144 B keeps float4 alignment and spreads banks
+        float* stage = reinterpret_cast<float*>(&ss.a[0][0]) + warp * (32 * PITCH);
         const int row = m0 + warp * 32 + lane;
-        float* dst = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d +
-                     static_cast<int64_t>(row) * args.ep.ldd;
+        float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d;
         const float bm = (args.ep.bias_m && row < args.m) ? args.ep.bias_m[row] : 0.f;
         const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
                             (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
+            if (n0 + c >= args.n) break;
             float v[32];
             if (total_iters == 0) {
 #pragma unroll
@@ -275,31 +280,40 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             } else {
                 tmem_ld32(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
             }
-            if (row < args.m) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    const int col = n0 + c + i;
-                    if (col >= args.n) break;
-                    float r[4];
+            for (int i = 0; i < 32; i += 4) {
+                float r[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float x = v[i + j] + bm;
-                        if (args.ep.bias_n && col + j < args.n) x += args.ep.bias_n[col + j];
-                        if (args.ep.relu) x = fmaxf(x, 0.f);
-                        r[j] = x;
-                    }
-                    if (vec_ok && col + 4 <= args.n) {
-                        float4* p = reinterpret_cast<float4*>(dst + col);
+                for (int j = 0; j < 4; ++j) {
+                    const int col = n0 + c + i + j;
+                    float x = v[i + j] + bm;
+                    if (args.ep.bias_n && col < args.n) x += args.ep.bias_n[col];
+                    if (args.ep.relu) x = fmaxf(x, 0.f);
+                    r[j] = x;
+                }
+                *reinterpret_cast<float4*>(stage + lane * PITCH + i) = make_float4(r[0], r[1], r[2], r[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3), cc = (lane & 7) * 4;
+                const int grow = m0 + warp * 32 + r, gcol = n0 + c + cc;
+                if (grow < args.m && gcol < args.n) {
+                    float4 val = *reinterpret_cast<const float4*>(stage + r * PITCH + cc);
+                    float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
+                    if (vec_ok && gcol + 4 <= args.n) {
                         if (args.ep.accumulate) {
-                            float4 o = *p;
-                            r[0] += o.x; r[1] += o.y; r[2] += o.z; r[3] += o.w;
+                            float4 o = *reinterpret_cast<const float4*>(p);
+                            val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
                         }
-                        *p = make_float4(r[0], r[1], r[2], r[3]);
+                        *reinterpret_cast<float4*>(p) = val;
                     } else {
-                        for (int j = 0; j < 4 && col + j < args.n; ++j) dst[col + j] = args.ep.accumulate ? dst[col + j] + r[j] : r[j];
+                        const float e[4] = {val.x, val.y, val.z, val.w};
+                        for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
                     }
                 }
             }
+            __syncwarp();
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
