@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) bn_stats_kernel(const float* __restri
     // This block's images [n0, n1); its threads walk the (image, position) pairs of that slab
     // flattened, so every thread is busy whatever the plane size.
     const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
-    const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+    const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
     const int64_t plane_stride = static_cast<int64_t>(c_total) * hw;
     const float* slab = x + (n0 * c_total + c) * hw;
     if ((hw & 3) == 0) {
@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __re
     double s1 = 0.0, s2 = 0.0;
     {
         const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
-        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
         const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
         const int64_t stride = static_cast<int64_t>(c_total) * hw;
         const float* xslab = x + (n0 * c_total + c) * hw;
@@ -350,7 +350,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_stats_kernel(const f
     double s1 = 0.0, s2 = 0.0;
     {
         const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
-        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
         const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
         const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
         const float* xslab = x + (n0 * c_total + c) * h * w;
@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
     double sb = 0.0;
     {
         const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
-        const int64_t n0 = blockIdx.y * per, n1 = min(n_img, n0 + per);
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
         const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
         const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
         const float* xslab = x + (n0 * c_total + c) * h * w;
@@ -489,7 +489,9 @@ double powi(double a, int n) {  // f64::powi (compiler-rt __powidf2)
 int stat_splits(WbBackend* be, int c, int64_t n_img, int64_t items_per_image) {
     int64_t want = (8LL * be->sm_count + c - 1) / c;
     int64_t need = (n_img * items_per_image + (int64_t(1) << 30) - 1) / (int64_t(1) << 30);
-    return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::max(want, need), n_img)));
+    int64_t splits = std::max<int64_t>(1, std::min<int64_t>(std::max(want, need), n_img));
+    int64_t per = (n_img + splits - 1) / splits;
+    return static_cast<int>((n_img + per - 1) / per);  // no slab is empty
 }
 
 }  // namespace
