@@ -435,6 +435,82 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
     if (threadIdx.x == 0 && bias_part) bias_part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = rs[0];
 }
 
+// Width-multiple-of-4 variants: one thread handles two neighbouring pooled elements, i.e. a 2x4 patch
+// of x, with 128-bit loads and stores; same arithmetic as the kernels above.
+template <bool WRITE_DX>
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, const float* __restrict__ x,
+                                                                         const float* __restrict__ dyp, const float* __restrict__ mean,
+                                                                         const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                                         const float* __restrict__ beta, const float* __restrict__ dgamma,
+                                                                         const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
+                                                                         int w, float inv_count, double* __restrict__ part) {
+    const int c = blockIdx.x;
+    const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
+    float k1 = 0.f, k2 = 0.f, gr = 0.f;
+    if (WRITE_DX) { k1 = dbeta[c] * inv_count; k2 = dgamma[c] * inv_count; gr = g * r; }
+    const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
+    const uint32_t owp = static_cast<uint32_t>(ow >> 1), pairs = static_cast<uint32_t>(oh) * owp;
+    const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+    const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);
+    const uint32_t items = static_cast<uint32_t>(n1 - n0) * pairs;
+    const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+    const float* xslab = x + (n0 * c_total + c) * h * w;
+    const float* gslab = dyp + (n0 * c_total + c) * pooled;
+    float* dslab = WRITE_DX ? dx + (n0 * c_total + c) * h * w : nullptr;
+    double s1 = 0.0, s2 = 0.0;
+    float a1 = 0.f, a2 = 0.f;
+    int flushed = 0;
+#pragma unroll 2
+    for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+        const uint32_t n = j / pairs, i = j - n * pairs;
+        const uint32_t oy = i / owp, oxp = i - oy * owp;
+        const int64_t o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
+        const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
+        const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
+        const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
+        const float va[4] = {r0.x, r0.y, r1.x, r1.y}, vb[4] = {r0.z, r0.w, r1.z, r1.w};
+        float ga[4], gb[4], xa[4], xb[4];
+        pool_window_grads(va, m, r, g, b, gy.x, ga, xa);
+        pool_window_grads(vb, m, r, g, b, gy.y, gb, xb);
+        if (WRITE_DX) {
+            float da[4], db[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                da[k] = gr * (ga[k] - k1 - xa[k] * k2);
+                db[k] = gr * (gb[k] - k1 - xb[k] * k2);
+                a1 += da[k] + db[k];
+            }
+            *reinterpret_cast<float4*>(dslab + o) = make_float4(da[0], da[1], db[0], db[1]);
+            *reinterpret_cast<float4*>(dslab + o + w) = make_float4(da[2], da[3], db[2], db[3]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a1 += ga[k] + gb[k];
+                a2 += ga[k] * xa[k] + gb[k] * xb[k];
+            }
+        }
+        if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+    }
+    s1 += a1;
+    s2 += a2;
+    __shared__ double r1s[THREADS], r2s[THREADS];
+    r1s[threadIdx.x] = s1;
+    r2s[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1s[threadIdx.x] += r1s[threadIdx.x + s]; r2s[threadIdx.x] += r2s[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && part) {
+        if (WRITE_DX) {
+            part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = r1s[0];  // sum of dx: the conv bias gradient
+        } else {
+            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1s[0];
+            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2s[0];
+        }
+    }
+}
+
 __global__ void sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
     int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= c_total) return;
@@ -645,15 +721,27 @@ extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy
     double* part = static_cast<double*>(s);
     double* bias_part = part + static_cast<size_t>(c) * splits * 2;
     dim3 grid(static_cast<unsigned>(c), splits);
-    bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
-                                                                  static_cast<int>(h), static_cast<int>(w), part);
+    const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(dy_pooled) & 7) == 0;
+    const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
+    if (pairs)
+        bn_relu_pool_bwd_pair_kernel<false><<<grid, THREADS, 0, b->stream>>>(nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr,
+                                                                            nullptr, n, static_cast<int>(c), static_cast<int>(h),
+                                                                            static_cast<int>(w), inv_count, part);
+    else
+        bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
+                                                                      static_cast<int>(h), static_cast<int>(w), part);
     WB_LAUNCH_OK(b);
     bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
-    bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
-                                                               static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
-                                                               static_cast<float>(1.0 / static_cast<double>(n * h * w)),
-                                                               dbias_conv ? bias_part : nullptr);
+    if (pairs)
+        bn_relu_pool_bwd_pair_kernel<true><<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
+                                                                           static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
+                                                                           inv_count, dbias_conv ? bias_part : nullptr);
+    else
+        bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
+                                                                   static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
+                                                                   dbias_conv ? bias_part : nullptr);
     WB_LAUNCH_OK(b);
     if (dbias_conv) {
         sum_parts_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(bias_part, splits, static_cast<int>(c), dbias_conv);

@@ -42,6 +42,7 @@ struct Layer {
     float* save_rstd = nullptr;
     float* cols = nullptr;      // [B, cin*9, h*w]
     float* conv_out = nullptr;  // [B, cout, h, w]
+    float* w_pad = nullptr;     // [cout, round_up(cin*9, 4)]: weight rows re-pitched to 16 bytes when cin*9 is not a multiple of 4
     float* out_act = nullptr;   // layer output
     int64_t out_elems = 0;      // per-sample size of the layer output
     bool relu_bwd_done = false;
@@ -284,6 +285,7 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
             int64_t hw = static_cast<int64_t>(L.h) * L.w;
             A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
             A(dev_alloc_t(t, batch * L.cout * hw, &L.conv_out));
+            if ((L.cin * 9) % 4 != 0) A(dev_alloc_t(t, static_cast<int64_t>(L.cout) * ((L.cin * 9 + 3) / 4 * 4), &L.w_pad));
             A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
             A(dev_alloc_t(t, L.cout, &L.running_mean));
             A(dev_alloc_t(t, L.cout, &L.running_var));
@@ -429,6 +431,14 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
             { OpTimer tm(t, i, "im2col"); WB_TRY(wb_im2col_into(b, &xv, &cp, L.cols)); }
             WbGemmOperand Aw{t->theta + L.off_w, L.cout, ck, ck, 0, false};
+            if (L.w_pad) {
+                // TMA needs a 16-byte row pitch: copy the [O, C*9] weight into rows of round_up(C*9, 4) floats.
+                const int64_t ckp = (ck + 3) / 4 * 4;
+                WB_CHECK_CUDA(cudaMemcpy2DAsync(L.w_pad, ckp * sizeof(float), t->theta + L.off_w, ck * sizeof(float), ck * sizeof(float), L.cout,
+                                                cudaMemcpyDeviceToDevice, b->stream));
+                Aw.ptr = L.w_pad;
+                Aw.ld = ckp;
+            }
             WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
             tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
             { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep)); }
