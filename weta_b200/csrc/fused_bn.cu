@@ -1,0 +1,580 @@
+// BatchNorm2d and the fused conv-block tail (BatchNorm -> ReLU -> MaxPool2d(2)), forward and backward.
+//   batch norm 2d    crates/weta-nn/src/functional.rs:144-180  (~9 reductions + ~20 element-wise passes per call)
+//   BN + ReLU + pool crates/weta/examples/mnist_cnn.rs:18-20, 22-24; max-pool ties share the gradient
+//                    (crates/weta-autograd/src/ops.rs:305-314), ReLU passes it where its input is positive (ops.rs:85)
+// These results are tolerance-checked, not bit-checked, so this file is compiled with FMA contraction on;
+// the running-statistics update alone keeps the reference's exact rounding sequence (explicit _rn ops).
+#include <algorithm>
+#include <cmath>
+
+#include "common.h"
+
+namespace {
+
+constexpr int THREADS = 256;
+
+// ---- per-channel statistics over [N, C, HW] -----------------------------------------------------
+// grid (C, S): block (c, s) covers images n = s, s + S, ...  Values are shifted by the channel's
+// first element before squaring so the one-pass variance does not cancel.
+__global__ void __launch_bounds__(THREADS) bn_stats_kernel(const float* __restrict__ x, int64_t n_img, int c_total, int64_t hw,
+                                                            double* __restrict__ part) {
+    const int c = blockIdx.x;
+    const float pivot = x[static_cast<int64_t>(c) * hw];
+    double s1 = 0.0, s2 = 0.0;
+    // This block's images [n0, n1); its threads walk the (image, position) pairs of that slab
+    // flattened, so every thread is busy whatever the plane size.
+    const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+    const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
+    const int64_t plane_stride = static_cast<int64_t>(c_total) * hw;
+    const float* slab = x + (n0 * c_total + c) * hw;
+    if ((hw & 3) == 0) {
+        const uint32_t q = static_cast<uint32_t>(hw >> 2), items = static_cast<uint32_t>(n1 - n0) * q;  // host checks the range
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / q, p = j - n * q;
+            float4 v = *reinterpret_cast<const float4*>(slab + n * plane_stride + p * 4);
+            float d0 = v.x - pivot, d1 = v.y - pivot, d2 = v.z - pivot, d3 = v.w - pivot;
+            a1 += (d0 + d1) + (d2 + d3);
+            a2 += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+            if (++flushed == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }  // keep f32 partial sums short
+        }
+        s1 += a1;
+        s2 += a2;
+    } else {
+        const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / uhw, p = j - n * uhw;
+            float d = slab[n * plane_stride + p] - pivot;
+            a1 += d;
+            a2 += d * d;
+            if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+        }
+        s1 += a1;
+        s2 += a2;
+    }
+    __shared__ double r1[THREADS], r2[THREADS];
+    r1[threadIdx.x] = s1;
+    r2[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1[threadIdx.x] += r1[threadIdx.x + s]; r2[threadIdx.x] += r2[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1[0];
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2[0];
+    }
+}
+
+// mean, biased variance, rstd; running stats as crates/weta-nn/src/functional.rs:163-168.
+__global__ void bn_finalize_kernel(const double* __restrict__ part, int splits, const float* __restrict__ x, int c_total, int64_t hw,
+                                   int64_t count, float eps, float momentum, float one_minus_momentum, float* __restrict__ mean,
+                                   float* __restrict__ rstd,
+                                   float* __restrict__ running_mean, float* __restrict__ running_var) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= c_total) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < splits; ++s) {
+        s1 += part[(static_cast<int64_t>(c) * splits + s) * 2];
+        s2 += part[(static_cast<int64_t>(c) * splits + s) * 2 + 1];
+    }
+    double pivot = x[static_cast<int64_t>(c) * hw];
+    double dm = s1 / static_cast<double>(count);
+    double var = s2 / static_cast<double>(count) - dm * dm;
+    if (var < 0.0) var = 0.0;
+    float m = static_cast<float>(pivot + dm), v = static_cast<float>(var);
+    mean[c] = m;
+    rstd[c] = 1.f / sqrtf(v + eps);
+    if (running_mean) {
+        // running = running*(1-m) + batch*m with every product and sum rounded separately (functional.rs:165-167)
+        float unbiased = __fadd_rn(__fmul_rn(v, static_cast<float>(static_cast<double>(count) / static_cast<double>((count > 2 ? count : 2) - 1))), 0.f);
+        running_mean[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_mean[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(m, momentum), 0.f));
+        running_var[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_var[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(unbiased, momentum), 0.f));
+    }
+}
+
+// y = ((x - mean) * rstd) * gamma + beta, optionally ReLU.  One (n, c) plane per blockIdx.y.
+__global__ void __launch_bounds__(THREADS) bn_apply_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, int c_total, int64_t hw, int relu) {
+    int64_t plane = blockIdx.y;
+    int c = static_cast<int>(plane % c_total);
+    float m = mean[c], r = rstd[c], g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
+    const float* src = x + plane * hw;
+    float* dst = y + plane * hw;
+    for (int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4; i < hw; i += static_cast<int64_t>(gridDim.x) * THREADS * 4) {
+        if (i + 4 <= hw && (hw & 3) == 0) {
+            float4 v = *reinterpret_cast<const float4*>(src + i);
+            float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float t = ((o[k] - m) * r) * g + b;
+                o[k] = relu ? (t > 0.f ? t : 0.f) : t;
+            }
+            *reinterpret_cast<float4*>(dst + i) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            for (int64_t j = i; j < hw && j < i + 4; ++j) {
+                float t = ((src[j] - m) * r) * g + b;
+                dst[j] = relu ? (t > 0.f ? t : 0.f) : t;
+            }
+        }
+    }
+}
+
+// Plain BN backward statistics: sum(dy) and sum(dy * xhat) per channel.  Same grid as bn_stats.
+__global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                                const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                int64_t n_img, int c_total, int64_t hw, double* __restrict__ part) {
+    const int c = blockIdx.x;
+    const float m = mean[c], r = rstd[c];
+    double s1 = 0.0, s2 = 0.0;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
+        const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
+        const int64_t stride = static_cast<int64_t>(c_total) * hw;
+        const float* xslab = x + (n0 * c_total + c) * hw;
+        const float* gslab = dy + (n0 * c_total + c) * hw;
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / uhw, i = j - n * uhw;
+            float g = gslab[n * stride + i];
+            a1 += g;
+            a2 += g * ((xslab[n * stride + i] - m) * r);
+            if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+        }
+        s1 += a1;
+        s2 += a2;
+    }
+    __shared__ double r1[THREADS], r2[THREADS];
+    r1[threadIdx.x] = s1;
+    r2[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1[threadIdx.x] += r1[threadIdx.x + s]; r2[threadIdx.x] += r2[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1[0];
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2[0];
+    }
+}
+
+// dbeta = sum dy, dgamma = sum dy*xhat (gradients of the affine parameters).
+__global__ void bn_bwd_finalize_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ dgamma,
+                                       float* __restrict__ dbeta) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= c_total) return;
+    double s1 = 0.0, s2 = 0.0;
+    for (int s = 0; s < splits; ++s) {
+        s1 += part[(static_cast<int64_t>(c) * splits + s) * 2];
+        s2 += part[(static_cast<int64_t>(c) * splits + s) * 2 + 1];
+    }
+    dbeta[c] = static_cast<float>(s1);
+    dgamma[c] = static_cast<float>(s2);
+}
+
+// dx = gamma * rstd * (dy - dbeta/count - xhat * dgamma/count)
+__global__ void __launch_bounds__(THREADS) bn_bwd_dx_kernel(float* __restrict__ dx, const float* __restrict__ x, const float* __restrict__ dy,
+                                                             const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                             const float* __restrict__ gamma, const float* __restrict__ dgamma,
+                                                             const float* __restrict__ dbeta, int c_total, int64_t hw, float inv_count) {
+    int64_t plane = blockIdx.y;
+    int c = static_cast<int>(plane % c_total);
+    float m = mean[c], r = rstd[c], g = gamma ? gamma[c] : 1.f;
+    float k1 = dbeta[c] * inv_count, k2 = dgamma[c] * inv_count, gr = g * r;
+    const float* xs = x + plane * hw;
+    const float* gs = dy + plane * hw;
+    float* dst = dx + plane * hw;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; i < hw; i += static_cast<int64_t>(gridDim.x) * THREADS) {
+        float xh = (xs[i] - m) * r;
+        dst[i] = gr * (gs[i] - k1 - xh * k2);
+    }
+}
+
+// ---- conv block tail: BN -> ReLU -> 2x2 max pool, one pass each way ------------------------------
+// Forward: one thread per pooled element.
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_kernel(float* __restrict__ yp, const float* __restrict__ x,
+                                                                    const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                    const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                    int c_total, int h, int w, int64_t total) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
+    if (i >= total) return;
+    const int ow = w >> 1, oh = h >> 1;
+    int ox = static_cast<int>(i % ow);
+    int64_t t = i / ow;
+    int oy = static_cast<int>(t % oh);
+    int64_t plane = t / oh;
+    int c = static_cast<int>(plane % c_total);
+    float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
+    const float* src = x + plane * h * w + static_cast<int64_t>(2 * oy) * w + 2 * ox;
+    float2 r0 = *reinterpret_cast<const float2*>(src);
+    float2 r1 = *reinterpret_cast<const float2*>(src + w);
+    float v[4] = {r0.x, r0.y, r1.x, r1.y};
+    float best = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        best = fmaxf(best, fmaxf(fmaf((v[k] - m) * r, g, b), 0.f));
+    }
+    yp[i] = best;
+}
+
+// Backward recompute for one pooled element: the gradient each of the 4 window positions receives
+// through max-pool (ties share equally, crates/weta-autograd/src/ops.rs:305-314) and ReLU
+// (g * step(pre-activation), ops.rs:85), plus xhat at those positions.
+// The pooled maximum is never negative (it follows a ReLU); when it is zero every position is at or
+// below the ReLU threshold and receives nothing.  Otherwise the winners are the positions equal to
+// the maximum and each gets (1/count) * dy, the reference's mask/count then * g.
+__device__ __forceinline__ void pool_window_grads(const float v[4], float m, float r, float g, float b, float dyp, float gout[4], float xh[4]) {
+    float act[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        xh[k] = (v[k] - m) * r;
+        act[k] = fmaxf(fmaf(xh[k], g, b), 0.f);
+    }
+    const float best = fmaxf(fmaxf(act[0], act[1]), fmaxf(act[2], act[3]));
+    const int cnt = (act[0] == best) + (act[1] == best) + (act[2] == best) + (act[3] == best);
+    const float inv = cnt == 1 ? 1.f : (cnt == 2 ? 0.5f : (cnt == 3 ? (1.f / 3.f) : 0.25f));
+    const float share = best > 0.f ? inv * dyp : 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) gout[k] = act[k] == best ? share : 0.f;
+}
+
+// Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
+struct FastDiv {
+    uint32_t d, s;
+    uint64_t mul;
+    __host__ FastDiv() : d(1), s(0), mul(1ull << 32) {}
+    __host__ explicit FastDiv(uint32_t div) : d(div) {
+        s = 0;
+        while ((1ull << s) < div) ++s;
+        mul = ((1ull << (32 + s)) + div - 1) / div;
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> (32 + s)); }
+};
+
+// grid (C, S) like bn_stats: sums of the full-resolution gradient and of gradient * xhat.
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_stats_kernel(const float* __restrict__ x, const float* __restrict__ dyp,
+                                                                          const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                          const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                          int64_t n_img, int c_total, int h, int w, double* __restrict__ part) {
+    const int c = blockIdx.x;
+    const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
+    const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
+    double s1 = 0.0, s2 = 0.0;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
+        const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
+        const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+        const float* xslab = x + (n0 * c_total + c) * h * w;
+        const float* gslab = dyp + (n0 * c_total + c) * pooled;
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / up, i = j - n * up;
+            const uint32_t oy = i / static_cast<uint32_t>(ow), ox = i - oy * ow;
+            const float* src = xslab + n * xstride + 2 * oy * w + 2 * ox;
+            float2 r0 = *reinterpret_cast<const float2*>(src);
+            float2 r1 = *reinterpret_cast<const float2*>(src + w);
+            float v[4] = {r0.x, r0.y, r1.x, r1.y}, go[4], xh[4];
+            pool_window_grads(v, m, r, g, b, gslab[n * gstride + i], go, xh);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { a1 += go[k]; a2 += go[k] * xh[k]; }
+            if (++flushed == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+        }
+        s1 += a1;
+        s2 += a2;
+    }
+    __shared__ double r1s[THREADS], r2s[THREADS];
+    r1s[threadIdx.x] = s1;
+    r2s[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1s[threadIdx.x] += r1s[threadIdx.x + s]; r2s[threadIdx.x] += r2s[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1s[0];
+        part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2s[0];
+    }
+}
+
+// dx at full resolution; also per-(channel, split) sums of dx, which is the gradient of the
+// convolution bias that feeds this BatchNorm.  grid (C, S), same walk as the stats kernel.
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __restrict__ dx, const float* __restrict__ x,
+                                                                       const float* __restrict__ dyp, const float* __restrict__ mean,
+                                                                       const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                                       const float* __restrict__ beta, const float* __restrict__ dgamma,
+                                                                       const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
+                                                                       int w, float inv_count, double* __restrict__ bias_part) {
+    const int c = blockIdx.x;
+    const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
+    const float k1 = dbeta[c] * inv_count, k2 = dgamma[c] * inv_count, gr = g * r;
+    const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
+    double sb = 0.0;
+    {
+        const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+        const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
+        const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
+        const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+        const float* xslab = x + (n0 * c_total + c) * h * w;
+        const float* gslab = dyp + (n0 * c_total + c) * pooled;
+        float* dslab = dx + (n0 * c_total + c) * h * w;
+        float a = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / up, i = j - n * up;
+            const uint32_t oy = i / static_cast<uint32_t>(ow), ox = i - oy * ow;
+            const int64_t o = n * xstride + static_cast<int64_t>(2 * oy) * w + 2 * ox;
+            float2 r0 = *reinterpret_cast<const float2*>(xslab + o);
+            float2 r1 = *reinterpret_cast<const float2*>(xslab + o + w);
+            float v[4] = {r0.x, r0.y, r1.x, r1.y}, go[4], xh[4], d[4];
+            pool_window_grads(v, m, r, g, b, gslab[n * gstride + i], go, xh);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { d[k] = gr * (go[k] - k1 - xh[k] * k2); a += d[k]; }
+            *reinterpret_cast<float2*>(dslab + o) = make_float2(d[0], d[1]);
+            *reinterpret_cast<float2*>(dslab + o + w) = make_float2(d[2], d[3]);
+            if (++flushed == 64) { sb += a; a = 0.f; flushed = 0; }
+        }
+        sb += a;
+    }
+    __shared__ double rs[THREADS];
+    rs[threadIdx.x] = sb;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) rs[threadIdx.x] += rs[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && bias_part) bias_part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = rs[0];
+}
+
+// Width-multiple-of-4 variants: one thread handles two neighbouring pooled elements, i.e. a 2x4 patch
+// of x, with 128-bit loads and stores; same arithmetic as the kernels above.
+template <bool WRITE_DX>
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, const float* __restrict__ x,
+                                                                         const float* __restrict__ dyp, const float* __restrict__ mean,
+                                                                         const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                                         const float* __restrict__ beta, const float* __restrict__ dgamma,
+                                                                         const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
+                                                                         int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
+                                                                         FastDiv div_owp) {
+    const int c = blockIdx.x;
+    const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
+    float k1 = 0.f, k2 = 0.f, gr = 0.f;
+    if (WRITE_DX) { k1 = dbeta[c] * inv_count; k2 = dgamma[c] * inv_count; gr = g * r; }
+    const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
+    const uint32_t owp = static_cast<uint32_t>(ow >> 1), pairs = static_cast<uint32_t>(oh) * owp;
+    const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
+    const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);
+    const uint32_t items = static_cast<uint32_t>(n1 - n0) * pairs;
+    const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
+    const float* xslab = x + (n0 * c_total + c) * h * w;
+    const float* gslab = dyp + (n0 * c_total + c) * pooled;
+    float* dslab = WRITE_DX ? dx + (n0 * c_total + c) * h * w : nullptr;
+    double s1 = 0.0, s2 = 0.0;
+    float a1 = 0.f, a2 = 0.f;
+    int flushed = 0;
+#pragma unroll 2
+    for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+        const uint32_t n = div_pairs.div(j), i = j - n * pairs;
+        const uint32_t oy = div_owp.div(i), oxp = i - oy * owp;
+        const int64_t o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
+        const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
+        const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
+        const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
+        const float va[4] = {r0.x, r0.y, r1.x, r1.y}, vb[4] = {r0.z, r0.w, r1.z, r1.w};
+        float ga[4], gb[4], xa[4], xb[4];
+        pool_window_grads(va, m, r, g, b, gy.x, ga, xa);
+        pool_window_grads(vb, m, r, g, b, gy.y, gb, xb);
+        if (WRITE_DX) {
+            float da[4], db[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                da[k] = gr * (ga[k] - k1 - xa[k] * k2);
+                db[k] = gr * (gb[k] - k1 - xb[k] * k2);
+                a1 += da[k] + db[k];
+            }
+            *reinterpret_cast<float4*>(dslab + o) = make_float4(da[0], da[1], db[0], db[1]);
+            *reinterpret_cast<float4*>(dslab + o + w) = make_float4(da[2], da[3], db[2], db[3]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a1 += ga[k] + gb[k];
+                a2 += ga[k] * xa[k] + gb[k] * xb[k];
+            }
+        }
+        if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+    }
+    s1 += a1;
+    s2 += a2;
+    __shared__ double r1s[THREADS], r2s[THREADS];
+    r1s[threadIdx.x] = s1;
+    r2s[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1s[threadIdx.x] += r1s[threadIdx.x + s]; r2s[threadIdx.x] += r2s[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && part) {
+        if (WRITE_DX) {
+            part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = r1s[0];  // sum of dx: the conv bias gradient
+        } else {
+            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1s[0];
+            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2s[0];
+        }
+    }
+}
+
+__global__ void sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= c_total) return;
+    double s = 0.0;
+    for (int k = 0; k < splits; ++k) s += part[static_cast<int64_t>(c) * splits + k];
+    out[c] = static_cast<float>(s);
+}
+
+// Number of image slabs per channel for the per-channel reductions (grid = channels x slabs).  The grid
+// is sized to ONE resident wave of the kernel (occupancy x SM count): these kernels stream for the
+// whole launch, so a second, partly filled wave would cost as much as the first.  Also few enough
+// images per slab that the kernels' 32-bit item counters cannot overflow.
+template <class Kernel>
+int stat_splits(WbBackend* be, Kernel kernel, int c, int64_t n_img, int64_t items_per_image) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, THREADS, 0) != cudaSuccess || per_sm < 1) {
+        (void)cudaGetLastError();
+        per_sm = 4;
+    }
+    int64_t want = std::max<int64_t>(1, static_cast<int64_t>(per_sm) * be->sm_count / c);
+    int64_t need = (n_img * items_per_image + (int64_t(1) << 30) - 1) / (int64_t(1) << 30);
+    int64_t splits = std::max<int64_t>(1, std::min<int64_t>(std::max(want, need), n_img));
+    int64_t per = (n_img + splits - 1) / splits;
+    return static_cast<int>((n_img + per - 1) / per);  // no slab is empty
+}
+
+}  // namespace
+
+extern "C" int wb_bn2d_stats(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, double eps, double momentum, float* mean,
+                             float* rstd, float* running_mean, float* running_var) {
+    WB_REQUIRE(b && x && mean && rstd, WB_ERR_INVALID, "wb_bn2d_stats: null pointer");
+    WB_REQUIRE(n > 0 && c > 0 && hw > 0, WB_ERR_INVALID, "wb_bn2d_stats: empty input");
+    WbProfileScope ps(b, "bn2d_stats");
+    int splits = stat_splits(b, bn_stats_kernel, static_cast<int>(c), n, hw);
+    void* s = nullptr;
+    WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 2 * sizeof(double), &s));
+    bn_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, n, static_cast<int>(c), hw, static_cast<double*>(s));
+    WB_LAUNCH_OK(b);
+    bn_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(static_cast<double*>(s), splits, x, static_cast<int>(c), hw,
+                                                                                    n * hw, static_cast<float>(eps), static_cast<float>(momentum),
+                                                                                    static_cast<float>(1.0 - momentum), mean, rstd, running_mean,
+                                                                                    running_var);
+    WB_LAUNCH_OK(b);
+    return WB_OK;
+}
+
+extern "C" int wb_bn2d_apply(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* mean, const float* rstd,
+                             const float* gamma, const float* beta, int relu, float* y) {
+    WB_REQUIRE(b && x && y && mean && rstd, WB_ERR_INVALID, "wb_bn2d_apply: null pointer");
+    WbProfileScope ps(b, "bn2d_apply");
+    unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw / 4 + THREADS - 1) / THREADS, 64)));
+    WB_REQUIRE(c <= 65535, WB_ERR_UNSUPPORTED, "wb_bn2d_apply: too many channels");
+    // gridDim.y is limited to 65535: launch whole images' worth of planes at a time.
+    for (int64_t p0 = 0; p0 < n * c; p0 += 65535 / c * c) {
+        int64_t cnt = std::min<int64_t>(65535 / c * c, n * c - p0);
+        bn_apply_kernel<<<dim3(gx, static_cast<unsigned>(cnt)), THREADS, 0, b->stream>>>(y + p0 * hw, x + p0 * hw, mean, rstd, gamma, beta,
+                                                                                         static_cast<int>(c), hw, relu);
+        WB_LAUNCH_OK(b);
+    }
+    return WB_OK;
+}
+
+extern "C" int wb_bn2d_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* gamma, const float* beta,
+                           float* running_mean, float* running_var, double momentum, double eps, float* y, float* save_mean,
+                           float* save_rstd) {
+    WB_TRY(wb_bn2d_stats(b, x, n, c, hw, eps, momentum, save_mean, save_rstd, running_mean, running_var));
+    return wb_bn2d_apply(b, x, n, c, hw, save_mean, save_rstd, gamma, beta, 0, y);
+}
+
+extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_t n, int64_t c, int64_t hw, const float* gamma,
+                           const float* save_mean, const float* save_rstd, float* dx, float* dgamma, float* dbeta) {
+    WB_REQUIRE(b && x && dy && dx && dgamma && dbeta && save_mean && save_rstd, WB_ERR_INVALID, "wb_bn2d_bwd: null pointer");
+    WbProfileScope ps(b, "bn2d_bwd");
+    int splits = stat_splits(b, bn_bwd_stats_kernel, static_cast<int>(c), n, hw);
+    void* s = nullptr;
+    WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 2 * sizeof(double), &s));
+    bn_bwd_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, dy, save_mean, save_rstd, n, static_cast<int>(c), hw,
+                                                                                          static_cast<double*>(s));
+    WB_LAUNCH_OK(b);
+    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
+    WB_LAUNCH_OK(b);
+    unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw + THREADS - 1) / THREADS, 64)));
+    for (int64_t p0 = 0; p0 < n * c; p0 += 65535 / c * c) {
+        int64_t cnt = std::min<int64_t>(65535 / c * c, n * c - p0);
+        bn_bwd_dx_kernel<<<dim3(gx, static_cast<unsigned>(cnt)), THREADS, 0, b->stream>>>(dx + p0 * hw, x + p0 * hw, dy + p0 * hw, save_mean, save_rstd,
+                                                                                          gamma, dgamma, dbeta, static_cast<int>(c), hw,
+                                                                                          static_cast<float>(1.0 / static_cast<double>(n * hw)));
+        WB_LAUNCH_OK(b);
+    }
+    return WB_OK;
+}
+
+extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma,
+                                   const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
+                                   float* save_mean, float* save_rstd) {
+    WB_REQUIRE(b && x && gamma && beta && y_pooled, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: null pointer");
+    WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_fwd: height and width must be even");
+    WB_TRY(wb_bn2d_stats(b, x, n, c, h * w, eps, momentum, save_mean, save_rstd, running_mean, running_var));
+    WbProfileScope ps(b, "bn_relu_pool_fwd");
+    int64_t total = n * c * (h / 2) * (w / 2);
+    bn_relu_pool_fwd_kernel<<<static_cast<unsigned>((total + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+        y_pooled, x, save_mean, save_rstd, gamma, beta, static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), total);
+    WB_LAUNCH_OK(b);
+    return WB_OK;
+}
+
+extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
+                                   const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
+                                   float* dgamma, float* dbeta, float* dbias_conv) {
+    WB_REQUIRE(b && x && dy_pooled && dx && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
+    WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
+    WbProfileScope ps(b, "bn_relu_pool_bwd");
+    int splits = stat_splits(b, bn_relu_pool_bwd_pair_kernel<true>, static_cast<int>(c), n, h * w);
+    void* s = nullptr;
+    WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 3 * sizeof(double), &s));
+    double* part = static_cast<double*>(s);
+    double* bias_part = part + static_cast<size_t>(c) * splits * 2;
+    dim3 grid(static_cast<unsigned>(c), splits);
+    const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(dy_pooled) & 7) == 0;
+    const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
+    const FastDiv div_pairs(static_cast<uint32_t>(std::max<int64_t>(1, (h / 2) * (w / 4)))), div_owp(static_cast<uint32_t>(std::max<int64_t>(1, w / 4)));
+    if (pairs)
+        bn_relu_pool_bwd_pair_kernel<false><<<grid, THREADS, 0, b->stream>>>(nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr,
+                                                                            nullptr, n, static_cast<int>(c), static_cast<int>(h),
+                                                                            static_cast<int>(w), inv_count, part, div_pairs, div_owp);
+    else
+        bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
+                                                                      static_cast<int>(h), static_cast<int>(w), part);
+    WB_LAUNCH_OK(b);
+    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
+    WB_LAUNCH_OK(b);
+    if (pairs)
+        bn_relu_pool_bwd_pair_kernel<true><<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
+                                                                           static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
+                                                                           inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
+    else
+        bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
+                                                                   static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
+                                                                   dbias_conv ? bias_part : nullptr);
+    WB_LAUNCH_OK(b);
+    if (dbias_conv) {
+        sum_parts_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(bias_part, splits, static_cast<int>(c), dbias_conv);
+        WB_LAUNCH_OK(b);
+    }
+    return WB_OK;
+}
+

@@ -235,10 +235,14 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         args.split_stride_d = 0;
     }
     if (status == WB_OK) {
-        WB_REQUIRE(grid_batch * splits <= 65535, WB_ERR_UNSUPPORTED, "gemm: batch x split-K exceeds the grid limit");
-        dim3 grid(static_cast<unsigned>(tiles_n), static_cast<unsigned>(tiles_m), static_cast<unsigned>(grid_batch * splits));
+        args.tiles_m = tiles_m;
+        args.tiles_n = tiles_n;
+        const int64_t total_tiles = tiles * splits;
+        WB_REQUIRE(total_tiles < (int64_t(1) << 31), WB_ERR_UNSUPPORTED, "gemm: too many tiles");
+        args.total_tiles = static_cast<int>(total_tiles);
+        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, be->sm_count)));
         const bool amn = A.mn_major, bmn = B.mn_major;
-        constexpr int STG = 3;  // 3 x 32 KB: two CTAs share an SM, so one tile's epilogue overlaps the other's main loop
+        constexpr int STG = 5;  // 5 x 32 KB ring + 18 KB epilogue staging: one persistent CTA per SM
         if (!amn && !bmn) status = launch_tc<BN, STG, false, false>(be, st, args, grid);
         else if (!amn && bmn) status = launch_tc<BN, STG, false, true>(be, st, args, grid);
         else if (amn && !bmn) status = launch_tc<BN, STG, true, false>(be, st, args, grid);

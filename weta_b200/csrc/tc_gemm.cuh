@@ -1,9 +1,10 @@
 // TF32 tensor-core GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma
 // (kind::tf32, accumulator in TMEM) -> tcgen05.ld epilogue.
 //
-// One CTA computes one 128 x BN output tile.  Warp 0 (one elected lane) issues the TMA loads,
-// warp 1 (one lane) issues the MMAs, then all four warps read the accumulator back (warp w owns
-// TMEM lanes 32w..32w+31, i.e. tile rows 32w..32w+31) and store it.  Operands may be K-major
+// Persistent CTAs (one per SM) each walk a list of 128 x BN output tiles.  Warp 0 (one elected lane)
+// issues the TMA loads, warp 1 (one lane) issues the MMAs into one of two TMEM accumulators, and four
+// epilogue warps read the other accumulator back (a warp may read TMEM lanes 32*(warp%4)..+31, i.e. 32
+// tile rows) and store it, so one tile's epilogue overlaps the next tile's main loop.  Operands may be K-major
 // (contraction index contiguous) or MN-major (row/column index contiguous); both are described to
 // the tensor core through the shared-memory matrix descriptor, so no operand is ever transposed
 // in memory.  A "segment" is one (A map, B map, K extent) triple; up to three segments accumulate
@@ -24,7 +25,7 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 32;                 // 32 tf32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;              // K per tcgen05.mma for tf32
-constexpr int THREADS = 128;
+constexpr int THREADS = 192;          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 26;
 
 struct Segment {
@@ -50,6 +51,7 @@ struct Args {
     int splits;            // split-K factor: blockIdx.z = batch * splits + split
     int batched_a, batched_b;  // 0: operand shared by every batch (TMA coordinate 0)
     int kpb;                   // K blocks per image when the contraction spans the batch, else 0
+    int tiles_m, tiles_n, total_tiles;  // tile list walked by the persistent CTAs
     Epilogue ep;
     int64_t split_stride_d;    // distance between split-K partial outputs
     int* error_flag;
@@ -143,109 +145,217 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+constexpr int EPI_PITCH = 36;  // floats per staged row: 144 B keeps float4 alignment and spreads banks
+
 template <int BN, int STAGES>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
     alignas(1024) float a[STAGES][BM * BK];
     alignas(1024) float b[STAGES][BN * BK];
+    alignas(16) float stage[4][32 * EPI_PITCH];  // epilogue staging, one slab per epilogue warp
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t tmem_full;
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
     uint32_t tmem_base;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list round-robin.  Six warps:
+//   warp 0      TMA producer (one lane)            smem ring, STAGES deep
+//   warp 1      MMA issuer (one lane); owns TMEM   two accumulators of BN columns, used alternately
+//   warps 2..5  epilogue: TMEM -> registers -> shared staging -> coalesced global stores
+// so the stores of tile i overlap the loads and MMAs of tile i+1.
 // A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(THREADS, (STAGES <= 3 && BN <= 128) ? 2 : 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
+__global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using SS = SharedStorage<BN, STAGES>;
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int batch = blockIdx.z / args.splits, split = blockIdx.z % args.splits;
-    // This CTA's share of the K blocks (split-K).
     const int kb_per = (args.k_blocks + args.splits - 1) / args.splits;
-    const int kb_begin = split * kb_per;
-    const int kb_end = min(args.k_blocks, kb_begin + kb_per);
-    const int total_iters = max(0, kb_end - kb_begin) * args.num_segments;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&ss.full[s], 1);
             mbar_init(&ss.empty[s], 1);
         }
-        mbar_init(&ss.tmem_full, 1);
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&ss.tmem_full[a], 1);
+            mbar_init(&ss.tmem_empty[a], 4);  // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
-        // BN fp32 accumulator columns (a power of two >= 32).
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(BN)
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_d = ss.tmem_base;
+    const uint32_t tmem_base = ss.tmem_base;
     bool ok = true;
 
-    if (warp == 0 && lane == 0) {
-        // ---- TMA producer -------------------------------------------------------------------
-        constexpr uint32_t stage_bytes = (BM * BK + BN * BK) * sizeof(float);
-        int it = 0;
-        for (int sg = 0; sg < args.num_segments && ok; ++sg) {
-            const CUtensorMap* ma = &args.seg[sg].a;
-            const CUtensorMap* mb = &args.seg[sg].b;
-            for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&ss.full[s], stage_bytes);
-                // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
-                // operand pair, kpb blocks per image (a convolution's weight gradient); the image
-                // index becomes the third TMA coordinate and each image's tail is zero-filled.
-                const int k0 = (args.kpb > 0 ? kb % args.kpb : kb) * BK;
-                const int kz = args.kpb > 0 ? kb / args.kpb : 0;
-                const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
-                const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
-                if constexpr (A_MN) {
+    // Tile t -> (n block, m block, z = batch * splits + split); n fastest so neighbouring CTAs share A.
+    auto decode = [&](int t, int& m0, int& n0, int& batch, int& split, int& kb_begin, int& kb_end) {
+        const int nb = t % args.tiles_n;
+        const int r = t / args.tiles_n;
+        const int mb = r % args.tiles_m;
+        const int z = r / args.tiles_m;
+        m0 = mb * BM;
+        n0 = nb * BN;
+        batch = z / args.splits;
+        split = z % args.splits;
+        kb_begin = split * kb_per;
+        kb_end = min(args.k_blocks, kb_begin + kb_per);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ---------------------------------------------------------------
+            constexpr uint32_t stage_bytes = (BM * BK + BN * BK) * sizeof(float);
+            int it = 0;
+            for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x) {
+                int m0, n0, batch, split, kb_begin, kb_end;
+                decode(t, m0, n0, batch, split, kb_begin, kb_end);
+                for (int sg = 0; sg < args.num_segments && ok; ++sg) {
+                    const CUtensorMap* ma = &args.seg[sg].a;
+                    const CUtensorMap* mb = &args.seg[sg].b;
+                    for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
+                        mbar_expect_tx(&ss.full[s], stage_bytes);
+                        // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
+                        // operand pair, kpb blocks per image (a convolution's weight gradient); the image
+                        // index becomes the third TMA coordinate and each image's tail is zero-filled.
+                        const int k0 = (args.kpb > 0 ? kb % args.kpb : kb) * BK;
+                        const int kz = args.kpb > 0 ? kb / args.kpb : 0;
+                        const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
+                        const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
+                        if constexpr (A_MN) {
 #pragma unroll
-                    for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
-                } else {
-                    tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
-                }
-                if constexpr (B_MN) {
+                            for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
+                        } else {
+                            tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
+                        }
+                        if constexpr (B_MN) {
 #pragma unroll
-                    for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
-                } else {
-                    tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
+                            for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
+                        } else {
+                            tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
+                        }
+                    }
                 }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ---------------------------------------------------------------------
-        constexpr uint32_t idesc = make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-        for (int it = 0; it < total_iters; ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1;
-            if (!mbar_wait(&ss.full[s], ph)) { ok = false; break; }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer -----------------------------------------------------------------
+            constexpr uint32_t idesc = make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            int it = 0, tile_iter = 0;
+            for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+                int m0, n0, batch, split, kb_begin, kb_end;
+                decode(t, m0, n0, batch, split, kb_begin, kb_end);
+                const int acc = tile_iter & 1;
+                const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
+                // Wait until the epilogue has drained this accumulator (passes at once on first use).
+                if (!mbar_wait(&ss.tmem_empty[acc], (use & 1) ^ 1)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
+                const int iters = (kb_end - kb_begin) * args.num_segments;
+                for (int i = 0; i < iters; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&ss.full[s], ph)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_base = smem_u32(&ss.a[s][0]), b_base = smem_u32(&ss.b[s][0]);
+#pragma unroll
+                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                        // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8 elements is +32 B
+                        //          inside the swizzle row.
+                        // MN-major: each K index is a 128 B row of 32 consecutive M/N elements; rows come in
+                        //          groups of 4 (512 B apart, SBO), 32-element M/N blocks are 32*BK*4 B apart (LBO);
+                        //          a K step of 8 is two groups = +1024 B.
+                        uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
+                        uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
+                        umma_tf32(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
+                }
+                if (!ok) break;
+                umma_commit(&ss.tmem_full[acc]);  // accumulator complete once every MMA above has retired
+            }
+        }
+    } else {
+        // ---- epilogue warps ---------------------------------------------------------------------
+        const int ew = warp & 3;  // TMEM lane group this warp may read: lanes 32*ew .. 32*ew+31
+        float* stage = &ss.stage[ew][0];
+        const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
+                            (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
+        int tile_iter = 0;
+        for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+            int m0, n0, batch, split, kb_begin, kb_end;
+            decode(t, m0, n0, batch, split, kb_begin, kb_end);
+            const int acc = tile_iter & 1;
+            const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
+            if (!mbar_wait(&ss.tmem_full[acc], use & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_base = smem_u32(&ss.a[s][0]), b_base = smem_u32(&ss.b[s][0]);
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(ew * 32) << 16);
+            const int row = m0 + ew * 32 + lane;
+            float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d;
+            const float bm = (args.ep.bias_m && row < args.m) ? args.ep.bias_m[row] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                if (n0 + c >= args.n) break;
+                float v[32];
+                tmem_ld32(tmem_d + c, v);
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8 elements is +32 B
-                //          inside the swizzle row.
-                // MN-major: each K index is a 128 B row of 32 consecutive M/N elements; rows come in
-                //          groups of 4 (512 B apart, SBO), 32-element M/N blocks are 32*BK*4 B apart (LBO);
-                //          a K step of 8 is two groups = +1024 B.
-                uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
-                uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
-                umma_tf32(tmem_d, ad, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+                for (int i = 0; i < 32; i += 4) {
+                    float r[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int col = n0 + c + i + j;
+                        float x = v[i + j] + bm;
+                        if (args.ep.bias_n && col < args.n) x += args.ep.bias_n[col];
+                        if (args.ep.relu) x = fmaxf(x, 0.f);
+                        r[j] = x;
+                    }
+                    *reinterpret_cast<float4*>(stage + lane * EPI_PITCH + i) = make_float4(r[0], r[1], r[2], r[3]);
+                }
+                __syncwarp();
+                // Each store instruction of the warp now writes four 128-byte row segments.
+#pragma unroll
+                for (int it8 = 0; it8 < 8; ++it8) {
+                    const int r = it8 * 4 + (lane >> 3), cc = (lane & 7) * 4;
+                    const int grow = m0 + ew * 32 + r, gcol = n0 + c + cc;
+                    if (grow < args.m && gcol < args.n) {
+                        float4 val = *reinterpret_cast<const float4*>(stage + r * EPI_PITCH + cc);
+                        float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
+                        if (vec_ok && gcol + 4 <= args.n) {
+                            if (args.ep.accumulate) {
+                                float4 o = *reinterpret_cast<const float4*>(p);
+                                val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(p) = val;
+                        } else {
+                            const float e[4] = {val.x, val.y, val.z, val.w};
+                            for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
+                        }
+                    }
+                }
+                __syncwarp();
             }
-            umma_commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
+            // All of this warp's TMEM reads for the tile are done: hand the accumulator back.
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ss.tmem_empty[acc]);
         }
-        umma_commit(&ss.tmem_full);
     }
     if (!ok) {
         atomicExch(args.error_flag, 1);
@@ -253,73 +363,10 @@ __global__ void __launch_bounds__(THREADS, (STAGES <= 3 && BN <= 128) ? 2 : 1) g
         const long long t0 = clock64();
         while (clock64() - t0 < 4000000) {}
     }
-    __syncwarp();
-
-    // ---- epilogue: TMEM -> registers -> global ----------------------------------------------
-    bool ready = total_iters == 0 ? true : mbar_wait(&ss.tmem_full, 0);
-    if (!ready && lane == 0) atomicExch(args.error_flag, 1);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ready) {
-        // Each thread holds one accumulator row (32 columns per tcgen05.ld).  The rows are staged through
-        // shared memory (the pipeline buffers are idle by now) so that every store instruction of a warp
-        // writes four 128-byte row segments instead of 32 scattered 16-byte pieces.
-        constexpr int PITCH = 36;  // floats; 144 B keeps float4 alignment and spreads banks
-        float* stage = reinterpret_cast<float*>(&ss.a[0][0]) + warp * (32 * PITCH);
-        const int row = m0 + warp * 32 + lane;
-        float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d;
-        const float bm = (args.ep.bias_m && row < args.m) ? args.ep.bias_m[row] : 0.f;
-        const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
-                            (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-            if (n0 + c >= args.n) break;
-            float v[32];
-            if (total_iters == 0) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            } else {
-                tmem_ld32(tmem_d + (static_cast<uint32_t>(warp * 32) << 16) + c, v);
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-                float r[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int col = n0 + c + i + j;
-                    float x = v[i + j] + bm;
-                    if (args.ep.bias_n && col < args.n) x += args.ep.bias_n[col];
-                    if (args.ep.relu) x = fmaxf(x, 0.f);
-                    r[j] = x;
-                }
-                *reinterpret_cast<float4*>(stage + lane * PITCH + i) = make_float4(r[0], r[1], r[2], r[3]);
-            }
-            __syncwarp();
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-                const int r = it * 4 + (lane >> 3), cc = (lane & 7) * 4;
-                const int grow = m0 + warp * 32 + r, gcol = n0 + c + cc;
-                if (grow < args.m && gcol < args.n) {
-                    float4 val = *reinterpret_cast<const float4*>(stage + r * PITCH + cc);
-                    float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
-                    if (vec_ok && gcol + 4 <= args.n) {
-                        if (args.ep.accumulate) {
-                            float4 o = *reinterpret_cast<const float4*>(p);
-                            val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
-                        }
-                        *reinterpret_cast<float4*>(p) = val;
-                    } else {
-                        const float e[4] = {val.x, val.y, val.z, val.w};
-                        for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
-                    }
-                }
-            }
-            __syncwarp();
-        }
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(BN) : "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
