@@ -157,7 +157,9 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     if (!operand_ok(A, batch) || !operand_ok(B, batch)) return WB_ERR_UNSUPPORTED;
     GemmState* st = nullptr;
     WB_TRY(get_state(be, &st));
-    constexpr int BN = 128;
+    // 128 x 256 tiles when the output is wide enough: half the A traffic and twice the MMA work per
+    // pipeline stage; 128 x 128 otherwise.
+    const int BN = n > 128 ? 256 : 128;
     tc::Args args{};
     void *hi_a = nullptr, *hi_b = nullptr;
     size_t ka = 0, kb = 0;
@@ -242,11 +244,18 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         args.total_tiles = static_cast<int>(total_tiles);
         dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, be->sm_count)));
         const bool amn = A.mn_major, bmn = B.mn_major;
-        constexpr int STG = 5;  // 5 x 32 KB ring + 18 KB epilogue staging: one persistent CTA per SM
-        if (!amn && !bmn) status = launch_tc<BN, STG, false, false>(be, st, args, grid);
-        else if (!amn && bmn) status = launch_tc<BN, STG, false, true>(be, st, args, grid);
-        else if (amn && !bmn) status = launch_tc<BN, STG, true, false>(be, st, args, grid);
-        else status = launch_tc<BN, STG, true, true>(be, st, args, grid);
+        // Shared memory: 4 x 48 KB ring (BN = 256) or 5 x 32 KB (BN = 128) + 18 KB epilogue staging; one persistent CTA per SM.
+        if (BN == 256) {
+            if (!amn && !bmn) status = launch_tc<256, 4, false, false>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<256, 4, false, true>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<256, 4, true, false>(be, st, args, grid);
+            else status = launch_tc<256, 4, true, true>(be, st, args, grid);
+        } else {
+            if (!amn && !bmn) status = launch_tc<128, 5, false, false>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<128, 5, false, true>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<128, 5, true, false>(be, st, args, grid);
+            else status = launch_tc<128, 5, true, true>(be, st, args, grid);
+        }
     }
     if (status == WB_OK && splits > 1) {
         const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
