@@ -240,28 +240,48 @@ def main():
     # ---- roofline of the dominant kernel --------------------------------------------------------
     peaks = load_peaks()
     hw1, hw2 = cfg.hw * cfg.hw, (cfg.hw // 2) ** 2
-    flops = {  # algorithmic 2*M*N*K per launch, per rank
-        "L0.conv_fwd_gemm": 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1, "L0.conv_wgrad_gemm": 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1,
-        "L1.conv_fwd_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2, "L1.conv_wgrad_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2,
-        "L1.conv_dgrad_gemm": 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2,
-        "L3.linear_fwd_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4), "L3.linear_wgrad_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4),
-        "L3.linear_dgrad_gemm": 2.0 * batch * cfg.hidden * cfg.c2 * (hw2 // 4),
+    fc_in = cfg.c2 * (hw2 // 4)
+    act1, act2 = 4.0 * batch * cfg.c1 * hw1, 4.0 * batch * cfg.c2 * hw2      # bytes of each conv output
+    in1, in2 = 4.0 * batch * cfg.in_ch * hw1, 4.0 * batch * cfg.c1 * hw2     # bytes of each conv input
+    work = {  # per launch, per rank: ("tensor", algorithmic 2*M*N*K flops) or ("hbm", algorithmic bytes moved)
+        "L0.conv_fwd_gemm": ("tensor", 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1), "L0.conv_wgrad_gemm": ("tensor", 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1),
+        "L1.conv_fwd_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2), "L1.conv_wgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
+        "L1.conv_dgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
+        "L3.linear_fwd_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in), "L3.linear_wgrad_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in),
+        "L3.linear_dgrad_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in),
+        "L5.linear_fwd_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden), "L5.linear_wgrad_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden),
+        "L5.linear_dgrad_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden),
+        "L0.im2col": ("hbm", in1 * 10), "L1.im2col": ("hbm", in2 * 10), "L1.col2im": ("hbm", in2 * 10),
+        # BN+ReLU+pool: forward reads x twice (statistics, apply) and writes x/4; backward reads x and dy/4 twice and writes dx
+        "L0.bn_relu_pool_fwd": ("hbm", act1 * 2.25), "L1.bn_relu_pool_fwd": ("hbm", act2 * 2.25),
+        "L0.bn_relu_pool_bwd": ("hbm", act1 * 3.5), "L1.bn_relu_pool_bwd": ("hbm", act2 * 3.5),
+        "L2.dropout_fwd": ("hbm", 8.0 * batch * fc_in), "L2.dropout_bwd": ("hbm", 8.0 * batch * fc_in),
+        "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
+        "L6.adam": ("hbm", 28.0 * tr.arena_len),
     }
-    top = max(op_times.items(), key=lambda kv: kv[1][1])
     shares = {k: round(v[1] / total_ms, 4) for k, v in sorted(op_times.items(), key=lambda kv: -kv[1][1])}
-    top_name, (top_calls, top_ms) = top
+    top_name, (top_calls, top_ms) = max(op_times.items(), key=lambda kv: kv[1][1])
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
-    if top_name in flops:
-        achieved = flops[top_name] / (top_ms / top_calls * 1e-3) / 1e12
-        roofline = {"kernel": top_name, "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                    "traffic": None, "peak_note": f"{peaks['source']} sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate)",
-                    "avg_ms_per_launch": top_ms / top_calls, "launches": top_calls}
+    per_op = {}
+    for k, (calls, ms) in op_times.items():
+        if k in work:
+            kind, amount = work[k]
+            rate = amount / (ms / calls * 1e-3)
+            per_op[k] = {"bound": kind, "achieved": rate / (1e12 if kind == "tensor" else 1e9), "unit": "TFLOP/s" if kind == "tensor" else "GB/s",
+                         "frac": rate / (tf32_peak * 1e12 if kind == "tensor" else peaks["hbm_gbs"] * 1e9), "avg_ms": ms / calls}
+    if top_name in per_op:
+        o = per_op[top_name]
+        roofline = {"kernel": top_name, "bound": o["bound"], "achieved": o["achieved"], "peak": tf32_peak if o["bound"] == "tensor" else peaks["hbm_gbs"],
+                    "unit": o["unit"], "frac": o["frac"], "traffic": None, "avg_ms_per_launch": o["avg_ms"], "launches": top_calls,
+                    "peak_note": (f"{peaks['source']} sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate)" if o["bound"] == "tensor"
+                                  else f"{peaks['source']} copy bandwidth")}
     else:
         roofline = {"kernel": top_name, "bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
                     "avg_ms_per_launch": top_ms / top_calls, "launches": top_calls}
-    gemm_ms = sum(v[1] for k, v in op_times.items() if k in flops)
-    gemm_flops = sum(flops[k] * v[0] for k, v in op_times.items() if k in flops)
+    gemm_ms = sum(v[1] for k, v in op_times.items() if k in work and work[k][0] == "tensor")
+    gemm_flops = sum(work[k][1] * v[0] for k, v in op_times.items() if k in work and work[k][0] == "tensor")
     roofline["all_contractions_tflops"] = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    roofline["per_op"] = {k: {"bound": v["bound"], "achieved": round(v["achieved"], 1), "frac": round(v["frac"], 3)} for k, v in per_op.items()}
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(THREADS) dropout_mask_kernel(float* __restrict
 // One warp per row.  loss_row = -(z[y] - max - log(sum exp(z - max))); p = exp(z - lse);
 // dz = (p - onehot) * gscale, with gscale = upstream_grad / N for the mean reduction.
 __global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
-                                                              int cols, float* __restrict__ probs, float* __restrict__ dz,
+                                                              int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                               float* __restrict__ row_loss, float gscale) {
     int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
@@ -86,8 +86,9 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __rest
     for (int c = lane; c < cols; c += 32) {
         float p = expf(zr[c] - lse);
         if (probs) probs[row * cols + c] = p;
-        if (dz) dz[row * cols + c] = (p - (c == y ? 1.f : 0.f)) * gscale;
+        if (dz) dz[row * dz_pitch + c] = (p - (c == y ? 1.f : 0.f)) * gscale;
     }
+    if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;  // padding columns of a pitched gradient
     if (lane == 0 && row_loss) row_loss[row] = (y >= 0 && y < cols) ? -(zr[y] - lse) : 0.f;
 }
 
@@ -184,10 +185,12 @@ extern "C" int wb_dropout_mask(WbBackend* b, float* mask, int64_t n, double p, u
     return WB_OK;
 }
 
-extern "C" int wb_softmax_ce(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs,
-                             float* dlogits, float* row_loss, float* mean_loss, double upstream) {
+// dlogits rows may be padded to `dz_pitch` floats (>= cols, padding zero-filled) so that a following
+// tensor-core contraction can read them through TMA even when cols is not a multiple of 4.
+int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs, float* dlogits,
+                          int64_t dz_pitch, float* row_loss, float* mean_loss, double upstream) {
     WB_REQUIRE(b && logits && labels, WB_ERR_INVALID, "wb_softmax_ce: null pointer");
-    WB_REQUIRE(cols > 0 && cols < (int64_t(1) << 31), WB_ERR_INVALID, "wb_softmax_ce: bad class count");
+    WB_REQUIRE(cols > 0 && cols < (int64_t(1) << 31) && dz_pitch >= cols, WB_ERR_INVALID, "wb_softmax_ce: bad class count");
     if (rows == 0) return WB_OK;
     WbProfileScope ps(b, "softmax_ce");
     float* rl = row_loss;
@@ -198,13 +201,19 @@ extern "C" int wb_softmax_ce(WbBackend* b, const float* logits, const int64_t* l
     }
     int64_t threads = rows * 32;
     softmax_ce_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        logits, labels, rows, static_cast<int>(cols), probs, dlogits, rl, static_cast<float>(upstream * (1.0 / static_cast<double>(rows))));
+        logits, labels, rows, static_cast<int>(cols), probs, dlogits, static_cast<int>(dz_pitch), rl,
+        static_cast<float>(upstream * (1.0 / static_cast<double>(rows))));
     WB_LAUNCH_OK(b);
     if (mean_loss) {
         mean_kernel<<<1, THREADS, 0, b->stream>>>(rl, rows, mean_loss);
         WB_LAUNCH_OK(b);
     }
     return WB_OK;
+}
+
+extern "C" int wb_softmax_ce(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs,
+                             float* dlogits, float* row_loss, float* mean_loss, double upstream) {
+    return wb_softmax_ce_pitched(b, logits, labels, rows, cols, probs, dlogits, cols, row_loss, mean_loss, upstream);
 }
 
 extern "C" int wb_adam_step(WbBackend* b, float* theta, const float* grad, float* m, float* v, int64_t n, int64_t t, double lr,

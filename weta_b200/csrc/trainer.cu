@@ -20,6 +20,9 @@
 #include "common.h"
 #include "gemm.h"
 
+int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs, float* dlogits,
+                          int64_t dz_pitch, float* row_loss, float* mean_loss, double upstream);
+
 namespace {
 
 enum { L_CONV = 0, L_LINEAR = 1, L_DROPOUT = 2 };
@@ -59,7 +62,8 @@ struct WbTrainer {
     float *theta = nullptr, *grad = nullptr, *m = nullptr, *v = nullptr;
     float* x_in = nullptr;       // staged input  [B, in_elems]
     int64_t* y_in = nullptr;     // staged labels [B]
-    float* dlogits = nullptr;
+    float* dlogits = nullptr;    // [B, dl_pitch]: rows padded to a multiple of 4 floats for TMA
+    int64_t dl_pitch = 0;
     float* loss_dev = nullptr;
     float* loss_pinned = nullptr;
     float* gbuf[2] = {nullptr, nullptr};  // ping-pong gradient-of-activation buffers
@@ -175,10 +179,10 @@ int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, i
 }
 
 // dst[j] = sum_i src[i][j] over a dense [rows, cols] matrix (a bias gradient, crates/weta-autograd/src/ops.rs:46-58).
-int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, float* dst) {
+int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, int64_t pitch, float* dst) {
     WbView v{};
     v.data = const_cast<float*>(src); v.dtype = WB_F32; v.ndim = 2;
-    v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = cols; v.stride[1] = 1;
+    v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = pitch; v.stride[1] = 1;
     return wb_reduce_into(t->be, WB_SUM, &v, 0, dst);
 }
 
@@ -276,7 +280,8 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
     A(dev_alloc_t(t, t->n_params, &t->v));
     A(dev_alloc_t(t, batch * t->in_elems, &t->x_in));
     A(dev_alloc_t(t, batch, &t->y_in));
-    A(dev_alloc_t(t, batch * t->classes, &t->dlogits));
+    t->dl_pitch = (t->classes + 3) / 4 * 4;
+    A(dev_alloc_t(t, batch * t->dl_pitch, &t->dlogits));
     A(dev_alloc_t(t, 4, &t->loss_dev));
     int64_t max_act = batch * t->in_elems, max_dcols = 0;
     bool first_conv = true;
@@ -463,7 +468,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
         }
     }
     // ---- loss: cross-entropy, mean over the batch (crates/weta-autograd/src/ops.rs:499-519) ---
-    { OpTimer tm(t, nl, "softmax_ce"); WB_TRY(wb_softmax_ce(b, act, t->y_in, B, t->classes, nullptr, t->dlogits, nullptr, t->loss_dev, 1.0)); }
+    { OpTimer tm(t, nl, "softmax_ce"); WB_TRY(wb_softmax_ce_pitched(b, act, t->y_in, B, t->classes, nullptr, t->dlogits, t->dl_pitch, nullptr, t->loss_dev, 1.0)); }
     // ---- backward ---------------------------------------------------------------------------
     const float* g = t->dlogits;  // gradient w.r.t. the current layer's output
     int pp = 0;
@@ -473,17 +478,18 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
         const bool need_dx = i > 0;
         if (L.kind == L_LINEAR) {
             float* gz = const_cast<float*>(g);
+            const int64_t gld = (i == nl - 1) ? t->dl_pitch : L.out;  // row pitch of dZ (the logits' gradient is padded)
             if (L.relu && !L.relu_bwd_done) WB_TRY(relu_bwd_inplace(t, gz, L.out_act, B * L.out));
             // MatmulBw (ops.rs:821-827): dW = dZ^T X, db = sum over the batch, dX = dZ W
-            WbGemmOperand Az{gz, L.out, B, L.out, 0, true};
+            WbGemmOperand Az{gz, L.out, B, gld, 0, true};
             WbGemmOperand Bx{in_act, L.in, B, L.in, 0, true};
             tc::Epilogue epw{t->grad + L.off_w, L.in, 0, nullptr, nullptr, 0, 0};
             { OpTimer tm(t, i, "linear_wgrad_gemm"); WB_TRY(gemm(t, Az, Bx, 1, L.out, L.in, static_cast<int>(B), epw)); }
-            { OpTimer tm(t, i, "linear_bias_grad"); WB_TRY(column_sum(t, gz, B, L.out, t->grad + L.off_b)); }
+            { OpTimer tm(t, i, "linear_bias_grad"); WB_TRY(column_sum(t, gz, B, L.out, gld, t->grad + L.off_b)); }
             if (need_dx) {
                 float* dx = t->gbuf[pp];
                 pp ^= 1;
-                WbGemmOperand Ad{gz, B, L.out, L.out, 0, false};
+                WbGemmOperand Ad{gz, B, L.out, gld, 0, false};
                 WbGemmOperand Bw{t->theta + L.off_w, L.in, L.out, L.in, 0, true};
                 tc::Epilogue epx{dx, L.in, 0, nullptr, nullptr, 0, 0};
                 { OpTimer tm(t, i, "linear_dgrad_gemm"); WB_TRY(gemm(t, Ad, Bw, 1, static_cast<int>(B), L.in, L.out, epx)); }
@@ -529,7 +535,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 t->matmul_mode = WB_MM_FP32;
                 s = gemm(t, Ad, Bt, B, L.cout, static_cast<int>(ck), static_cast<int>(hw), ept);
                 t->matmul_mode = saved;
-                if (s == WB_OK) s = column_sum(t, static_cast<float*>(tmp), B, L.cout * ck, t->grad + L.off_w);
+                if (s == WB_OK) s = column_sum(t, static_cast<float*>(tmp), B, L.cout * ck, L.cout * ck, t->grad + L.off_w);
                 wb_arena_free(b, tmp, klass);
             }
             delete wt;
