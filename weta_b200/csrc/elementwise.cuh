@@ -124,76 +124,81 @@ __global__ void __launch_bounds__(THREADS) ew_strided(TO* __restrict__ out, cons
 
 // ---- tile ---------------------------------------------------------------------------------------
 // Output viewed as [..outer.., P, ..mid.., L] (collapsed dims).  `pd` is the dim along which the
-// transposed operand(s) have unit stride; L is the output's inner dim.  A block owns a 32(P) x
-// 32(L) tile for one setting of all other dims.  tmode[o]: 1 = operand o is read along P through
-// shared memory, 0 = it is read along L directly.
-constexpr int TILE = 32;
-constexpr int TILE_ROWS = 8;
+// transposed operand(s) have unit stride; L is the output's inner dim.  A block owns a TILE(P) x
+// TILE(L) tile for one setting of all other dims: transposed operands are read with threads running
+// along P (coalesced), parked in shared memory, and consumed with threads running along L, so the
+// output (and any operand that is already L-contiguous) is written/read coalesced as well.
+// tmode[o]: 1 = operand o is read along P through shared memory, 0 = it is read along L directly.
+constexpr int TILE = 64;
+constexpr int TILE_THREADS = 256;
+constexpr int TILE_ROWS = TILE_THREADS / TILE;  // 4 rows of the tile per pass, 16 passes
 
 template <class TI, class TO, int NOPS, class F>
-__global__ void __launch_bounds__(TILE * TILE_ROWS) ew_tile(TO* __restrict__ out, const TI* __restrict__ a,
-                                                            const TI* __restrict__ b, Plan p, int pd, int tmode_a,
-                                                            int tmode_b, int64_t tiles_p, int64_t tiles_l, F f) {
-    __shared__ TI sm[NOPS][TILE][TILE + 1];
+__global__ void __launch_bounds__(TILE_THREADS) ew_tile(TO* __restrict__ out, const TI* __restrict__ a, const TI* __restrict__ b, Plan p,
+                                                        int pd, int tmode_a, int tmode_b, uint32_t tiles_p, uint32_t tiles_l, F f) {
+    extern __shared__ __align__(16) unsigned char tile_raw[];
+    TI(*sm)[TILE][TILE + 1] = reinterpret_cast<TI(*)[TILE][TILE + 1]>(tile_raw);
     const int L = p.nd - 1;
-    int64_t bid = blockIdx.x;
-    int64_t tl = bid % tiles_l;
+    uint32_t bid = blockIdx.x;
+    const uint32_t tl = bid % tiles_l;
     bid /= tiles_l;
-    int64_t tp = bid % tiles_p;
+    const uint32_t tp = bid % tiles_p;
     bid /= tiles_p;
-    // Remaining dims (all but pd and L), innermost first.
-    int64_t oa = p.off[0], ob = p.off[1], oo = 0;
-    int64_t ostride[WB_MAX_DIMS];
-    {
-        int64_t s = 1;
-        for (int d = p.nd - 1; d >= 0; --d) {
-            ostride[d] = s;
-            s *= p.size[d];
+    // Remaining dims (all but pd and L), innermost first; `s` is the output stride of dim d.
+    int64_t oa = p.off[0], ob = p.off[1], oo = 0, s = p.size[L], ostride_p = 0;
+    for (int d = L - 1; d >= 0; --d) {
+        const uint32_t sz = static_cast<uint32_t>(p.size[d]);
+        if (d == pd) {
+            ostride_p = s;
+        } else {
+            const uint32_t q = bid / sz, c = bid - q * sz;
+            bid = q;
+            oa += c * p.st[0][d];
+            if (NOPS > 1) ob += c * p.st[1][d];
+            oo += c * s;
         }
+        s *= sz;
     }
-    for (int d = p.nd - 2; d >= 0; --d) {
-        if (d == pd) continue;
-        int64_t c = bid % p.size[d];
-        bid /= p.size[d];
-        oa += c * p.st[0][d];
-        if (NOPS > 1) ob += c * p.st[1][d];
-        oo += c * ostride[d];
-    }
-    const int64_t p0 = tp * TILE, l0 = tl * TILE;
+    const int64_t p0 = static_cast<int64_t>(tp) * TILE, l0 = static_cast<int64_t>(tl) * TILE;
     const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
     const int64_t szp = p.size[pd], szl = p.size[L];
+    const int64_t sap = p.st[0][pd], sal = p.st[0][L], sbp = p.st[1][pd], sbl = p.st[1][L];
     // Stage transposed operands: threads run along P (their unit-stride dim).
     if (tmode_a) {
-#pragma unroll
-        for (int j = 0; j < TILE; j += TILE_ROWS) {
-            int64_t pi = p0 + tx, li = l0 + ty + j;
-            if (pi < szp && li < szl) sm[0][ty + j][tx] = a[oa + pi * p.st[0][pd] + li * p.st[0][L]];
+        const int64_t pi = p0 + tx;
+#pragma unroll 4
+        for (int j = ty; j < TILE; j += TILE_ROWS) {
+            const int64_t li = l0 + j;
+            if (pi < szp && li < szl) sm[0][j][tx] = a[oa + pi * sap + li * sal];
         }
     }
     if constexpr (NOPS > 1) {
         if (tmode_b) {
-#pragma unroll
-            for (int j = 0; j < TILE; j += TILE_ROWS) {
-                int64_t pi = p0 + tx, li = l0 + ty + j;
-                if (pi < szp && li < szl) sm[1][ty + j][tx] = b[ob + pi * p.st[1][pd] + li * p.st[1][L]];
+            const int64_t pi = p0 + tx;
+#pragma unroll 4
+            for (int j = ty; j < TILE; j += TILE_ROWS) {
+                const int64_t li = l0 + j;
+                if (pi < szp && li < szl) sm[1][j][tx] = b[ob + pi * sbp + li * sbl];
             }
         }
     }
     __syncthreads();
     // Compute: threads run along L (the output's unit-stride dim).
-#pragma unroll
-    for (int j = 0; j < TILE; j += TILE_ROWS) {
-        int64_t pi = p0 + ty + j, li = l0 + tx;
-        if (pi < szp && li < szl) {
-            TI x = tmode_a ? sm[0][tx][ty + j] : a[oa + pi * p.st[0][pd] + li * p.st[0][L]];
+    const int64_t li = l0 + tx;
+    if (li < szl) {
+#pragma unroll 4
+        for (int j = ty; j < TILE; j += TILE_ROWS) {
+            const int64_t pi = p0 + j;
+            if (pi >= szp) break;
+            TI x = tmode_a ? sm[0][tx][j] : a[oa + pi * sap + li * sal];
             TO r;
             if constexpr (NOPS > 1) {
-                TI y = tmode_b ? sm[1][tx][ty + j] : b[ob + pi * p.st[1][pd] + li * p.st[1][L]];
+                TI y = tmode_b ? sm[1][tx][j] : b[ob + pi * sbp + li * sbl];
                 r = f(x, y);
             } else {
                 r = f(x);
             }
-            out[oo + pi * ostride[pd] + li] = r;
+            out[oo + pi * ostride_p + li] = r;
         }
     }
 }
@@ -260,8 +265,17 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
         int64_t rest = wp.n / (wp.size[pd] * wp.size[L]);
         int64_t blocks = tiles_p * tiles_l * rest;
         if (blocks < (int64_t(1) << 31)) {
-            ew_tile<TI, TO, NOPS, F><<<static_cast<unsigned>(blocks), TILE * TILE_ROWS, 0, st>>>(
-                out, a, b, p, pd, tmode[0], tmode[1], tiles_p, tiles_l, f);
+            constexpr size_t tile_smem = sizeof(TI) * NOPS * TILE * (TILE + 1);
+            auto kern = ew_tile<TI, TO, NOPS, F>;
+            if (tile_smem > 48 * 1024) {
+                static bool attr_done = false;  // one flag per instantiation
+                if (!attr_done) {
+                    WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem)));
+                    attr_done = true;
+                }
+            }
+            kern<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
+                                                                                 static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), f);
             WB_LAUNCH_OK(be);
             return WB_OK;
         }

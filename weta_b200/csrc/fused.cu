@@ -22,18 +22,25 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t seed, uint64_t i) {
     return z ^ (z >> 31);
 }
 
-// rand_f32 element i for Uniform{0,1}: (f32)((z >> 11) * 2^-53), see random.cu.
-__device__ __forceinline__ float uniform01(uint64_t seed, uint64_t i) {
-    return __ull2float_rn(splitmix64(seed, i) >> 11) * 1.1102230246251565e-16f;
+// The 53-bit integer k behind rand_f32 element i: u = (f32)(k * 2^-53) (crates/weta-core/src/ops.rs:172-174).
+// `u > f32(p)` is monotone in k, so the host turns the float comparison into `k >= kmin` once
+// (dropout_threshold below) and the kernels never convert k to floating point: same mask, bit for bit.
+__device__ __forceinline__ uint64_t mix_tail(uint64_t z) {
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return (z ^ (z >> 31)) >> 11;
 }
 
+constexpr uint64_t GOLDEN = 0x9E3779B97F4A7C15ull;
+
 // ---- dropout ------------------------------------------------------------------------------------
-// mask = ((u > f32(p)) ? 1 : 0) * f32(1/(1-p)) + 0;  y = x * mask.  With relu_src != null the
-// incoming value is additionally multiplied by step(relu_src) (ReLU backward folded in).
+// mask = ((u > f32(p)) ? 1 : 0) * f32(1/(1-p)) + 0 = (k >= kmin) ? scale : 0;  y = x * mask.  With
+// relu_src != null the incoming value is additionally multiplied by step(relu_src) (ReLU backward folded in).
 __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ relu_src,
-                                                           int64_t n, float p, float scale, uint64_t seed) {
+                                                           int64_t n, uint64_t kmin, float scale, uint64_t seed) {
     int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
+    uint64_t z = seed + (static_cast<uint64_t>(i) + 1) * GOLDEN;
     if (i + 4 <= n) {
         float4 v = *reinterpret_cast<const float4*>(x + i);
         float in[4] = {v.x, v.y, v.z, v.w}, out[4];
@@ -44,23 +51,37 @@ __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y,
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            float mask = p > 0.f ? (uniform01(seed, static_cast<uint64_t>(i + k)) > p ? 1.f : 0.f) * scale + 0.f : 1.f;
+            float mask = mix_tail(z) >= kmin ? scale : 0.f;
+            z += GOLDEN;
             float g = in[k] * mask;
             out[k] = relu_src ? g * (rs[k] > 0.f ? 1.f : 0.f) : g;
         }
         *reinterpret_cast<float4*>(y + i) = make_float4(out[0], out[1], out[2], out[3]);
     } else {
         for (int64_t j = i; j < n; ++j) {
-            float mask = p > 0.f ? (uniform01(seed, static_cast<uint64_t>(j)) > p ? 1.f : 0.f) * scale + 0.f : 1.f;
+            float mask = mix_tail(z) >= kmin ? scale : 0.f;
+            z += GOLDEN;
             float g = x[j] * mask;
             y[j] = relu_src ? g * (relu_src[j] > 0.f ? 1.f : 0.f) : g;
         }
     }
 }
 
-__global__ void __launch_bounds__(THREADS) dropout_mask_kernel(float* __restrict__ m, int64_t n, float p, float scale, uint64_t seed) {
-    int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
-    if (i < n) m[i] = (uniform01(seed, static_cast<uint64_t>(i)) > p ? 1.f : 0.f) * scale + 0.f;
+__global__ void __launch_bounds__(THREADS) dropout_mask_kernel(float* __restrict__ m, int64_t n, uint64_t kmin, float scale, uint64_t seed) {
+    int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
+    if (i >= n) return;
+    uint64_t z = seed + (static_cast<uint64_t>(i) + 1) * GOLDEN;
+    float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[k] = mix_tail(z) >= kmin ? scale : 0.f;
+        z += GOLDEN;
+    }
+    if (i + 4 <= n && (reinterpret_cast<uintptr_t>(m) & 15) == 0) {
+        *reinterpret_cast<float4*>(m + i) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        for (int k = 0; k < 4 && i + k < n; ++k) m[i + k] = v[k];
+    }
 }
 
 // ---- softmax cross-entropy ----------------------------------------------------------------------
@@ -90,6 +111,47 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __rest
     }
     if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;  // padding columns of a pitched gradient
     if (lane == 0 && row_loss) row_loss[row] = (y >= 0 && y < cols) ? -(zr[y] - lse) : 0.f;
+}
+
+// Same, for rows of at most 32*PER_LANE classes: the row lives in registers, so the logits are read once.
+template <int PER_LANE>
+__global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+                                                                  int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
+                                                                  float* __restrict__ row_loss, float gscale) {
+    int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* zr = z + row * cols;
+    float v[PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int c = lane + 32 * k;
+        v[k] = c < cols ? zr[c] : -INFINITY;
+        mx = fmaxf(mx, v[k]);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k)
+        if (lane + 32 * k < cols) s += expf(v[k] - mx);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    const float lse = logf(s) + mx;
+    const int64_t y = labels[row];
+#pragma unroll
+    for (int k = 0; k < PER_LANE; ++k) {
+        int c = lane + 32 * k;
+        if (c < cols) {
+            float p = expf(v[k] - lse);
+            if (probs) probs[row * cols + c] = p;
+            if (dz) dz[row * dz_pitch + c] = (p - (c == y ? 1.f : 0.f)) * gscale;
+            if (row_loss && c == y) row_loss[row] = -(v[k] - lse);
+        }
+    }
+    if (row_loss && lane == 0 && (y < 0 || y >= cols)) row_loss[row] = 0.f;
+    if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;
 }
 
 // mean of row_loss in a fixed order (one block; rows is a batch size).
@@ -135,6 +197,21 @@ __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta
     v[i] = vn;
 }
 
+// Smallest 53-bit k whose uniform value (f32)((double)k * 2^-53) exceeds f32(p); 2^53 if none does.
+// p <= 0 keeps everything (the reference returns x unchanged for p = 0).
+uint64_t dropout_threshold(double p) {
+    if (p <= 0.0) return 0;
+    const float pf = static_cast<float>(p);
+    uint64_t lo = 0, hi = 1ull << 53;  // invariant: u(lo - 1) <= pf (or lo == 0), u(hi) > pf (or hi == 2^53)
+    while (lo < hi) {
+        uint64_t mid = lo + (hi - lo) / 2;
+        float u = static_cast<float>(static_cast<double>(mid) * (1.0 / 9007199254740992.0));
+        if (u > pf) hi = mid;
+        else lo = mid + 1;
+    }
+    return lo;
+}
+
 double powi(double a, int n) {  // f64::powi (compiler-rt __powidf2)
     double r = 1.0;
     int b = n;
@@ -159,7 +236,7 @@ extern "C" int wb_dropout_fwd(WbBackend* b, const float* x, float* y, int64_t n,
     bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     WB_REQUIRE(aligned, WB_ERR_INVALID, "wb_dropout_fwd: buffers must be 16-byte aligned");
     dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        y, x, nullptr, n, static_cast<float>(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+        y, x, nullptr, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -170,7 +247,7 @@ extern "C" int wb_dropout_relu_bwd(WbBackend* b, const float* dy, const float* r
     WbProfileScope ps(b, "dropout_bwd");
     int64_t threads = (n + 3) / 4;
     dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        dx, dy, relu_out, n, static_cast<float>(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+        dx, dy, relu_out, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -179,8 +256,8 @@ extern "C" int wb_dropout_mask(WbBackend* b, float* mask, int64_t n, double p, u
     WB_REQUIRE(b && mask, WB_ERR_INVALID, "wb_dropout_mask: null pointer");
     if (n == 0) return WB_OK;
     WbProfileScope ps(b, "dropout_mask");
-    dropout_mask_kernel<<<static_cast<unsigned>((n + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        mask, n, static_cast<float>(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+    dropout_mask_kernel<<<static_cast<unsigned>(((n + 3) / 4 + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+        mask, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -200,9 +277,13 @@ int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labe
         rl = static_cast<float*>(s);
     }
     int64_t threads = rows * 32;
-    softmax_ce_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        logits, labels, rows, static_cast<int>(cols), probs, dlogits, static_cast<int>(dz_pitch), rl,
-        static_cast<float>(upstream * (1.0 / static_cast<double>(rows))));
+    const unsigned grid = static_cast<unsigned>((threads + THREADS - 1) / THREADS);
+    const float gscale = static_cast<float>(upstream * (1.0 / static_cast<double>(rows)));
+    const int ic = static_cast<int>(cols), ip = static_cast<int>(dz_pitch);
+    if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    else if (cols <= 128) softmax_ce_reg_kernel<4><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    else if (cols <= 1024) softmax_ce_reg_kernel<32><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    else softmax_ce_kernel<<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
     WB_LAUNCH_OK(b);
     if (mean_loss) {
         mean_kernel<<<1, THREADS, 0, b->stream>>>(rl, rows, mean_loss);

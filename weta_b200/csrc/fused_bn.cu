@@ -134,18 +134,31 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __re
     {
         const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
         const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
-        const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
         const int64_t stride = static_cast<int64_t>(c_total) * hw;
         const float* xslab = x + (n0 * c_total + c) * hw;
         const float* gslab = dy + (n0 * c_total + c) * hw;
         float a1 = 0.f, a2 = 0.f;
         int flushed = 0;
-        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
-            const uint32_t n = j / uhw, i = j - n * uhw;
-            float g = gslab[n * stride + i];
-            a1 += g;
-            a2 += g * ((xslab[n * stride + i] - m) * r);
-            if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+        if ((hw & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0) {
+            const uint32_t q = static_cast<uint32_t>(hw >> 2), items = static_cast<uint32_t>(n1 - n0) * q;
+#pragma unroll 2
+            for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+                const uint32_t n = j / q, i = (j - n * q) * 4;
+                const float4 g = *reinterpret_cast<const float4*>(gslab + n * stride + i);
+                const float4 v = *reinterpret_cast<const float4*>(xslab + n * stride + i);
+                a1 += (g.x + g.y) + (g.z + g.w);
+                a2 += g.x * ((v.x - m) * r) + g.y * ((v.y - m) * r) + g.z * ((v.z - m) * r) + g.w * ((v.w - m) * r);
+                if (++flushed == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+            }
+        } else {
+            const uint32_t uhw = static_cast<uint32_t>(hw), items = static_cast<uint32_t>(n1 - n0) * uhw;
+            for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+                const uint32_t n = j / uhw, i = j - n * uhw;
+                float g = gslab[n * stride + i];
+                a1 += g;
+                a2 += g * ((xslab[n * stride + i] - m) * r);
+                if (++flushed == 256) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+            }
         }
         s1 += a1;
         s2 += a2;
@@ -190,6 +203,19 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_dx_kernel(float* __restrict__ 
     const float* xs = x + plane * hw;
     const float* gs = dy + plane * hw;
     float* dst = dx + plane * hw;
+    if ((hw & 3) == 0 && ((reinterpret_cast<uintptr_t>(xs) | reinterpret_cast<uintptr_t>(gs) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+        for (int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4; i < hw; i += static_cast<int64_t>(gridDim.x) * THREADS * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xs + i);
+            const float4 gg = *reinterpret_cast<const float4*>(gs + i);
+            float4 o;
+            o.x = gr * (gg.x - k1 - ((v.x - m) * r) * k2);
+            o.y = gr * (gg.y - k1 - ((v.y - m) * r) * k2);
+            o.z = gr * (gg.z - k1 - ((v.z - m) * r) * k2);
+            o.w = gr * (gg.w - k1 - ((v.w - m) * r) * k2);
+            *reinterpret_cast<float4*>(dst + i) = o;
+        }
+        return;
+    }
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x; i < hw; i += static_cast<int64_t>(gridDim.x) * THREADS) {
         float xh = (xs[i] - m) * r;
         dst[i] = gr * (gs[i] - k1 - xh * k2);
@@ -511,7 +537,7 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
     WB_LAUNCH_OK(b);
     bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
-    unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw + THREADS - 1) / THREADS, 64)));
+    unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw / 4 + THREADS - 1) / THREADS, 64)));
     for (int64_t p0 = 0; p0 < n * c; p0 += 65535 / c * c) {
         int64_t cnt = std::min<int64_t>(65535 / c * c, n * c - p0);
         bn_bwd_dx_kernel<<<dim3(gx, static_cast<unsigned>(cnt)), THREADS, 0, b->stream>>>(dx + p0 * hw, x + p0 * hw, dy + p0 * hw, save_mean, save_rstd,
