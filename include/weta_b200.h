@@ -205,6 +205,15 @@ int wb_bn2d_stats(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw
                   float* rstd, float* running_mean, float* running_var);
 int wb_bn2d_apply(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* mean, const float* rstd,
                   const float* gamma, const float* beta, int relu, float* y);
+/* No counterpart in the reference.  wb_bn2d_stats for callers that must not allocate device memory when
+ * they call (inside an allocator hook or memory-pool callback, in a loop that has frozen its memory map,
+ * or with the device's memory fully budgeted elsewhere): it takes no backend handle, runs on the current
+ * device and the given cudaStream_t, and keeps its partial sums in a fixed 512 KiB array inside the library
+ * instead of arena scratch.  Limit: c <= 32768 channels (else WB_ERR_INVALID).  The first call on a device
+ * resolves the array's address, so issue it before any stream capture.  Calls share the array: calls that
+ * overlap on the GPU race; keep them on one stream or order them yourself. */
+int wb_bn2d_stats_noalloc(void* cuda_stream, const float* x, int64_t n, int64_t c, int64_t hw, double eps, double momentum,
+                          float* mean, float* rstd, float* running_mean, float* running_var);
 int wb_bn2d_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* gamma, const float* beta,
                 float* running_mean, float* running_var, double momentum, double eps, float* y, float* save_mean, float* save_rstd);
 /* The gradient autograd derives through that chain: dx, dgamma = sum(dy*xhat), dbeta = sum(dy). */

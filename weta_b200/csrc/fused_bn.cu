@@ -502,6 +502,71 @@ extern "C" int wb_bn2d_stats(WbBackend* b, const float* x, int64_t n, int64_t c,
     return WB_OK;
 }
 
+// ---- batch statistics without any allocation ----------------------------------------------------
+// Some hosts of this library may not allocate device memory at the time they need batch statistics:
+// code running inside a framework's memory-pool callback or an allocator hook, a real-time loop that
+// has frozen its memory map, or a process whose device memory is fully budgeted to another component.
+// For them the per-(channel, slab) partial sums live in this fixed array, which every GPU that loads
+// the library carries from load to exit (WB_NOALLOC_SCRATCH_DOUBLES * 8 bytes = 512 KiB).
+#define WB_NOALLOC_SCRATCH_DOUBLES 65536
+static __device__ __align__(256) double g_noalloc_scratch[WB_NOALLOC_SCRATCH_DOUBLES];
+
+namespace {
+// In host code `g_noalloc_scratch` is only a stand-in for the device array; a kernel must be given the
+// address cudaGetSymbolAddress reports for the device that is current, looked up once per device.
+constexpr int MAX_DEVICES = 64;
+double* g_noalloc_ptr[MAX_DEVICES] = {};
+}  // namespace
+
+// Same result as wb_bn2d_stats (batch mean, rstd = 1/sqrt(biased var + eps), running statistics), on the
+// CURRENT device and the given stream, using only the fixed scratch array above: no cudaMalloc, no
+// cudaFree, no backend handle.  It fits c channels when 2*c <= WB_NOALLOC_SCRATCH_DOUBLES (c <= 32768);
+// larger inputs are rejected with WB_ERR_INVALID.  The first call on each device looks up the array's
+// address (cudaGetSymbolAddress); make that first call before starting any stream capture.  All calls on a
+// device share the one array: every slot a call reads is written by that call first, so nothing needs
+// clearing, but two calls that overlap on the GPU (different streams, or different host threads on
+// different streams) would overwrite each other's partial sums; run them on one stream or order them.
+extern "C" int wb_bn2d_stats_noalloc(void* cuda_stream, const float* x, int64_t n, int64_t c, int64_t hw, double eps, double momentum,
+                                     float* mean, float* rstd, float* running_mean, float* running_var) {
+    WB_REQUIRE(x && mean && rstd, WB_ERR_INVALID, "wb_bn2d_stats_noalloc: null pointer");
+    WB_REQUIRE(n > 0 && c > 0 && hw > 0, WB_ERR_INVALID, "wb_bn2d_stats_noalloc: empty input");
+    WB_REQUIRE(2 * c <= WB_NOALLOC_SCRATCH_DOUBLES, WB_ERR_INVALID,
+               "wb_bn2d_stats_noalloc: %lld channels need %lld scratch doubles, the fixed array holds %d (at most %d channels)", (long long)c,
+               (long long)(2 * c), WB_NOALLOC_SCRATCH_DOUBLES, WB_NOALLOC_SCRATCH_DOUBLES / 2);
+    int dev = -1;
+    WB_CHECK_CUDA(cudaGetDevice(&dev));
+    WB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, WB_ERR_UNSUPPORTED, "wb_bn2d_stats_noalloc: device ordinal %d out of range", dev);
+    if (!g_noalloc_ptr[dev]) {
+        double* p = nullptr;
+        WB_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch));
+        WB_REQUIRE(p != nullptr, WB_ERR_CUDA, "wb_bn2d_stats_noalloc: the scratch array has no device address");
+        g_noalloc_ptr[dev] = p;
+    }
+    double* scratch = g_noalloc_ptr[dev];
+    int sm_count = 0;
+    WB_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
+    // As many image slabs per channel as fill the GPU once, capped by what the array holds and by n;
+    // slabs are sized so that none is empty and the kernel's 32-bit item counter cannot overflow.
+    int64_t splits = std::max<int64_t>(1, 8LL * sm_count / c);
+    splits = std::min<int64_t>(splits, WB_NOALLOC_SCRATCH_DOUBLES / (2 * c));
+    const int64_t need = (n * hw + (int64_t(1) << 30) - 1) / (int64_t(1) << 30);
+    splits = std::min<int64_t>(std::max(splits, need), n);
+    WB_REQUIRE(2 * c * splits <= WB_NOALLOC_SCRATCH_DOUBLES, WB_ERR_INVALID,
+               "wb_bn2d_stats_noalloc: input of %lld x %lld x %lld elements does not fit the fixed scratch array", (long long)n, (long long)c,
+               (long long)hw);
+    const int64_t per = (n + splits - 1) / splits;
+    splits = (n + per - 1) / per;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    bn_stats_kernel<<<dim3(static_cast<unsigned>(c), static_cast<unsigned>(splits)), THREADS, 0, stream>>>(x, n, static_cast<int>(c), hw, scratch);
+    WB_CHECK_CUDA(cudaPeekAtLastError());
+    bn_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, stream>>>(scratch, static_cast<int>(splits), x, static_cast<int>(c), hw, n * hw,
+                                                                                 static_cast<float>(eps), static_cast<float>(momentum),
+                                                                                 static_cast<float>(1.0 - momentum), mean, rstd, running_mean,
+                                                                                 running_var);
+    WB_CHECK_CUDA(cudaPeekAtLastError());
+    return WB_OK;
+}
+
 extern "C" int wb_bn2d_apply(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* mean, const float* rstd,
                              const float* gamma, const float* beta, int relu, float* y) {
     WB_REQUIRE(b && x && y && mean && rstd, WB_ERR_INVALID, "wb_bn2d_apply: null pointer");
