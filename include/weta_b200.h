@@ -229,6 +229,17 @@ int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int6
 int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                         const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                         float* dgamma, float* dbeta, float* dbias_conv);
+/* 3x3, stride 1, padding 1 convolution over contiguous NCHW f32 tensors as an implicit GEMM on the
+ * tensor cores (TF32 operands, f32 accumulation; no im2col matrix in memory).  Forward replaces the
+ * chain F::conv2d_ext builds (crates/weta-nn/src/functional.rs:84-106: im2col -> matmul -> add bias,
+ * bias may be NULL); backward replaces MatmulBw + Im2ColBw + the sum over the batch
+ * (crates/weta-autograd/src/ops.rs:821-827, 865-868): dweight [o,c,3,3] and dx [n,c,h,w], either may be
+ * NULL.  Shape rules: w % 4 == 0, c % 128 == 0, o % 32 == 0; WB_ERR_UNSUPPORTED otherwise (use wb_im2col +
+ * wb_matmul).  Scratch (two shifted copies of the image operand, the reordered weight) comes from the arena. */
+int wb_conv3x3_fwd(WbBackend* b, const float* x, const float* weight, const float* bias, int64_t n, int64_t c, int64_t h, int64_t w,
+                   int64_t o, float* y);
+int wb_conv3x3_bwd(WbBackend* b, const float* x, const float* weight, const float* dy, int64_t n, int64_t c, int64_t h, int64_t w,
+                   int64_t o, float* dx, float* dweight);
 /* Adam::step / AdamW for one flat parameter range at step t >= 1 (crates/weta-optim/src/lib.rs:210-239,
  * 276-283), every f32 rounding of the 13-call chain kept.  grad_scale multiplies the gradient first
  * (1/world after a summing all-reduce); 1.0 leaves the chain untouched. */

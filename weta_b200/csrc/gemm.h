@@ -18,4 +18,17 @@ struct WbGemmOperand {
 int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int mode,
                int force_splits, int64_t span_batch);
 
+// Implicit-GEMM 3x3 convolution pieces (forward / input gradient: mode 1, weight gradient: mode 2); see gemm_tcgen05.cu.
+int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const img[3], int64_t batch, int64_t ch, int64_t h, int64_t w, int m,
+                    tc::Epilogue ep);
+
+// Implicit 3x3 convolution built on wb_tc_conv_gemm (conv_implicit.cu).
+struct WbConv3 { int64_t n, c, h, w, o; };
+bool wb_conv3_eligible(const WbConv3& g);
+int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, float* left, float* right);
+int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n);
+int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y);
+int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float* const x3[3], float* dwr, float* dweight);
+int wb_conv3_dgrad(WbBackend* b, const WbConv3& g, const float* const dy3[3], const float* wt, float* dx);
+
 int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);

@@ -143,6 +143,75 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
     return WB_OK;
 }
 
+// Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
+// the persistent kernel, split-K finish.  `args` arrives with its tensor maps, k_blocks and mode fields set.
+int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool amn, bool bmn,
+              const tc::Epilogue& ep, int force_splits) {
+    args.m = m;
+    args.n = n;
+    args.error_flag = st->error_flag;
+    const int tiles_m = (m + tc::BM - 1) / tc::BM, tiles_n = (n + BN - 1) / BN;
+    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
+    int splits = 1;
+    if (force_splits > 0) splits = force_splits;
+    else if (tiles * 2 <= be->sm_count && args.k_blocks >= 16) {
+        splits = static_cast<int>(std::min<int64_t>(be->sm_count / tiles, args.k_blocks / 8));
+    }
+    splits = std::max(1, std::min(splits, args.k_blocks));
+    // Make every split non-empty.
+    int per = (args.k_blocks + splits - 1) / splits;
+    splits = (args.k_blocks + per - 1) / per;
+    args.splits = splits;
+    int status = WB_OK;
+    void* part = nullptr;
+    size_t kp = 0;
+    if (splits > 1) {
+        const int64_t per_split = grid_batch * static_cast<int64_t>(m) * n;
+        status = wb_arena_alloc(be, static_cast<size_t>(per_split) * splits * sizeof(float), &part, &kp);
+        if (status == WB_OK) {
+            args.ep = tc::Epilogue{static_cast<float*>(part), n, static_cast<int64_t>(m) * n, nullptr, nullptr, 0, 0};
+            args.split_stride_d = per_split;
+        }
+    } else {
+        args.ep = ep;
+        args.split_stride_d = 0;
+    }
+    if (status == WB_OK) {
+        args.tiles_m = tiles_m;
+        args.tiles_n = tiles_n;
+        const int64_t total_tiles = tiles * splits;
+        if (total_tiles >= (int64_t(1) << 31)) {
+            wb_set_error("gemm: too many tiles");
+            status = WB_ERR_UNSUPPORTED;
+        }
+        args.total_tiles = static_cast<int>(total_tiles);
+        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, be->sm_count)));
+        // Shared memory: 4 x 48 KB ring (BN = 256) or 5 x 32 KB (BN = 128) + 18 KB epilogue staging; one persistent CTA per SM.
+        if (status != WB_OK) {
+        } else if (BN == 256) {
+            if (!amn && !bmn) status = launch_tc<256, 4, false, false>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<256, 4, false, true>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<256, 4, true, false>(be, st, args, grid);
+            else status = launch_tc<256, 4, true, true>(be, st, args, grid);
+        } else {
+            if (!amn && !bmn) status = launch_tc<128, 5, false, false>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<128, 5, false, true>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<128, 5, true, false>(be, st, args, grid);
+            else status = launch_tc<128, 5, true, true>(be, st, args, grid);
+        }
+    }
+    if (status == WB_OK && splits > 1) {
+        const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
+        splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
+                                                                                        total, m, n, ep);
+        cudaError_t e = cudaPeekAtLastError();
+        if (e != cudaSuccess) { wb_set_error("split-K reduce launch failed: %s", cudaGetErrorString(e)); status = WB_ERR_CUDA; }
+        else be->launches++;
+    }
+    if (part) wb_arena_free(be, part, kp);
+    return status;
+}
+
 }  // namespace
 
 // Runs D = A x B (+ epilogue) on the tensor cores.  mode: WB_MM_TF32 or WB_MM_TF32X3.
@@ -198,8 +267,6 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         WB_TRY(make_map(st, A, batch, tc::BM, &args.seg[0].a));
         WB_TRY(make_map(st, B, batch, BN, &args.seg[0].b));
     }
-    args.m = m;
-    args.n = n;
     args.k_blocks = (k + tc::BK - 1) / tc::BK;
     args.kpb = 0;
     if (span_batch > 0) {
@@ -209,66 +276,63 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     }
     args.batched_a = A.batch_stride != 0;
     args.batched_b = B.batch_stride != 0;
-    args.error_flag = st->error_flag;
-    const int tiles_m = (m + tc::BM - 1) / tc::BM, tiles_n = (n + BN - 1) / BN;
-    const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
-    int splits = 1;
-    if (force_splits > 0) splits = force_splits;
-    else if (tiles * 2 <= be->sm_count && args.k_blocks >= 16) {
-        splits = static_cast<int>(std::min<int64_t>(be->sm_count / tiles, args.k_blocks / 8));
-    }
-    splits = std::max(1, std::min(splits, args.k_blocks));
-    // Make every split non-empty.
-    int per = (args.k_blocks + splits - 1) / splits;
-    splits = (args.k_blocks + per - 1) / per;
-    args.splits = splits;
-    int status = WB_OK;
-    void* part = nullptr;
-    size_t kp = 0;
-    if (splits > 1) {
-        const int64_t per_split = grid_batch * static_cast<int64_t>(m) * n;
-        status = wb_arena_alloc(be, static_cast<size_t>(per_split) * splits * sizeof(float), &part, &kp);
-        if (status == WB_OK) {
-            args.ep = tc::Epilogue{static_cast<float*>(part), n, static_cast<int64_t>(m) * n, nullptr, nullptr, 0, 0};
-            args.split_stride_d = per_split;
-        }
-    } else {
-        args.ep = ep;
-        args.split_stride_d = 0;
-    }
-    if (status == WB_OK) {
-        args.tiles_m = tiles_m;
-        args.tiles_n = tiles_n;
-        const int64_t total_tiles = tiles * splits;
-        WB_REQUIRE(total_tiles < (int64_t(1) << 31), WB_ERR_UNSUPPORTED, "gemm: too many tiles");
-        args.total_tiles = static_cast<int>(total_tiles);
-        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, be->sm_count)));
-        const bool amn = A.mn_major, bmn = B.mn_major;
-        // Shared memory: 4 x 48 KB ring (BN = 256) or 5 x 32 KB (BN = 128) + 18 KB epilogue staging; one persistent CTA per SM.
-        if (BN == 256) {
-            if (!amn && !bmn) status = launch_tc<256, 4, false, false>(be, st, args, grid);
-            else if (!amn && bmn) status = launch_tc<256, 4, false, true>(be, st, args, grid);
-            else if (amn && !bmn) status = launch_tc<256, 4, true, false>(be, st, args, grid);
-            else status = launch_tc<256, 4, true, true>(be, st, args, grid);
-        } else {
-            if (!amn && !bmn) status = launch_tc<128, 5, false, false>(be, st, args, grid);
-            else if (!amn && bmn) status = launch_tc<128, 5, false, true>(be, st, args, grid);
-            else if (amn && !bmn) status = launch_tc<128, 5, true, false>(be, st, args, grid);
-            else status = launch_tc<128, 5, true, true>(be, st, args, grid);
-        }
-    }
-    if (status == WB_OK && splits > 1) {
-        const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
-        splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
-                                                                                        total, m, n, ep);
-        cudaError_t e = cudaPeekAtLastError();
-        if (e != cudaSuccess) { wb_set_error("split-K reduce launch failed: %s", cudaGetErrorString(e)); status = WB_ERR_CUDA; }
-        else be->launches++;
-    }
-    if (part) wb_arena_free(be, part, kp);
+    int status = run_tiles(be, st, args, m, n, grid_batch, BN, A.mn_major, B.mn_major, ep, force_splits);
     if (hi_a) wb_arena_free(be, hi_a, ka);
     if (hi_b) wb_arena_free(be, hi_b, kb);
     return status;
+}
+
+// Implicit-GEMM 3x3 / stride 1 / padding 1 convolution pieces over NCHW tensors (see tc::Args::conv_mode).
+// img[kx] is the image tensor [batch][ch][h][w] shifted horizontally by kx-1 with zeros shifted in
+// (img[kx][y][x] = image[y][x+kx-1]; img[1] is the tensor itself).
+//   mode 1: D[batch][m][h*w] = Wr[m][tap][ch] (x) windows(img) (+ epilogue).  Forward with Wr = weights as [O][tap][C];
+//           input gradient with img = dY and Wr = weights as [C][flipped tap][O].
+//   mode 2: D[tap][ch][m] = sum over images and pixels of window_tap(img)[ch][px] * a[img][m][px]  (the weight gradient, a = dY).
+// Requirements (else WB_ERR_UNSUPPORTED, no message): w and h*w multiples of 4, ch a multiple of 32 (mode 1)
+// or of 128 (mode 2), 16-byte aligned pointers.
+int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const img[3], int64_t batch, int64_t ch, int64_t h, int64_t w, int m,
+                    tc::Epilogue ep) {
+    const int64_t hw = h * w;
+    if (w % 4 != 0 || hw % 4 != 0 || hw >= (int64_t(1) << 30)) return WB_ERR_UNSUPPORTED;
+    if (mode == 1 ? ch % 32 != 0 : ch % 128 != 0) return WB_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(img[0]) & 15) || (reinterpret_cast<uintptr_t>(img[1]) & 15) ||
+        (reinterpret_cast<uintptr_t>(img[2]) & 15))
+        return WB_ERR_UNSUPPORTED;
+    GemmState* st = nullptr;
+    WB_TRY(get_state(be, &st));
+    tc::Args args{};
+    args.num_segments = 1;
+    args.conv_mode = mode;
+    args.conv_w = static_cast<int>(w);
+    if (mode == 1) {
+        const int BN = hw > 128 ? 256 : 128;
+        const int64_t k = 9 * ch;
+        WbGemmOperand A{a, m, k, k, 0, false};
+        WB_TRY(make_map(st, A, 1, tc::BM, &args.seg[0].a));
+        for (int kx = 0; kx < 3; ++kx) {
+            WbGemmOperand B{img[kx], hw, ch, hw, ch * hw, true};
+            WB_TRY(make_map(st, B, batch, BN, &args.seg[kx].b));
+        }
+        args.k_blocks = static_cast<int>(k / tc::BK);
+        args.conv_cb = static_cast<int>(ch / 32);
+        args.batched_a = 0;
+        args.batched_b = 1;
+        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, BN, false, true, ep, 1);
+    }
+    const int BN = m > 128 ? 256 : 128;
+    for (int kx = 0; kx < 3; ++kx) {
+        WbGemmOperand A{img[kx], ch, hw, hw, ch * hw, false};
+        WB_TRY(make_map(st, A, batch, tc::BM, &args.seg[kx].a));
+    }
+    WbGemmOperand B{a, m, hw, hw, static_cast<int64_t>(m) * hw, false};
+    WB_TRY(make_map(st, B, batch, BN, &args.seg[0].b));
+    args.kpb = static_cast<int>((hw + tc::BK - 1) / tc::BK);
+    WB_REQUIRE(batch * args.kpb < (int64_t(1) << 31), WB_ERR_UNSUPPORTED, "conv weight gradient: contraction too long");
+    args.k_blocks = static_cast<int>(batch * args.kpb);
+    args.conv_cb = static_cast<int>(ch / tc::BM);
+    args.batched_a = 1;
+    args.batched_b = 1;
+    return run_tiles(be, st, args, static_cast<int>(9 * ch), m, 1, BN, false, false, ep, 0);
 }
 
 // Reads the device-side error flag the GEMM kernels raise when a bounded wait runs out.

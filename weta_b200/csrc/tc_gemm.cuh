@@ -52,6 +52,15 @@ struct Args {
     int batched_a, batched_b;  // 0: operand shared by every batch (TMA coordinate 0)
     int kpb;                   // K blocks per image when the contraction spans the batch, else 0
     int tiles_m, tiles_n, total_tiles;  // tile list walked by the persistent CTAs
+    // Implicit-GEMM convolution (3x3, stride 1, padding 1, NCHW).  The B operand is not a matrix in memory
+    // but windows of an image tensor [n][c][h*w]: a run of pixels moved by (ky-1) rows is the same run at
+    // flattened offset (ky-1)*w, which TMA can start at when w is a multiple of 4; the horizontal move by
+    // kx-1 would misalign the box, so seg[kx].b maps a copy of the tensor already shifted by kx-1 columns.
+    //   conv_mode 1 (forward, input gradient): A = reordered weights [M][tap][c], K index = (tap, c);
+    //     B chunks are 32 pixels x 32 channels, N-major.
+    //   conv_mode 2 (weight gradient): M index = (tap, c): A is one box of BM channels x 32 pixels of the tap's
+    //     window (seg[kx].a maps the shifted copies), K-major; B = dY [o][pixels] per image; K index = (image, pixel block).
+    int conv_mode, conv_w, conv_cb;  // conv_cb: 32-channel blocks per tap (mode 1) / BM-channel blocks per tap (mode 2)
     Epilogue ep;
     int64_t split_stride_d;    // distance between split-K partial outputs
     int* error_flag;
@@ -238,17 +247,37 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                         const int kz = args.kpb > 0 ? kb / args.kpb : 0;
                         const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
                         const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
-                        if constexpr (A_MN) {
+                        if (args.conv_mode == 1) {
+                            // kb = tap * conv_cb + channel block; tap = ky*3 + kx.  The window of tap (ky, kx) over a run
+                            // of pixels is the same run, moved (ky-1) image rows, of the copy shifted by kx-1; positions
+                            // before the first / after the last pixel are zero-filled by TMA, which is the padding.
+                            const int tap = kb / args.conv_cb, cb = kb - tap * args.conv_cb;
+                            const int ky = tap / 3, kx = tap - ky * 3;
+                            tma_load_3d(&ss.a[s][0], ma, &ss.full[s], kb * BK, m0, 0);
+                            const CUtensorMap* mx = &args.seg[kx].b;
+                            const int x0 = n0 + (ky - 1) * args.conv_w;
 #pragma unroll
-                            for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
+                            for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mx, &ss.full[s], x0 + c * 32, cb * 32, batch);
+                        } else if (args.conv_mode == 2) {
+                            // M tile = tap * conv_cb + channel block of BM; K block = 32 pixels of image kz.
+                            const int mbi = m0 / BM;
+                            const int tap = mbi / args.conv_cb, cb = mbi - tap * args.conv_cb;
+                            const int ky = tap / 3, kx = tap - ky * 3;
+                            tma_load_3d(&ss.a[s][0], &args.seg[kx].a, &ss.full[s], k0 + (ky - 1) * args.conv_w, cb * BM, kz);
+                            tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, kz);
                         } else {
-                            tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
-                        }
-                        if constexpr (B_MN) {
+                            if constexpr (A_MN) {
 #pragma unroll
-                            for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
-                        } else {
-                            tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
+                                for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
+                            } else {
+                                tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
+                            }
+                            if constexpr (B_MN) {
+#pragma unroll
+                                for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
+                            } else {
+                                tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
+                            }
                         }
                     }
                 }

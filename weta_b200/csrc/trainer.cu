@@ -14,6 +14,7 @@
 // while earlier layers are still being differentiated.
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -46,6 +47,11 @@ struct Layer {
     float* cols = nullptr;      // [B, cin*9, h*w]
     float* conv_out = nullptr;  // [B, cout, h, w]
     float* w_pad = nullptr;     // [cout, round_up(cin*9, 4)]: weight rows re-pitched to 16 bytes when cin*9 is not a multiple of 4
+    // Implicit-GEMM path (no cols / dcols): the input shifted one column right / left, the weight as
+    // [O][tap][C] and [C][flipped tap][O], and the weight gradient as the kernel writes it ([tap][C][O]).
+    bool implicit = false;
+    float* x_shift[2] = {nullptr, nullptr};
+    float *w_fwd = nullptr, *w_dgrad = nullptr, *dw_taps = nullptr;
     float* out_act = nullptr;   // layer output
     int64_t out_elems = 0;      // per-sample size of the layer output
     bool relu_bwd_done = false;
@@ -68,6 +74,7 @@ struct WbTrainer {
     float* loss_pinned = nullptr;
     float* gbuf[2] = {nullptr, nullptr};  // ping-pong gradient-of-activation buffers
     float* dcols = nullptr;
+    float* dy_shift[2] = {nullptr, nullptr};  // shifted copies of a conv block's output gradient (implicit input gradient)
     int64_t max_act = 0;
     int64_t t = 0;
     WbAdamConfig adam{};
@@ -283,26 +290,48 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
     t->dl_pitch = (t->classes + 3) / 4 * 4;
     A(dev_alloc_t(t, batch * t->dl_pitch, &t->dlogits));
     A(dev_alloc_t(t, 4, &t->loss_dev));
-    int64_t max_act = batch * t->in_elems, max_dcols = 0;
+    int64_t max_act = batch * t->in_elems, max_dcols = 0, max_dy_shift = 0;
     bool first_conv = true;
     for (Layer& L : t->layers) {
         if (L.kind == L_CONV) {
             int64_t hw = static_cast<int64_t>(L.h) * L.w;
-            A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
+            // The tensor-core implicit GEMM replaces im2col / col2im where its shape rules hold; TF32 mode only
+            // (the 3xTF32 and FP32 modes keep the explicit chain).
+            // WETA_B200_EXPLICIT_CONV=1 in the environment keeps every block on the explicit chain.
+            const char* force_explicit = std::getenv("WETA_B200_EXPLICIT_CONV");
+            L.implicit = matmul_mode == WB_MM_TF32 && wb_conv3_eligible(WbConv3{batch, L.cin, L.h, L.w, L.cout}) &&
+                         !(force_explicit && force_explicit[0] == '1');
+            if (L.implicit) {
+                const int64_t wn = static_cast<int64_t>(L.cout) * L.cin * 9;
+                A(dev_alloc_t(t, batch * L.cin * hw, &L.x_shift[0]));
+                A(dev_alloc_t(t, batch * L.cin * hw, &L.x_shift[1]));
+                A(dev_alloc_t(t, wn, &L.w_fwd));
+                A(dev_alloc_t(t, wn, &L.dw_taps));
+                if (!first_conv) {
+                    A(dev_alloc_t(t, wn, &L.w_dgrad));
+                    max_dy_shift = std::max(max_dy_shift, batch * L.cout * hw);
+                }
+            } else {
+                A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
+                if ((L.cin * 9) % 4 != 0) A(dev_alloc_t(t, static_cast<int64_t>(L.cout) * ((L.cin * 9 + 3) / 4 * 4), &L.w_pad));
+                if (!first_conv) max_dcols = std::max(max_dcols, batch * L.cin * 9 * hw);
+            }
             A(dev_alloc_t(t, batch * L.cout * hw, &L.conv_out));
-            if ((L.cin * 9) % 4 != 0) A(dev_alloc_t(t, static_cast<int64_t>(L.cout) * ((L.cin * 9 + 3) / 4 * 4), &L.w_pad));
             A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
             A(dev_alloc_t(t, L.cout, &L.running_mean));
             A(dev_alloc_t(t, L.cout, &L.running_var));
             A(dev_alloc_t(t, L.cout, &L.save_mean));
             A(dev_alloc_t(t, L.cout, &L.save_rstd));
             max_act = std::max(max_act, batch * L.cout * hw);
-            if (!first_conv) max_dcols = std::max(max_dcols, batch * L.cin * 9 * hw);
             first_conv = false;
         } else {
             A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
             max_act = std::max(max_act, batch * L.out_elems);
         }
+    }
+    if (max_dy_shift > 0) {
+        A(dev_alloc_t(t, max_dy_shift, &t->dy_shift[0]));
+        A(dev_alloc_t(t, max_dy_shift, &t->dy_shift[1]));
     }
     t->max_act = max_act;
     A(dev_alloc_t(t, max_act, &t->gbuf[0]));
@@ -429,6 +458,13 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
         if (L.kind == L_CONV) {
             // F::conv2d_ext (crates/weta-nn/src/functional.rs:84-106): im2col, W[O, C*9] x cols[n], + bias[O,1]
             const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
+            if (L.implicit) {
+                const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
+                { OpTimer tm(t, i, "conv_shift_x"); WB_TRY(wb_conv3_shift_copies(b, act, B * L.cin * L.h, L.w, L.x_shift[0], L.x_shift[1])); }
+                WB_TRY(wb_conv3_weight_reorder(b, 0, t->theta + L.off_w, L.w_fwd, L.cout, L.cin));
+                const float* x3[3] = {L.x_shift[0], act, L.x_shift[1]};
+                { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(wb_conv3_fwd(b, geo, x3, L.w_fwd, t->theta + L.off_b, L.conv_out)); }
+            } else {
             WbView xv{};
             xv.data = const_cast<float*>(act); xv.dtype = WB_F32; xv.ndim = 4;
             xv.shape[0] = B; xv.shape[1] = L.cin; xv.shape[2] = L.h; xv.shape[3] = L.w;
@@ -447,6 +483,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
             tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
             { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep)); }
+            }
             // BatchNorm2d (train) -> ReLU -> MaxPool2d(2)
             {
                 OpTimer tm(t, i, "bn_relu_pool_fwd");
@@ -516,6 +553,20 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 WB_TRY(wb_bn_relu_pool_bwd(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
                                            L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_b));
             }
+            if (L.implicit) {
+                const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
+                const float* x3[3] = {L.x_shift[0], in_act, L.x_shift[1]};
+                { OpTimer tm(t, i, "conv_wgrad_gemm"); WB_TRY(wb_conv3_wgrad(b, geo, dconv, x3, L.dw_taps, t->grad + L.off_w)); }
+                if (need_dx) {
+                    { OpTimer tm(t, i, "conv_shift_dy"); WB_TRY(wb_conv3_shift_copies(b, dconv, B * L.cout * L.h, L.w, t->dy_shift[0], t->dy_shift[1])); }
+                    WB_TRY(wb_conv3_weight_reorder(b, 1, t->theta + L.off_w, L.w_dgrad, L.cout, L.cin));
+                    float* dx = t->gbuf[pp];
+                    pp ^= 1;
+                    const float* d3[3] = {t->dy_shift[0], dconv, t->dy_shift[1]};
+                    { OpTimer tm(t, i, "conv_dgrad_gemm"); WB_TRY(wb_conv3_dgrad(b, geo, d3, L.w_dgrad, dx)); }
+                    g = dx;
+                }
+            } else {
             OpTimer* wt = new OpTimer(t, i, "conv_wgrad_gemm");
             // dW[O, C*9] = sum_n dY[n] cols[n]^T: one contraction over (n, position), not a batched
             // product followed by a reduction over n (ops.rs:821-827 + sum_to_shape).
@@ -555,6 +606,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 WbConvParams cp{3, 3, 1, 1, 1, 1, 1, 1};
                 { OpTimer tm(t, i, "col2im"); WB_TRY(wb_col2im_into(b, &cv, &cp, L.cin, L.h, L.w, dx)); }
                 g = dx;
+            }
             }
         }
         if (t->cb && L.range_len > 0) t->cb(t->cb_user, t->grad + L.range_begin, L.range_len);
