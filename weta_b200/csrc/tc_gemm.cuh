@@ -25,7 +25,8 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 32;                 // 32 tf32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;              // K per tcgen05.mma for tf32
-constexpr int THREADS = 192;          // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
 constexpr uint32_t SPIN_LIMIT = 1u << 26;
 
 struct Segment {
@@ -138,8 +139,8 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-    uint32_t r[32];
+// Issues the TMEM load of 32 columns of this warp's 32 lanes; the registers are valid after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -148,20 +149,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
           "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
           "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
           "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        : "r"(taddr)
+        : "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-constexpr int EPI_PITCH = 36;  // floats per staged row: 144 B keeps float4 alignment and spreads banks
 
 template <int BN, int STAGES>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
     alignas(1024) float a[STAGES][BM * BK];
     alignas(1024) float b[STAGES][BN * BK];
-    alignas(16) float stage[4][32 * EPI_PITCH];  // epilogue staging, one slab per epilogue warp
+    // Epilogue staging, one 32 x 32 slab per epilogue warp; 16-byte chunk j of row r sits at chunk j ^ (r & 7),
+    // so the row-per-lane writes and the row-segment reads are both free of bank conflicts without padding.
+    alignas(128) float stage[EPI_WARPS][32 * 32];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t tmem_full[2];
@@ -173,10 +174,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list round-robin.  Six warps:
+// Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list round-robin.  Ten warps:
 //   warp 0      TMA producer (one lane)            smem ring, STAGES deep
 //   warp 1      MMA issuer (one lane); owns TMEM   two accumulators of BN columns, used alternately
-//   warps 2..5  epilogue: TMEM -> registers -> shared staging -> coalesced global stores
+//   warps 2..9  epilogue: TMEM -> registers -> shared staging -> coalesced global stores
 // so the stores of tile i overlap the loads and MMAs of tile i+1.
 // A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
 template <int BN, int STAGES, bool A_MN, bool B_MN>
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ss.tmem_full[a], 1);
-            mbar_init(&ss.tmem_empty[a], 4);  // one arrival per epilogue warp
+            mbar_init(&ss.tmem_empty[a], EPI_WARPS);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -323,10 +324,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         }
     } else {
         // ---- epilogue warps ---------------------------------------------------------------------
-        const int ew = warp & 3;  // TMEM lane group this warp may read: lanes 32*ew .. 32*ew+31
-        float* stage = &ss.stage[ew][0];
+        // A warp may read the TMEM lanes 32*(warp % 4) .. +31 only; the two warps that share a lane group
+        // take one half of the tile's columns each.
+        const int lg = warp & 3;
+        const int half = (warp - 2) >> 2;
+        constexpr int HALF_N = BN / 2;
+        float* stage = &ss.stage[warp - 2][0];
         const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
                             (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
+        const int sw = lane & 7;  // this lane's row (lane) & 7 when writing a staged row
         int tile_iter = 0;
         for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x, ++tile_iter) {
             int m0, n0, batch, split, kb_begin, kb_end;
@@ -335,55 +341,82 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
             if (!mbar_wait(&ss.tmem_full[acc], use & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN) + (static_cast<uint32_t>(ew * 32) << 16);
-            const int row = m0 + ew * 32 + lane;
+            const int cbase = half * HALF_N;
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN + cbase) + (static_cast<uint32_t>(lg * 32) << 16);
+            const int row = m0 + lg * 32 + lane;
             float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d + static_cast<int64_t>(split) * args.split_stride_d;
             const float bm = (args.ep.bias_m && row < args.m) ? args.ep.bias_m[row] : 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                if (n0 + c >= args.n) break;
-                float v[32];
-                tmem_ld32(tmem_d + c, v);
+            const float* bias_n = args.ep.bias_n;
+            const bool relu = args.ep.relu != 0;
+            // Whole 32-row x HALF_N-column slab inside the matrix, vector stores possible, plain overwrite.
+            const bool fast = vec_ok && !args.ep.accumulate && m0 + lg * 32 + 32 <= args.m && n0 + cbase + HALF_N <= args.n;
+            // The loop below is fully unrolled and every TMEM load is issued unconditionally (columns past the
+            // matrix edge are allocated accumulator columns, just unused), so the registers of a load in flight
+            // are never merged with other values before its wait.
+            uint32_t raw[32];
+            tmem_ld32_issue(tmem_d, raw);
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float r[4];
+            for (int c = 0; c < HALF_N; c += 32) {
+                const int col0 = n0 + cbase + c;
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int col = n0 + c + i + j;
-                        float x = v[i + j] + bm;
-                        if (args.ep.bias_n && col < args.n) x += args.ep.bias_n[col];
-                        if (args.ep.relu) x = fmaxf(x, 0.f);
-                        r[j] = x;
+                for (int i = 0; i < 8; ++i) {
+                    float4 r = make_float4(__uint_as_float(raw[4 * i]) + bm, __uint_as_float(raw[4 * i + 1]) + bm,
+                                           __uint_as_float(raw[4 * i + 2]) + bm, __uint_as_float(raw[4 * i + 3]) + bm);
+                    if (bias_n) {
+                        const int col = col0 + 4 * i;
+                        if (col + 0 < args.n) r.x += bias_n[col + 0];
+                        if (col + 1 < args.n) r.y += bias_n[col + 1];
+                        if (col + 2 < args.n) r.z += bias_n[col + 2];
+                        if (col + 3 < args.n) r.w += bias_n[col + 3];
                     }
-                    *reinterpret_cast<float4*>(stage + lane * EPI_PITCH + i) = make_float4(r[0], r[1], r[2], r[3]);
+                    if (relu) { r.x = fmaxf(r.x, 0.f); r.y = fmaxf(r.y, 0.f); r.z = fmaxf(r.z, 0.f); r.w = fmaxf(r.w, 0.f); }
+                    *reinterpret_cast<float4*>(stage + lane * 32 + ((i ^ sw) << 2)) = r;
+                }
+                // The registers are free again: fetch the next 32 columns while this slab is stored.
+                if (c + 32 < HALF_N) {
+                    tmem_ld32_issue(tmem_d + c + 32, raw);
+                } else {
+                    // Last TMEM read of this warp for the tile: hand the accumulator back before the stores.
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ss.tmem_empty[acc]);
                 }
                 __syncwarp();
-                // Each store instruction of the warp now writes four 128-byte row segments.
+                if (col0 >= args.n) continue;  // warp-uniform: nothing of this slab lies inside the matrix
+                // Each store instruction of the warp writes four 128-byte row segments.
+                const int rsub = lane >> 3, cc = lane & 7;
+                if (fast) {
+                    float* p = out_base + static_cast<int64_t>(m0 + lg * 32 + rsub) * args.ep.ldd + col0 + cc * 4;
+                    const int64_t step = static_cast<int64_t>(args.ep.ldd) * 4;
 #pragma unroll
-                for (int it8 = 0; it8 < 8; ++it8) {
-                    const int r = it8 * 4 + (lane >> 3), cc = (lane & 7) * 4;
-                    const int grow = m0 + ew * 32 + r, gcol = n0 + c + cc;
-                    if (grow < args.m && gcol < args.n) {
-                        float4 val = *reinterpret_cast<const float4*>(stage + r * EPI_PITCH + cc);
-                        float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
-                        if (vec_ok && gcol + 4 <= args.n) {
-                            if (args.ep.accumulate) {
-                                float4 o = *reinterpret_cast<const float4*>(p);
-                                val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
+                    for (int it8 = 0; it8 < 8; ++it8) {
+                        const int r = it8 * 4 + rsub;
+                        *reinterpret_cast<float4*>(p + it8 * step) = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                    }
+                } else {
+#pragma unroll 1
+                    for (int it8 = 0; it8 < 8; ++it8) {
+                        const int r = it8 * 4 + rsub;
+                        const int grow = m0 + lg * 32 + r, gcol = col0 + cc * 4;
+                        if (grow < args.m && gcol < args.n) {
+                            float4 val = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                            float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
+                            if (vec_ok && gcol + 4 <= args.n) {
+                                if (args.ep.accumulate) {
+                                    float4 o = *reinterpret_cast<const float4*>(p);
+                                    val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
+                                }
+                                *reinterpret_cast<float4*>(p) = val;
+                            } else {
+                                const float e[4] = {val.x, val.y, val.z, val.w};
+                                for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
                             }
-                            *reinterpret_cast<float4*>(p) = val;
-                        } else {
-                            const float e[4] = {val.x, val.y, val.z, val.w};
-                            for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
                         }
                     }
                 }
                 __syncwarp();
             }
-            // All of this warp's TMEM reads for the tile are done: hand the accumulator back.
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ss.tmem_empty[acc]);
         }
     }
     if (!ok) {
