@@ -223,6 +223,69 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_dx_kernel(float* __restrict__ 
 }
 
 // ---- conv block tail: BN -> ReLU -> 2x2 max pool, one pass each way ------------------------------
+// Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
+struct FastDiv {
+    uint32_t d, s;
+    uint64_t mul;
+    __host__ FastDiv() : d(1), s(0), mul(1ull << 32) {}
+    __host__ explicit FastDiv(uint32_t div) : d(div) {
+        s = 0;
+        while ((1ull << s) < div) ++s;
+        mul = ((1ull << (32 + s)) + div - 1) / div;
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> (32 + s)); }
+};
+
+// Forward, w % 8 == 0: one thread per four pooled values of a row (two float4 loads from each of two input
+// rows, one float4 store).  SHIFT also writes the pooled tensor shifted one column right (left[y][x] = y[y][x-1])
+// and left (right[y][x] = y[y][x+1]) with zeros shifted in: the three copies an implicit-GEMM convolution of the
+// pooled tensor reads.  The neighbour values come from the adjacent lanes, so SHIFT needs rows that do not
+// straddle warps: w / 8 must divide 32.
+template <bool SHIFT>
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_quad_kernel(float* __restrict__ yp, float* __restrict__ y_left,
+                                                                         float* __restrict__ y_right, const float* __restrict__ x,
+                                                                         const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                         const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                         int c_total, int h, int w, uint32_t total, FastDiv div_ipp,
+                                                                         FastDiv div_owq, FastDiv div_c) {
+    const uint32_t owq = static_cast<uint32_t>(w >> 3), ipp = static_cast<uint32_t>(h >> 1) * owq;
+    const int64_t plane_elems = static_cast<int64_t>(h) * w;
+    const uint32_t stride = gridDim.x * THREADS;
+    for (uint32_t base = blockIdx.x * THREADS + (threadIdx.x & ~31u); base < total; base += stride) {
+        const uint32_t j = base + (threadIdx.x & 31u);
+        const bool valid = j < total;
+        float4 out = make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t oxq = 0;
+        if (valid) {
+            const uint32_t plane = div_ipp.div(j), i = j - plane * ipp;
+            const uint32_t oy = div_owq.div(i);
+            oxq = i - oy * owq;
+            const uint32_t c = plane - div_c.div(plane) * static_cast<uint32_t>(c_total);
+            const float m = __ldg(mean + c), r = __ldg(rstd + c), g = __ldg(gamma + c), b = __ldg(beta + c);
+            const float* src = x + static_cast<int64_t>(plane) * plane_elems + static_cast<int64_t>(2 * oy) * w + 8 * oxq;
+            const float4 a0 = *reinterpret_cast<const float4*>(src), a1 = *reinterpret_cast<const float4*>(src + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(src + w), b1 = *reinterpret_cast<const float4*>(src + w + 4);
+#define WB_BN_ACT(v) fmaf(((v) - m) * r, g, b)
+            out.x = fmaxf(fmaxf(fmaxf(WB_BN_ACT(a0.x), WB_BN_ACT(a0.y)), fmaxf(WB_BN_ACT(b0.x), WB_BN_ACT(b0.y))), 0.f);
+            out.y = fmaxf(fmaxf(fmaxf(WB_BN_ACT(a0.z), WB_BN_ACT(a0.w)), fmaxf(WB_BN_ACT(b0.z), WB_BN_ACT(b0.w))), 0.f);
+            out.z = fmaxf(fmaxf(fmaxf(WB_BN_ACT(a1.x), WB_BN_ACT(a1.y)), fmaxf(WB_BN_ACT(b1.x), WB_BN_ACT(b1.y))), 0.f);
+            out.w = fmaxf(fmaxf(fmaxf(WB_BN_ACT(a1.z), WB_BN_ACT(a1.w)), fmaxf(WB_BN_ACT(b1.z), WB_BN_ACT(b1.w))), 0.f);
+#undef WB_BN_ACT
+            reinterpret_cast<float4*>(yp)[j] = out;
+        }
+        if (SHIFT) {
+            float prev = __shfl_up_sync(0xffffffffu, out.w, 1), next = __shfl_down_sync(0xffffffffu, out.x, 1);
+            if (valid) {
+                if (oxq == 0) prev = 0.f;
+                if (oxq == owq - 1) next = 0.f;
+                reinterpret_cast<float4*>(y_left)[j] = make_float4(prev, out.x, out.y, out.z);
+                reinterpret_cast<float4*>(y_right)[j] = make_float4(out.y, out.z, out.w, next);
+            }
+        }
+    }
+}
+
+
 // Forward: one thread per pooled element.
 __global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_kernel(float* __restrict__ yp, const float* __restrict__ x,
                                                                     const float* __restrict__ mean, const float* __restrict__ rstd,
@@ -269,19 +332,6 @@ __device__ __forceinline__ void pool_window_grads(const float v[4], float m, flo
 #pragma unroll
     for (int k = 0; k < 4; ++k) gout[k] = act[k] == best ? share : 0.f;
 }
-
-// Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
-struct FastDiv {
-    uint32_t d, s;
-    uint64_t mul;
-    __host__ FastDiv() : d(1), s(0), mul(1ull << 32) {}
-    __host__ explicit FastDiv(uint32_t div) : d(div) {
-        s = 0;
-        while ((1ull << s) < div) ++s;
-        mul = ((1ull << (32 + s)) + div - 1) / div;
-    }
-    __device__ __forceinline__ uint32_t div(uint32_t n) const { return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> (32 + s)); }
-};
 
 // grid (C, S) like bn_stats: sums of the full-resolution gradient and of gradient * xhat.
 __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_stats_kernel(const float* __restrict__ x, const float* __restrict__ dyp,
@@ -381,8 +431,12 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
 
 // Width-multiple-of-4 variants: one thread handles two neighbouring pooled elements, i.e. a 2x4 patch
 // of x, with 128-bit loads and stores; same arithmetic as the kernels above.
-template <bool WRITE_DX>
-__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, const float* __restrict__ x,
+// SHIFT (with WRITE_DX): also writes dx shifted one column right (dx_left[y][x] = dx[y][x-1]) and left
+// (dx_right[y][x] = dx[y][x+1]), zeros shifted in; the neighbour values come from the adjacent lanes, so
+// w / 4 must divide 32.
+template <bool WRITE_DX, bool SHIFT>
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, float* __restrict__ dx_left,
+                                                                         float* __restrict__ dx_right, const float* __restrict__ x,
                                                                          const float* __restrict__ dyp, const float* __restrict__ mean,
                                                                          const float* __restrict__ rstd, const float* __restrict__ gamma,
                                                                          const float* __restrict__ beta, const float* __restrict__ dgamma,
@@ -406,32 +460,52 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* _
     float a1 = 0.f, a2 = 0.f;
     int flushed = 0;
 #pragma unroll 2
-    for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
-        const uint32_t n = div_pairs.div(j), i = j - n * pairs;
-        const uint32_t oy = div_owp.div(i), oxp = i - oy * owp;
-        const int64_t o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
-        const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
-        const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
-        const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
-        const float va[4] = {r0.x, r0.y, r1.x, r1.y}, vb[4] = {r0.z, r0.w, r1.z, r1.w};
-        float ga[4], gb[4], xa[4], xb[4];
-        pool_window_grads(va, m, r, g, b, gy.x, ga, xa);
-        pool_window_grads(vb, m, r, g, b, gy.y, gb, xb);
-        if (WRITE_DX) {
-            float da[4], db[4];
+    for (uint32_t base = threadIdx.x & ~31u; base < items; base += THREADS) {
+        const uint32_t j = base + (threadIdx.x & 31u);
+        const bool valid = j < items;
+        float da[4] = {0.f, 0.f, 0.f, 0.f}, db[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t oxp = 0;
+        int64_t o = 0;
+        if (valid) {
+            const uint32_t n = div_pairs.div(j), i = j - n * pairs;
+            const uint32_t oy = div_owp.div(i);
+            oxp = i - oy * owp;
+            o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
+            const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
+            const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
+            const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
+            const float va[4] = {r0.x, r0.y, r1.x, r1.y}, vb[4] = {r0.z, r0.w, r1.z, r1.w};
+            float ga[4], gb[4], xa[4], xb[4];
+            pool_window_grads(va, m, r, g, b, gy.x, ga, xa);
+            pool_window_grads(vb, m, r, g, b, gy.y, gb, xb);
+            if (WRITE_DX) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                da[k] = gr * (ga[k] - k1 - xa[k] * k2);
-                db[k] = gr * (gb[k] - k1 - xb[k] * k2);
-                a1 += da[k] + db[k];
+                for (int k = 0; k < 4; ++k) {
+                    da[k] = gr * (ga[k] - k1 - xa[k] * k2);
+                    db[k] = gr * (gb[k] - k1 - xb[k] * k2);
+                    a1 += da[k] + db[k];
+                }
+                *reinterpret_cast<float4*>(dslab + o) = make_float4(da[0], da[1], db[0], db[1]);
+                *reinterpret_cast<float4*>(dslab + o + w) = make_float4(da[2], da[3], db[2], db[3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    a1 += ga[k] + gb[k];
+                    a2 += ga[k] * xa[k] + gb[k] * xb[k];
+                }
             }
-            *reinterpret_cast<float4*>(dslab + o) = make_float4(da[0], da[1], db[0], db[1]);
-            *reinterpret_cast<float4*>(dslab + o + w) = make_float4(da[2], da[3], db[2], db[3]);
-        } else {
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                a1 += ga[k] + gb[k];
-                a2 += ga[k] * xa[k] + gb[k] * xb[k];
+        }
+        if (WRITE_DX && SHIFT) {
+            float p0 = __shfl_up_sync(0xffffffffu, db[1], 1), p1 = __shfl_up_sync(0xffffffffu, db[3], 1);
+            float n0v = __shfl_down_sync(0xffffffffu, da[0], 1), n1v = __shfl_down_sync(0xffffffffu, da[2], 1);
+            if (valid) {
+                if (oxp == 0) p0 = p1 = 0.f;
+                if (oxp == owp - 1) n0v = n1v = 0.f;
+                const int64_t so = (n0 * c_total + c) * h * w + o;
+                *reinterpret_cast<float4*>(dx_left + so) = make_float4(p0, da[0], da[1], db[0]);
+                *reinterpret_cast<float4*>(dx_left + so + w) = make_float4(p1, da[2], da[3], db[2]);
+                *reinterpret_cast<float4*>(dx_right + so) = make_float4(da[1], db[0], db[1], n0v);
+                *reinterpret_cast<float4*>(dx_right + so + w) = make_float4(da[3], db[2], db[3], n1v);
             }
         }
         if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
@@ -613,38 +687,74 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
     return WB_OK;
 }
 
-extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma,
-                                   const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
-                                   float* save_mean, float* save_rstd) {
+// BatchNorm2d (training statistics) -> ReLU -> MaxPool2d(2); y_left / y_right (both or neither) also receive the
+// pooled tensor shifted one column right / left, zeros shifted in (needs w / 8 in {1, 2, 4, ..., 32}, aligned buffers).
+int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
+                                float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
+                                float* save_rstd, float* y_left, float* y_right) {
     WB_REQUIRE(b && x && gamma && beta && y_pooled, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_fwd: height and width must be even");
+    WB_REQUIRE((y_left == nullptr) == (y_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_fwd: give both shifted outputs or neither");
     WB_TRY(wb_bn2d_stats(b, x, n, c, h * w, eps, momentum, save_mean, save_rstd, running_mean, running_var));
     WbProfileScope ps(b, "bn_relu_pool_fwd");
-    int64_t total = n * c * (h / 2) * (w / 2);
-    bn_relu_pool_fwd_kernel<<<static_cast<unsigned>((total + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        y_pooled, x, save_mean, save_rstd, gamma, beta, static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), total);
+    const int64_t total = n * c * (h / 2) * (w / 2);
+    if (total == 0) return WB_OK;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y_pooled) | reinterpret_cast<uintptr_t>(y_left) |
+                           reinterpret_cast<uintptr_t>(y_right)) & 15) == 0;
+    const bool quads = w % 8 == 0 && aligned && total / 4 < (int64_t(1) << 31) && n * c < (int64_t(1) << 31);
+    WB_REQUIRE(!y_left || (quads && 32 % (w / 8) == 0), WB_ERR_UNSUPPORTED,
+               "wb_bn_relu_pool_fwd: shifted outputs need w / 8 in {1, 2, 4, 8, 16, 32} and 16-byte aligned buffers");
+    if (quads) {
+        const uint32_t items = static_cast<uint32_t>(total / 4);
+        const FastDiv div_ipp(static_cast<uint32_t>((h / 2) * (w / 8))), div_owq(static_cast<uint32_t>(w / 8)), div_c(static_cast<uint32_t>(c));
+        const unsigned grid = static_cast<unsigned>(std::min<int64_t>((items + THREADS - 1) / THREADS, static_cast<int64_t>(b->sm_count) * 8));
+        if (y_left)
+            bn_relu_pool_fwd_quad_kernel<true><<<grid, THREADS, 0, b->stream>>>(y_pooled, y_left, y_right, x, save_mean, save_rstd, gamma, beta,
+                                                                               static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
+                                                                               items, div_ipp, div_owq, div_c);
+        else
+            bn_relu_pool_fwd_quad_kernel<false><<<grid, THREADS, 0, b->stream>>>(y_pooled, nullptr, nullptr, x, save_mean, save_rstd, gamma, beta,
+                                                                                static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
+                                                                                items, div_ipp, div_owq, div_c);
+    } else {
+        bn_relu_pool_fwd_kernel<<<static_cast<unsigned>((total + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+            y_pooled, x, save_mean, save_rstd, gamma, beta, static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), total);
+    }
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
 
-extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
-                                   const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
-                                   float* dgamma, float* dbeta, float* dbias_conv) {
+extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma,
+                                   const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
+                                   float* save_mean, float* save_rstd) {
+    return wb_bn_relu_pool_fwd_shifted(b, x, n, c, h, w, gamma, beta, running_mean, running_var, momentum, eps, y_pooled, save_mean, save_rstd,
+                                       nullptr, nullptr);
+}
+
+// Backward of BatchNorm2d -> ReLU -> MaxPool2d(2); dx_left / dx_right (both or neither) also receive dx shifted one
+// column right / left, zeros shifted in (needs w / 4 in {1, 2, 4, ..., 32} and 16-byte aligned buffers).
+int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
+                                const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
+                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right) {
     WB_REQUIRE(b && x && dy_pooled && dx && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
+    WB_REQUIRE((dx_left == nullptr) == (dx_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_bwd: give both shifted outputs or neither");
     WbProfileScope ps(b, "bn_relu_pool_bwd");
-    int splits = stat_splits(b, bn_relu_pool_bwd_pair_kernel<true>, static_cast<int>(c), n, h * w);
+    int splits = stat_splits(b, bn_relu_pool_bwd_pair_kernel<true, false>, static_cast<int>(c), n, h * w);
     void* s = nullptr;
     WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 3 * sizeof(double), &s));
     double* part = static_cast<double*>(s);
     double* bias_part = part + static_cast<size_t>(c) * splits * 2;
     dim3 grid(static_cast<unsigned>(c), splits);
-    const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx)) & 15) == 0 &&
+    const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dx_left) |
+                                        reinterpret_cast<uintptr_t>(dx_right)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(dy_pooled) & 7) == 0;
+    WB_REQUIRE(!dx_left || (pairs && 32 % (w / 4) == 0), WB_ERR_UNSUPPORTED,
+               "wb_bn_relu_pool_bwd: shifted outputs need w / 4 in {1, 2, 4, 8, 16, 32} and 16-byte aligned buffers");
     const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
     const FastDiv div_pairs(static_cast<uint32_t>(std::max<int64_t>(1, (h / 2) * (w / 4)))), div_owp(static_cast<uint32_t>(std::max<int64_t>(1, w / 4)));
     if (pairs)
-        bn_relu_pool_bwd_pair_kernel<false><<<grid, THREADS, 0, b->stream>>>(nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr,
+        bn_relu_pool_bwd_pair_kernel<false, false><<<grid, THREADS, 0, b->stream>>>(nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr,
                                                                             nullptr, n, static_cast<int>(c), static_cast<int>(h),
                                                                             static_cast<int>(w), inv_count, part, div_pairs, div_owp);
     else
@@ -653,10 +763,16 @@ extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy
     WB_LAUNCH_OK(b);
     bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
-    if (pairs)
-        bn_relu_pool_bwd_pair_kernel<true><<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
-                                                                           static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
-                                                                           inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
+    if (pairs && dx_left)
+        bn_relu_pool_bwd_pair_kernel<true, true><<<grid, THREADS, 0, b->stream>>>(dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma,
+                                                                                 beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
+                                                                                 static_cast<int>(w), inv_count,
+                                                                                 dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
+    else if (pairs)
+        bn_relu_pool_bwd_pair_kernel<true, false><<<grid, THREADS, 0, b->stream>>>(dx, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma,
+                                                                                  beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
+                                                                                  static_cast<int>(w), inv_count,
+                                                                                  dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
     else
         bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
                                                                    static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
@@ -667,5 +783,12 @@ extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy
         WB_LAUNCH_OK(b);
     }
     return WB_OK;
+}
+
+extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
+                                   const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
+                                   float* dgamma, float* dbeta, float* dbias_conv) {
+    return wb_bn_relu_pool_bwd_shifted(b, x, dy_pooled, n, c, h, w, gamma, beta, save_mean, save_rstd, dx, dgamma, dbeta, dbias_conv, nullptr,
+                                       nullptr);
 }
 

@@ -21,6 +21,12 @@
 #include "common.h"
 #include "gemm.h"
 
+int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
+                                float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
+                                float* save_rstd, float* y_left, float* y_right);
+int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
+                                const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
+                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right);
 int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs, float* dlogits,
                           int64_t dz_pitch, float* row_loss, float* mean_loss, double upstream);
 
@@ -50,6 +56,8 @@ struct Layer {
     // Implicit-GEMM path (no cols / dcols): the input shifted one column right / left, the weight as
     // [O][tap][C] and [C][flipped tap][O], and the weight gradient as the kernel writes it ([tap][C][O]).
     bool implicit = false;
+    bool x_shift_fused = false;   // the previous block's BN/ReLU/pool pass writes x_shift
+    bool dy_shift_fused = false;  // this block's BN/ReLU/pool backward writes the trainer's dy_shift
     float* x_shift[2] = {nullptr, nullptr};
     float *w_fwd = nullptr, *w_dgrad = nullptr, *dw_taps = nullptr;
     float* out_act = nullptr;   // layer output
@@ -307,6 +315,12 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
                 A(dev_alloc_t(t, batch * L.cin * hw, &L.x_shift[1]));
                 A(dev_alloc_t(t, wn, &L.w_fwd));
                 A(dev_alloc_t(t, wn, &L.dw_taps));
+                L.dy_shift_fused = !first_conv && L.w % 4 == 0 && 32 % (L.w / 4) == 0;
+                {
+                    // input = the pooled output of a conv block directly before this one, whose width is 2 * L.w
+                    const size_t li = static_cast<size_t>(&L - t->layers.data());
+                    L.x_shift_fused = li > 0 && t->layers[li - 1].kind == L_CONV && (2 * L.w) % 8 == 0 && 32 % (2 * L.w / 8) == 0;
+                }
                 if (!first_conv) {
                     A(dev_alloc_t(t, wn, &L.w_dgrad));
                     max_dy_shift = std::max(max_dy_shift, batch * L.cout * hw);
@@ -460,7 +474,10 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
             if (L.implicit) {
                 const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
-                { OpTimer tm(t, i, "conv_shift_x"); WB_TRY(wb_conv3_shift_copies(b, act, B * L.cin * L.h, L.w, L.x_shift[0], L.x_shift[1])); }
+                if (!L.x_shift_fused) {
+                    OpTimer tm(t, i, "conv_shift_x");
+                    WB_TRY(wb_conv3_shift_copies(b, act, B * L.cin * L.h, L.w, L.x_shift[0], L.x_shift[1]));
+                }
                 WB_TRY(wb_conv3_weight_reorder(b, 0, t->theta + L.off_w, L.w_fwd, L.cout, L.cin));
                 const float* x3[3] = {L.x_shift[0], act, L.x_shift[1]};
                 { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(wb_conv3_fwd(b, geo, x3, L.w_fwd, t->theta + L.off_b, L.conv_out)); }
@@ -487,8 +504,12 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             // BatchNorm2d (train) -> ReLU -> MaxPool2d(2)
             {
                 OpTimer tm(t, i, "bn_relu_pool_fwd");
-                WB_TRY(wb_bn_relu_pool_fwd(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.running_mean,
-                                           L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd));
+                // The block that follows reads its input in three column-shifted copies when it is an implicit GEMM:
+                // write the two extra copies from here instead of re-reading the pooled tensor.
+                Layer* next = (i + 1 < nl && t->layers[i + 1].kind == L_CONV && t->layers[i + 1].x_shift_fused) ? &t->layers[i + 1] : nullptr;
+                WB_TRY(wb_bn_relu_pool_fwd_shifted(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
+                                                   L.running_mean, L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd,
+                                                   next ? next->x_shift[0] : nullptr, next ? next->x_shift[1] : nullptr));
             }
             act = L.out_act;
         } else if (L.kind == L_LINEAR) {
@@ -550,15 +571,20 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             pp ^= 1;
             {
                 OpTimer tm(t, i, "bn_relu_pool_bwd");
-                WB_TRY(wb_bn_relu_pool_bwd(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
-                                           L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_b));
+                const bool fuse = L.implicit && need_dx && L.dy_shift_fused;
+                WB_TRY(wb_bn_relu_pool_bwd_shifted(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
+                                                   L.save_mean, L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta,
+                                                   t->grad + L.off_b, fuse ? t->dy_shift[0] : nullptr, fuse ? t->dy_shift[1] : nullptr));
             }
             if (L.implicit) {
                 const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
                 const float* x3[3] = {L.x_shift[0], in_act, L.x_shift[1]};
                 { OpTimer tm(t, i, "conv_wgrad_gemm"); WB_TRY(wb_conv3_wgrad(b, geo, dconv, x3, L.dw_taps, t->grad + L.off_w)); }
                 if (need_dx) {
-                    { OpTimer tm(t, i, "conv_shift_dy"); WB_TRY(wb_conv3_shift_copies(b, dconv, B * L.cout * L.h, L.w, t->dy_shift[0], t->dy_shift[1])); }
+                    if (!L.dy_shift_fused) {
+                        OpTimer tm(t, i, "conv_shift_dy");
+                        WB_TRY(wb_conv3_shift_copies(b, dconv, B * L.cout * L.h, L.w, t->dy_shift[0], t->dy_shift[1]));
+                    }
                     WB_TRY(wb_conv3_weight_reorder(b, 1, t->theta + L.off_w, L.w_dgrad, L.cout, L.cin));
                     float* dx = t->gbuf[pp];
                     pp ^= 1;
