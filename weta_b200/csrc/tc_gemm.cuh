@@ -228,60 +228,83 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ---------------------------------------------------------------
+            // Walks this CTA's (tile, segment, K block) sequence and fills the shared-memory ring.  (Asking L2 to
+            // fetch boxes further ahead with cp.async.bulk.prefetch.tensor was tried and made every contraction
+            // slower: the kernel is bound by the bytes the SM pulls through L2, and a prefetch pulls them twice.)
             constexpr uint32_t stage_bytes = (BM * BK + BN * BK) * sizeof(float);
-            int it = 0;
-            for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x) {
-                int m0, n0, batch, split, kb_begin, kb_end;
-                decode(t, m0, n0, batch, split, kb_begin, kb_end);
-                for (int sg = 0; sg < args.num_segments && ok; ++sg) {
-                    const CUtensorMap* ma = &args.seg[sg].a;
-                    const CUtensorMap* mb = &args.seg[sg].b;
-                    for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-                        const int s = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1;
-                        if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
-                        mbar_expect_tx(&ss.full[s], stage_bytes);
-                        // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
-                        // operand pair, kpb blocks per image (a convolution's weight gradient); the image
-                        // index becomes the third TMA coordinate and each image's tail is zero-filled.
-                        const int k0 = (args.kpb > 0 ? kb % args.kpb : kb) * BK;
-                        const int kz = args.kpb > 0 ? kb / args.kpb : 0;
-                        const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
-                        const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
-                        if (args.conv_mode == 1) {
-                            // kb = tap * conv_cb + channel block; tap = ky*3 + kx.  The window of tap (ky, kx) over a run
-                            // of pixels is the same run, moved (ky-1) image rows, of the copy shifted by kx-1; positions
-                            // before the first / after the last pixel are zero-filled by TMA, which is the padding.
-                            const int tap = kb / args.conv_cb, cb = kb - tap * args.conv_cb;
-                            const int ky = tap / 3, kx = tap - ky * 3;
-                            tma_load_3d(&ss.a[s][0], ma, &ss.full[s], kb * BK, m0, 0);
-                            const CUtensorMap* mx = &args.seg[kx].b;
-                            const int x0 = n0 + (ky - 1) * args.conv_w;
+            struct Cursor { int t, sg, kb, m0, n0, batch, split, kb_begin, kb_end; };
+            auto start = [&](Cursor& c, int t) {
+                c.t = t;
+                c.sg = 0;
+                if (t < args.total_tiles) {
+                    decode(t, c.m0, c.n0, c.batch, c.split, c.kb_begin, c.kb_end);
+                    c.kb = c.kb_begin;
+                }
+            };
+            auto next = [&](Cursor& c) {
+                if (++c.kb >= c.kb_end) {
+                    c.kb = c.kb_begin;
+                    if (++c.sg >= args.num_segments) start(c, c.t + static_cast<int>(gridDim.x));
+                }
+            };
+            // One K block of operands into ring slot s.
+            auto issue = [&](const int s, const Cursor& c) {
+                const CUtensorMap* ma = &args.seg[c.sg].a;
+                const CUtensorMap* mb = &args.seg[c.sg].b;
+                const int m0 = c.m0, n0 = c.n0, batch = c.batch, kb = c.kb;
+                uint64_t* bar = &ss.full[s];
+                auto copy = [&](float* dst, const CUtensorMap* map, int x, int y, int z) { tma_load_3d(dst, map, bar, x, y, z); };
+                // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
+                // operand pair, kpb blocks per image (a convolution's weight gradient); the image
+                // index becomes the third TMA coordinate and each image's tail is zero-filled.
+                const int k0 = (args.kpb > 0 ? kb % args.kpb : kb) * BK;
+                const int kz = args.kpb > 0 ? kb / args.kpb : 0;
+                const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
+                const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
+                if (args.conv_mode == 1) {
+                    // kb = channel block * 9 + tap, tap = ky*3 + kx: the nine taps of a channel block follow one
+                    // another, so the rows a tap shares with the previous ones (same pixels, moved by a row) are
+                    // still in L2.  The window of tap (ky, kx) over a run of pixels is the same run, moved (ky-1)
+                    // image rows, of the copy shifted by kx-1; positions before the first / after the last pixel
+                    // are zero-filled by TMA, which is the padding.  A's columns are ordered (tap, channel).
+                    const int cb = kb / 9, tap = kb - cb * 9;
+                    const int ky = tap / 3, kx = tap - ky * 3;
+                    copy(&ss.a[s][0], ma, (tap * args.conv_cb + cb) * BK, m0, 0);
+                    const CUtensorMap* mx = &args.seg[kx].b;
+                    const int x0 = n0 + (ky - 1) * args.conv_w;
 #pragma unroll
-                            for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mx, &ss.full[s], x0 + c * 32, cb * 32, batch);
-                        } else if (args.conv_mode == 2) {
-                            // M tile = tap * conv_cb + channel block of BM; K block = 32 pixels of image kz.
-                            const int mbi = m0 / BM;
-                            const int tap = mbi / args.conv_cb, cb = mbi - tap * args.conv_cb;
-                            const int ky = tap / 3, kx = tap - ky * 3;
-                            tma_load_3d(&ss.a[s][0], &args.seg[kx].a, &ss.full[s], k0 + (ky - 1) * args.conv_w, cb * BM, kz);
-                            tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, kz);
-                        } else {
-                            if constexpr (A_MN) {
+                    for (int ch = 0; ch < BN / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mx, x0 + ch * 32, cb * 32, batch);
+                } else if (args.conv_mode == 2) {
+                    // M tile = tap * conv_cb + channel block of BM; K block = 32 pixels of image kz.
+                    const int mbi = m0 / BM;
+                    const int tap = mbi / args.conv_cb, cb = mbi - tap * args.conv_cb;
+                    const int ky = tap / 3, kx = tap - ky * 3;
+                    copy(&ss.a[s][0], &args.seg[kx].a, k0 + (ky - 1) * args.conv_w, cb * BM, kz);
+                    copy(&ss.b[s][0], mb, k0, n0, kz);
+                } else {
+                    if constexpr (A_MN) {
 #pragma unroll
-                                for (int c = 0; c < BM / 32; ++c) tma_load_3d(&ss.a[s][c * 32 * BK], ma, &ss.full[s], m0 + c * 32, k0, za);
-                            } else {
-                                tma_load_3d(&ss.a[s][0], ma, &ss.full[s], k0, m0, za);
-                            }
-                            if constexpr (B_MN) {
+                        for (int ch = 0; ch < BM / 32; ++ch) copy(&ss.a[s][ch * 32 * BK], ma, m0 + ch * 32, k0, za);
+                    } else {
+                        copy(&ss.a[s][0], ma, k0, m0, za);
+                    }
+                    if constexpr (B_MN) {
 #pragma unroll
-                                for (int c = 0; c < BN / 32; ++c) tma_load_3d(&ss.b[s][c * 32 * BK], mb, &ss.full[s], n0 + c * 32, k0, zb);
-                            } else {
-                                tma_load_3d(&ss.b[s][0], mb, &ss.full[s], k0, n0, zb);
-                            }
-                        }
+                        for (int ch = 0; ch < BN / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mb, n0 + ch * 32, k0, zb);
+                    } else {
+                        copy(&ss.b[s][0], mb, k0, n0, zb);
                     }
                 }
+            };
+            Cursor cur;
+            start(cur, static_cast<int>(blockIdx.x));
+            for (int it = 0; cur.t < args.total_tiles; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
+                mbar_expect_tx(&ss.full[s], stage_bytes);
+                issue(s, cur);
+                next(cur);
             }
         }
     } else if (warp == 1) {
