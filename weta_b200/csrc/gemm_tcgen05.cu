@@ -128,34 +128,67 @@ __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, 
     lo[i] = v - h;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS>
 int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
-    using SS = tc::SharedStorage<BN, STAGES>;
+    using SS = tc::SharedStorage<BN, STAGES, CTAS>;
     constexpr size_t smem = sizeof(SS) + 1024;
-    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN>;
+    static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS>;
     static bool attr_done = false;
     if (!attr_done) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_done = true;
     }
-    kern<<<grid, tc::THREADS, smem, be->stream>>>(args);
+    if (CTAS == 1) {
+        kern<<<grid, tc::THREADS, smem, be->stream>>>(args);
+    } else {
+        // Clusters of two CTAs (an MMA pair); grid.x is even.
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(tc::THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = be->stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            wb_set_error("cluster launch of the paired GEMM failed: %s", cudaGetErrorString(e));
+            return WB_ERR_CUDA;
+        }
+    }
     WB_LAUNCH_OK(be);
     return WB_OK;
 }
 
+// Two CTAs per 256 x 256 tile when the output has more than one 128-row block: a third fewer operand bytes per
+// flop through L2, which is what bounds these contractions.  WETA_B200_NO_PAIRS=1 keeps single-CTA tiles.
+bool pair_mode(int m, int BN) {
+    static const bool off = [] { const char* e = std::getenv("WETA_B200_NO_PAIRS"); return e && e[0] == '1'; }();
+    return !off && BN == 256 && m > tc::BM;
+}
+
 // Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
 // the persistent kernel, split-K finish.  `args` arrives with its tensor maps, k_blocks and mode fields set.
-int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool amn, bool bmn,
+int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool pair, bool amn, bool bmn,
               const tc::Epilogue& ep, int force_splits) {
     args.m = m;
     args.n = n;
     args.error_flag = st->error_flag;
-    const int tiles_m = (m + tc::BM - 1) / tc::BM, tiles_n = (n + BN - 1) / BN;
+    // pair: CTA pairs on 256-row tiles; the caller sized the B tensor map's box for it (BN / 2 rows per CTA).
+    const int tile_m = pair ? 2 * tc::BM : tc::BM;
+    const int workers = pair ? be->sm_count / 2 : be->sm_count;  // CTAs or CTA pairs that walk the tile list
+    const int tiles_m = (m + tile_m - 1) / tile_m, tiles_n = (n + BN - 1) / BN;
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
     int splits = 1;
     if (force_splits > 0) splits = force_splits;
-    else if (tiles * 2 <= be->sm_count && args.k_blocks >= 16) {
-        splits = static_cast<int>(std::min<int64_t>(be->sm_count / tiles, args.k_blocks / 8));
+    else if (tiles * 2 <= workers && args.k_blocks >= 16) {
+        splits = static_cast<int>(std::min<int64_t>(workers / tiles, args.k_blocks / 8));
     }
     splits = std::max(1, std::min(splits, args.k_blocks));
     // Make every split non-empty.
@@ -185,19 +218,25 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             status = WB_ERR_UNSUPPORTED;
         }
         args.total_tiles = static_cast<int>(total_tiles);
-        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, be->sm_count)));
-        // Shared memory: 4 x 48 KB ring (BN = 256) or 5 x 32 KB (BN = 128) + 18 KB epilogue staging; one persistent CTA per SM.
+        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, workers) * (pair ? 2 : 1)));
+        // Shared memory: a 192 KB ring (6 x 32 KB per CTA of a pair, 4 x 48 KB for BN = 256, 5 x 32 KB for BN = 128)
+        // + 32 KB epilogue staging; one persistent CTA per SM.
         if (status != WB_OK) {
+        } else if (pair) {
+            if (!amn && !bmn) status = launch_tc<256, 6, false, false, 2>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<256, 6, false, true, 2>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<256, 6, true, false, 2>(be, st, args, grid);
+            else status = launch_tc<256, 6, true, true, 2>(be, st, args, grid);
         } else if (BN == 256) {
-            if (!amn && !bmn) status = launch_tc<256, 4, false, false>(be, st, args, grid);
-            else if (!amn && bmn) status = launch_tc<256, 4, false, true>(be, st, args, grid);
-            else if (amn && !bmn) status = launch_tc<256, 4, true, false>(be, st, args, grid);
-            else status = launch_tc<256, 4, true, true>(be, st, args, grid);
+            if (!amn && !bmn) status = launch_tc<256, 4, false, false, 1>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<256, 4, false, true, 1>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<256, 4, true, false, 1>(be, st, args, grid);
+            else status = launch_tc<256, 4, true, true, 1>(be, st, args, grid);
         } else {
-            if (!amn && !bmn) status = launch_tc<128, 5, false, false>(be, st, args, grid);
-            else if (!amn && bmn) status = launch_tc<128, 5, false, true>(be, st, args, grid);
-            else if (amn && !bmn) status = launch_tc<128, 5, true, false>(be, st, args, grid);
-            else status = launch_tc<128, 5, true, true>(be, st, args, grid);
+            if (!amn && !bmn) status = launch_tc<128, 5, false, false, 1>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<128, 5, false, true, 1>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<128, 5, true, false, 1>(be, st, args, grid);
+            else status = launch_tc<128, 5, true, true, 1>(be, st, args, grid);
         }
     }
     if (status == WB_OK && splits > 1) {
@@ -229,6 +268,8 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     // 128 x 256 tiles when the output is wide enough: half the A traffic and twice the MMA work per
     // pipeline stage; 128 x 128 otherwise.
     const int BN = n > 128 ? 256 : 128;
+    const bool pair = pair_mode(m, BN);
+    const int b_box = pair ? BN / 2 : BN;  // B rows one CTA loads per K block
     tc::Args args{};
     void *hi_a = nullptr, *hi_b = nullptr;
     size_t ka = 0, kb = 0;
@@ -256,16 +297,16 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         if (s2 != WB_OK) { wb_arena_free(be, hi_a, ka); return s2; }
         args.num_segments = 3;
         int s = make_map(st, Ah, batch, tc::BM, &args.seg[0].a);
-        if (s == WB_OK) s = make_map(st, Bh, batch, BN, &args.seg[0].b);
+        if (s == WB_OK) s = make_map(st, Bh, batch, b_box, &args.seg[0].b);
         if (s == WB_OK) s = make_map(st, Ah, batch, tc::BM, &args.seg[1].a);
-        if (s == WB_OK) s = make_map(st, Bl, batch, BN, &args.seg[1].b);
+        if (s == WB_OK) s = make_map(st, Bl, batch, b_box, &args.seg[1].b);
         if (s == WB_OK) s = make_map(st, Al, batch, tc::BM, &args.seg[2].a);
-        if (s == WB_OK) s = make_map(st, Bh, batch, BN, &args.seg[2].b);
+        if (s == WB_OK) s = make_map(st, Bh, batch, b_box, &args.seg[2].b);
         if (s != WB_OK) { wb_arena_free(be, hi_a, ka); wb_arena_free(be, hi_b, kb); return s; }
     } else {
         args.num_segments = 1;
         WB_TRY(make_map(st, A, batch, tc::BM, &args.seg[0].a));
-        WB_TRY(make_map(st, B, batch, BN, &args.seg[0].b));
+        WB_TRY(make_map(st, B, batch, b_box, &args.seg[0].b));
     }
     args.k_blocks = (k + tc::BK - 1) / tc::BK;
     args.kpb = 0;
@@ -276,7 +317,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     }
     args.batched_a = A.batch_stride != 0;
     args.batched_b = B.batch_stride != 0;
-    int status = run_tiles(be, st, args, m, n, grid_batch, BN, A.mn_major, B.mn_major, ep, force_splits);
+    int status = run_tiles(be, st, args, m, n, grid_batch, BN, pair, A.mn_major, B.mn_major, ep, force_splits);
     if (hi_a) wb_arena_free(be, hi_a, ka);
     if (hi_b) wb_arena_free(be, hi_b, kb);
     return status;
@@ -317,22 +358,28 @@ int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const 
         args.conv_cb = static_cast<int>(ch / 32);
         args.batched_a = 0;
         args.batched_b = 1;
-        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, BN, false, true, ep, 1);
+        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, BN, pair_mode(m, BN), false, true, ep, 1);
     }
     const int BN = m > 128 ? 256 : 128;
     for (int kx = 0; kx < 3; ++kx) {
         WbGemmOperand A{img[kx], ch, hw, hw, ch * hw, false};
         WB_TRY(make_map(st, A, batch, tc::BM, &args.seg[kx].a));
     }
-    WbGemmOperand B{a, m, hw, hw, static_cast<int64_t>(m) * hw, false};
-    WB_TRY(make_map(st, B, batch, BN, &args.seg[0].b));
     args.kpb = static_cast<int>((hw + tc::BK - 1) / tc::BK);
     WB_REQUIRE(batch * args.kpb < (int64_t(1) << 31), WB_ERR_UNSUPPORTED, "conv weight gradient: contraction too long");
     args.k_blocks = static_cast<int>(batch * args.kpb);
     args.conv_cb = static_cast<int>(ch / tc::BM);
     args.batched_a = 1;
     args.batched_b = 1;
-    return run_tiles(be, st, args, static_cast<int>(9 * ch), m, 1, BN, false, false, ep, 0);
+    // Rows come in blocks of BM = 128 (tap, channel block).  Paired CTAs take two blocks per tile; with an odd block
+    // count (9 for 128 channels) half a tile would idle for the whole contraction, and handing the odd block to a
+    // second launch makes that launch re-read all of dY for a ninth of the work: both measured slower than
+    // single-CTA tiles, which are used then.
+    const int blocks = static_cast<int>(9 * ch / tc::BM);
+    const bool pair = pair_mode(blocks * tc::BM, BN) && blocks % 2 == 0;
+    WbGemmOperand B{a, m, hw, hw, static_cast<int64_t>(m) * hw, false};
+    WB_TRY(make_map(st, B, batch, pair ? BN / 2 : BN, &args.seg[0].b));
+    return run_tiles(be, st, args, blocks * tc::BM, m, 1, BN, pair, false, false, ep, 0);
 }
 
 // Reads the device-side error flag the GEMM kernels raise when a bounded wait runs out.

@@ -139,6 +139,49 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster act as one 256-row MMA --------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Shared::cluster address of the same shared-memory location in CTA `cta` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load issued by either CTA of a pair; the bytes are counted on the barrier at cluster address `bar`
+// (the leader CTA's), which cta_group::2 allows to live in the other CTA than the destination.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+// D[256 x N] (+)= A[256 x 8] B[8 x N]: rows 0-127 of A and D live in the leader CTA, rows 128-255 in its peer;
+// each CTA's shared memory holds N/2 rows of B.  Issued by the leader only.
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Completion of the pair's MMAs issued so far, signalled on the barrier at cluster address `bar` (either CTA's).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
 // Issues the TMEM load of 32 columns of this warp's 32 lanes; the registers are valid after tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
     asm volatile(
@@ -155,11 +198,11 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CTAS>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
     alignas(1024) float a[STAGES][BM * BK];
-    alignas(1024) float b[STAGES][BN * BK];
+    alignas(1024) float b[STAGES][BN / CTAS * BK];  // a CTA of a pair holds half of the tile's B rows
     // Epilogue staging, one 32 x 32 slab per epilogue warp; 16-byte chunk j of row r sits at chunk j ^ (r & 7),
     // so the row-per-lane writes and the row-segment reads are both free of bank conflicts without padding.
     alignas(128) float stage[EPI_WARPS][32 * 32];
@@ -180,14 +223,24 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 //   warps 2..9  epilogue: TMEM -> registers -> shared staging -> coalesced global stores
 // so the stores of tile i overlap the loads and MMAs of tile i+1.
 // A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+// CTAS = 2: launched as clusters of two CTAs that share one (2*BM) x BN tile.  Each loads its own BM rows of A
+// and its own BN/2 rows of B (a third fewer bytes per flop through L2 than two independent BM x BN tiles); the
+// even CTA (the leader) issues cta_group::2 MMAs that read both CTAs' shared memory and write both CTAs' TMEM;
+// each CTA stores its own BM rows of the result.  Barriers: `full` and `tmem_empty` are the leader's (the peer's
+// loads and epilogue warps signal them remotely), `empty` and `tmem_full` exist in both CTAs and the leader's
+// commits signal each of them.
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using SS = SharedStorage<BN, STAGES>;
+    using SS = SharedStorage<BN, STAGES, CTAS>;
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
+    constexpr int TILE_M = BM * CTAS;   // output rows per tile
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_per = (args.k_blocks + args.splits - 1) / args.splits;
+    const int rank = CTAS == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int first_tile = static_cast<int>(blockIdx.x) / CTAS, tile_step = static_cast<int>(gridDim.x) / CTAS;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -196,17 +249,24 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&ss.tmem_full[a], 1);
-            mbar_init(&ss.tmem_empty[a], EPI_WARPS);  // one arrival per epilogue warp
+            mbar_init(&ss.tmem_empty[a], EPI_WARPS * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (CTAS == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = ss.tmem_base;
     bool ok = true;
@@ -217,7 +277,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         const int r = t / args.tiles_n;
         const int mb = r % args.tiles_m;
         const int z = r / args.tiles_m;
-        m0 = mb * BM;
+        m0 = mb * TILE_M;
         n0 = nb * BN;
         batch = z / args.splits;
         split = z % args.splits;
@@ -231,7 +291,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             // Walks this CTA's (tile, segment, K block) sequence and fills the shared-memory ring.  (Asking L2 to
             // fetch boxes further ahead with cp.async.bulk.prefetch.tensor was tried and made every contraction
             // slower: the kernel is bound by the bytes the SM pulls through L2, and a prefetch pulls them twice.)
-            constexpr uint32_t stage_bytes = (BM * BK + BN * BK) * sizeof(float);
+            constexpr uint32_t stage_bytes = (BM * BK + B_ROWS * BK) * sizeof(float);  // this CTA's share of a stage
             struct Cursor { int t, sg, kb, m0, n0, batch, split, kb_begin, kb_end; };
             auto start = [&](Cursor& c, int t) {
                 c.t = t;
@@ -244,16 +304,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             auto next = [&](Cursor& c) {
                 if (++c.kb >= c.kb_end) {
                     c.kb = c.kb_begin;
-                    if (++c.sg >= args.num_segments) start(c, c.t + static_cast<int>(gridDim.x));
+                    if (++c.sg >= args.num_segments) start(c, c.t + tile_step);
                 }
             };
             // One K block of operands into ring slot s.
             auto issue = [&](const int s, const Cursor& c) {
                 const CUtensorMap* ma = &args.seg[c.sg].a;
                 const CUtensorMap* mb = &args.seg[c.sg].b;
-                const int m0 = c.m0, n0 = c.n0, batch = c.batch, kb = c.kb;
+                // This CTA's rows of A and of B inside the tile.
+                const int m0 = c.m0 + rank * BM, n0 = c.n0 + rank * B_ROWS, batch = c.batch, kb = c.kb;
                 uint64_t* bar = &ss.full[s];
-                auto copy = [&](float* dst, const CUtensorMap* map, int x, int y, int z) { tma_load_3d(dst, map, bar, x, y, z); };
+                const uint32_t leader_bar = CTAS == 2 ? map_to_cta(smem_u32(bar), 0) : 0;
+                auto copy = [&](float* dst, const CUtensorMap* map, int x, int y, int z) {
+                    if constexpr (CTAS == 2) tma_load_3d_pair(dst, map, leader_bar, x, y, z);
+                    else tma_load_3d(dst, map, bar, x, y, z);
+                };
                 // kpb > 0: the contraction runs over (image, position) pairs of a batched K-major
                 // operand pair, kpb blocks per image (a convolution's weight gradient); the image
                 // index becomes the third TMA coordinate and each image's tail is zero-filled.
@@ -273,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                     const CUtensorMap* mx = &args.seg[kx].b;
                     const int x0 = n0 + (ky - 1) * args.conv_w;
 #pragma unroll
-                    for (int ch = 0; ch < BN / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mx, x0 + ch * 32, cb * 32, batch);
+                    for (int ch = 0; ch < B_ROWS / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mx, x0 + ch * 32, cb * 32, batch);
                 } else if (args.conv_mode == 2) {
                     // M tile = tap * conv_cb + channel block of BM; K block = 32 pixels of image kz.
                     const int mbi = m0 / BM;
@@ -290,29 +355,38 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                     }
                     if constexpr (B_MN) {
 #pragma unroll
-                        for (int ch = 0; ch < BN / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mb, n0 + ch * 32, k0, zb);
+                        for (int ch = 0; ch < B_ROWS / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mb, n0 + ch * 32, k0, zb);
                     } else {
                         copy(&ss.b[s][0], mb, k0, n0, zb);
                     }
                 }
             };
             Cursor cur;
-            start(cur, static_cast<int>(blockIdx.x));
+            start(cur, first_tile);
             for (int it = 0; cur.t < args.total_tiles; ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
-                mbar_expect_tx(&ss.full[s], stage_bytes);
+                if (rank == 0) mbar_expect_tx(&ss.full[s], stage_bytes * CTAS);  // the leader's barrier counts both CTAs' bytes
                 issue(s, cur);
                 next(cur);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer -----------------------------------------------------------------
-            constexpr uint32_t idesc = make_idesc(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (the leader CTA of a pair) ----------------------------------------
+            constexpr uint32_t idesc = make_idesc(TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            // A completion is signalled in this CTA and, for a pair, at the same barrier of the peer.
+            auto commit = [&](uint64_t* bar) {
+                if constexpr (CTAS == 2) {
+                    umma_commit_pair(smem_u32(bar));
+                    umma_commit_pair(map_to_cta(smem_u32(bar), 1));
+                } else {
+                    umma_commit(bar);
+                }
+            };
             int it = 0, tile_iter = 0;
-            for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+            for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
                 int m0, n0, batch, split, kb_begin, kb_end;
                 decode(t, m0, n0, batch, split, kb_begin, kb_end);
                 const int acc = tile_iter & 1;
@@ -337,12 +411,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                         //          a K step of 8 is two groups = +1024 B.
                         uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
                         uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
-                        umma_tf32(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        if constexpr (CTAS == 2) umma_tf32_pair(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        else umma_tf32(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
                     }
-                    umma_commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
+                    commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
                 }
                 if (!ok) break;
-                umma_commit(&ss.tmem_full[acc]);  // accumulator complete once every MMA above has retired
+                commit(&ss.tmem_full[acc]);  // accumulator complete once every MMA above has retired
             }
         }
     } else {
@@ -357,9 +432,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                             (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
         const int sw = lane & 7;  // this lane's row (lane) & 7 when writing a staged row
         int tile_iter = 0;
-        for (int t = blockIdx.x; t < args.total_tiles && ok; t += gridDim.x, ++tile_iter) {
+        for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
             int m0, n0, batch, split, kb_begin, kb_end;
             decode(t, m0, n0, batch, split, kb_begin, kb_end);
+            m0 += rank * BM;  // this CTA's rows of the tile
             const int acc = tile_iter & 1;
             const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
             if (!mbar_wait(&ss.tmem_full[acc], use & 1)) { ok = false; break; }
@@ -403,7 +479,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
                     // Last TMEM read of this warp for the tile: hand the accumulator back before the stores.
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&ss.tmem_empty[acc]);
+                    if (lane == 0) {
+                        if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.tmem_empty[acc]), 0));
+                        else mbar_arrive(&ss.tmem_empty[acc]);
+                    }
                 }
                 __syncwarp();
                 if (col0 >= args.n) continue;  // warp-uniform: nothing of this slab lies inside the matrix
@@ -450,8 +529,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();  // neither CTA frees TMEM or leaves while its peer may still signal or write it
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
