@@ -73,9 +73,11 @@ bool wb_conv3_eligible(const WbConv3& g) {
 }
 
 // y[n][o][h][w] = conv(x, weight) + bias[o];  wr = weight as [o][tap][c] (wb_conv3_weight_reorder kind 0).
-int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y) {
+// channel_sums (optional, zeroed by the caller): receives per output channel (sum y, sum y^2) over the batch.
+int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y, double* channel_sums) {
     const int64_t hw = g.h * g.w;
     tc::Epilogue ep{y, hw, g.o * hw, nullptr, bias, 0, 0};
+    ep.row_stats = channel_sums;
     return wb_tc_conv_gemm(b, 1, wr, x3, g.n, g.c, g.h, g.w, static_cast<int>(g.o), ep);
 }
 
@@ -138,7 +140,7 @@ extern "C" int wb_conv3x3_fwd(WbBackend* b, const float* x, const float* weight,
     WB_TRY(wb_conv3_shift_copies(b, x, n * c * h, static_cast<int>(w), left, right));
     WB_TRY(wb_conv3_weight_reorder(b, 0, weight, wr, static_cast<int>(o), static_cast<int>(c)));
     const float* x3[3] = {left, x, right};
-    return wb_conv3_fwd(b, g, x3, wr, bias, y);
+    return wb_conv3_fwd(b, g, x3, wr, bias, y, nullptr);
 }
 
 extern "C" int wb_conv3x3_bwd(WbBackend* b, const float* x, const float* weight, const float* dy, int64_t n, int64_t c, int64_t h, int64_t w,

@@ -96,6 +96,25 @@ __global__ void bn_finalize_kernel(const double* __restrict__ part, int splits, 
     }
 }
 
+// The same from plain sums (sum x, sum x^2 per channel, in double) that a producer of x accumulated while it wrote x.
+__global__ void bn_finalize_sums_kernel(const double* __restrict__ sums, int c_total, int64_t count, float eps, float momentum,
+                                        float one_minus_momentum, float* __restrict__ mean, float* __restrict__ rstd,
+                                        float* __restrict__ running_mean, float* __restrict__ running_var) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= c_total) return;
+    const double dm = sums[2 * c] / static_cast<double>(count);
+    double var = sums[2 * c + 1] / static_cast<double>(count) - dm * dm;
+    if (var < 0.0) var = 0.0;
+    float m = static_cast<float>(dm), v = static_cast<float>(var);
+    mean[c] = m;
+    rstd[c] = 1.f / sqrtf(v + eps);
+    if (running_mean) {
+        float unbiased = __fadd_rn(__fmul_rn(v, static_cast<float>(static_cast<double>(count) / static_cast<double>((count > 2 ? count : 2) - 1))), 0.f);
+        running_mean[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_mean[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(m, momentum), 0.f));
+        running_var[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_var[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(unbiased, momentum), 0.f));
+    }
+}
+
 // y = ((x - mean) * rstd) * gamma + beta, optionally ReLU.  One (n, c) plane per blockIdx.y.
 __global__ void __launch_bounds__(THREADS) bn_apply_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ mean,
                                                             const float* __restrict__ rstd, const float* __restrict__ gamma,
@@ -689,13 +708,23 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
 
 // BatchNorm2d (training statistics) -> ReLU -> MaxPool2d(2); y_left / y_right (both or neither) also receive the
 // pooled tensor shifted one column right / left, zeros shifted in (needs w / 8 in {1, 2, 4, ..., 32}, aligned buffers).
+// channel_sums (optional): per channel (sum x, sum x^2) in double, when the producer of x already has them.
 int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
                                 float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
-                                float* save_rstd, float* y_left, float* y_right) {
+                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums) {
     WB_REQUIRE(b && x && gamma && beta && y_pooled, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_fwd: height and width must be even");
     WB_REQUIRE((y_left == nullptr) == (y_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_fwd: give both shifted outputs or neither");
-    WB_TRY(wb_bn2d_stats(b, x, n, c, h * w, eps, momentum, save_mean, save_rstd, running_mean, running_var));
+    if (channel_sums) {
+        // (sum, sum of squares) per channel already accumulated by the kernel that wrote x
+        WB_REQUIRE(n * h * w > 0, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: empty input");
+        bn_finalize_sums_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(
+            channel_sums, static_cast<int>(c), n * h * w, static_cast<float>(eps), static_cast<float>(momentum), static_cast<float>(1.0 - momentum),
+            save_mean, save_rstd, running_mean, running_var);
+        WB_LAUNCH_OK(b);
+    } else {
+        WB_TRY(wb_bn2d_stats(b, x, n, c, h * w, eps, momentum, save_mean, save_rstd, running_mean, running_var));
+    }
     WbProfileScope ps(b, "bn_relu_pool_fwd");
     const int64_t total = n * c * (h / 2) * (w / 2);
     if (total == 0) return WB_OK;
@@ -728,7 +757,7 @@ extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int6
                                    const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
                                    float* save_mean, float* save_rstd) {
     return wb_bn_relu_pool_fwd_shifted(b, x, n, c, h, w, gamma, beta, running_mean, running_var, momentum, eps, y_pooled, save_mean, save_rstd,
-                                       nullptr, nullptr);
+                                       nullptr, nullptr, nullptr);
 }
 
 // Backward of BatchNorm2d -> ReLU -> MaxPool2d(2); dx_left / dx_right (both or neither) also receive dx shifted one

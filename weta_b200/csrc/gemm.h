@@ -27,7 +27,8 @@ struct WbConv3 { int64_t n, c, h, w, o; };
 bool wb_conv3_eligible(const WbConv3& g);
 int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, float* left, float* right);
 int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n);
-int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y);
+int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y,
+                 double* channel_sums);
 int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float* const x3[3], float* dwr, float* dweight);
 int wb_conv3_dgrad(WbBackend* b, const WbConv3& g, const float* const dy3[3], const float* wt, float* dx);
 

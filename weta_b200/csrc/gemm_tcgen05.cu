@@ -186,6 +186,7 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     const int tiles_m = (m + tile_m - 1) / tile_m, tiles_n = (n + BN - 1) / BN;
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
     int splits = 1;
+    if (ep.row_stats) force_splits = 1;  // row statistics come from finished values, not split-K partials
     if (force_splits > 0) splits = force_splits;
     else if (tiles * 2 <= workers && args.k_blocks >= 16) {
         splits = static_cast<int>(std::min<int64_t>(workers / tiles, args.k_blocks / 8));
@@ -265,8 +266,9 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     if (!operand_ok(A, batch) || !operand_ok(B, batch)) return WB_ERR_UNSUPPORTED;
     GemmState* st = nullptr;
     WB_TRY(get_state(be, &st));
-    // 128 x 256 tiles when the output is wide enough: half the A traffic and twice the MMA work per
-    // pipeline stage; 128 x 128 otherwise.
+    // 128 x 256 tiles when the output is wide enough: half the A traffic and twice the MMA work per pipeline
+    // stage; 128 x 128 otherwise.  (128-wide tiles for one-K-block contractions, with four accumulators in
+    // flight, measured slower than 256-wide ones.)
     const int BN = n > 128 ? 256 : 128;
     const bool pair = pair_mode(m, BN);
     const int b_box = pair ? BN / 2 : BN;  // B rows one CTA loads per K block

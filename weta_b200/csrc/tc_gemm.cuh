@@ -17,6 +17,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <type_traits>
 
 #include "common.h"
 
@@ -42,6 +43,11 @@ struct Epilogue {
     const float* bias_m;   // per output row, may be null
     int relu;
     int accumulate;        // out += result instead of out = result
+    // Optional per-row statistics of the stored values, added (atomically, in double) over the whole launch:
+    // row_stats[2*row] += sum, row_stats[2*row + 1] += sum of squares.  The caller zeroes the array.  For a
+    // convolution whose rows are output channels these are the sums batch normalisation needs, so the
+    // activation is not read again to get them.  Not available with split-K.
+    double* row_stats = nullptr;
 };
 
 struct Args {
@@ -208,8 +214,8 @@ struct SharedStorage {
     alignas(128) float stage[EPI_WARPS][32 * 32];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
-    uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
+    uint64_t tmem_full[4];   // one pair of barriers per TMEM accumulator: 512 / BN of them
+    uint64_t tmem_empty[4];
     uint32_t tmem_base;
 };
 
@@ -219,7 +225,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // Persistent kernel: gridDim.x CTAs (one per SM) walk the tile list round-robin.  Ten warps:
 //   warp 0      TMA producer (one lane)            smem ring, STAGES deep
-//   warp 1      MMA issuer (one lane); owns TMEM   two accumulators of BN columns, used alternately
+//   warp 1      MMA issuer (one lane); owns TMEM   512 / BN accumulators of BN columns, used in turn
 //   warps 2..9  epilogue: TMEM -> registers -> shared staging -> coalesced global stores
 // so the stores of tile i overlap the loads and MMAs of tile i+1.
 // A_MN: A tile arrives as BM/32 boxes of [32 m][BK k-rows]; otherwise one box of [BM rows][BK k].
@@ -236,6 +242,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
     constexpr int TILE_M = BM * CTAS;   // output rows per tile
+    constexpr int NACC = 512 / BN;      // accumulators in TMEM (all 512 columns), used round-robin: 2 or 4 tiles in flight
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_per = (args.k_blocks + args.splits - 1) / args.splits;
@@ -247,7 +254,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             mbar_init(&ss.full[s], 1);
             mbar_init(&ss.empty[s], 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < NACC; ++a) {
             mbar_init(&ss.tmem_full[a], 1);
             mbar_init(&ss.tmem_empty[a], EPI_WARPS * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
         }
@@ -255,11 +262,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     }
     if (warp == 1) {
         if constexpr (CTAS == 2) {
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(512)
                          : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
         } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(2 * BN)
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss.tmem_base)), "r"(512)
                          : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
@@ -389,8 +396,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
                 int m0, n0, batch, split, kb_begin, kb_end;
                 decode(t, m0, n0, batch, split, kb_begin, kb_end);
-                const int acc = tile_iter & 1;
-                const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
+                const int acc = tile_iter % NACC;
+                const uint32_t use = static_cast<uint32_t>(tile_iter / NACC);
                 // Wait until the epilogue has drained this accumulator (passes at once on first use).
                 if (!mbar_wait(&ss.tmem_empty[acc], (use & 1) ^ 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -431,13 +438,25 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
                             (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
         const int sw = lane & 7;  // this lane's row (lane) & 7 when writing a staged row
+        // Per-row statistics: f32 partial sums per tile, carried in double across the tiles this thread sees of
+        // the same row, flushed with two atomics when the row changes and at the end.
+        double* const row_stats = args.ep.row_stats;
+        double st1 = 0.0, st2 = 0.0;
+        int st_row = -1;
+        auto flush_stats = [&]() {
+            if (st_row >= 0 && st_row < args.m) {
+                atomicAdd(row_stats + 2 * st_row, st1);
+                atomicAdd(row_stats + 2 * st_row + 1, st2);
+            }
+            st1 = st2 = 0.0;
+        };
         int tile_iter = 0;
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
             int m0, n0, batch, split, kb_begin, kb_end;
             decode(t, m0, n0, batch, split, kb_begin, kb_end);
             m0 += rank * BM;  // this CTA's rows of the tile
-            const int acc = tile_iter & 1;
-            const uint32_t use = static_cast<uint32_t>(tile_iter >> 1);
+            const int acc = tile_iter % NACC;
+            const uint32_t use = static_cast<uint32_t>(tile_iter / NACC);
             if (!mbar_wait(&ss.tmem_full[acc], use & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int cbase = half * HALF_N;
@@ -452,74 +471,111 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
             // The loop below is fully unrolled and every TMEM load is issued unconditionally (columns past the
             // matrix edge are allocated accumulator columns, just unused), so the registers of a load in flight
             // are never merged with other values before its wait.
-            uint32_t raw[32];
-            tmem_ld32_issue(tmem_d, raw);
-#pragma unroll
-            for (int c = 0; c < HALF_N; c += 32) {
-                const int col0 = n0 + cbase + c;
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float4 r = make_float4(__uint_as_float(raw[4 * i]) + bm, __uint_as_float(raw[4 * i + 1]) + bm,
-                                           __uint_as_float(raw[4 * i + 2]) + bm, __uint_as_float(raw[4 * i + 3]) + bm);
-                    if (bias_n) {
-                        const int col = col0 + 4 * i;
-                        if (col + 0 < args.n) r.x += bias_n[col + 0];
-                        if (col + 1 < args.n) r.y += bias_n[col + 1];
-                        if (col + 2 < args.n) r.z += bias_n[col + 2];
-                        if (col + 3 < args.n) r.w += bias_n[col + 3];
-                    }
-                    if (relu) { r.x = fmaxf(r.x, 0.f); r.y = fmaxf(r.y, 0.f); r.z = fmaxf(r.z, 0.f); r.w = fmaxf(r.w, 0.f); }
-                    *reinterpret_cast<float4*>(stage + lane * 32 + ((i ^ sw) << 2)) = r;
+            // Two compiled copies of the tile drain, with and without the row statistics, so that the common case
+            // carries none of the statistics' code.
+            auto drain = [&](auto stats_tag) {
+                constexpr bool STATS = decltype(stats_tag)::value;
+                if (STATS && row != st_row) {
+                    flush_stats();
+                    st_row = row;
                 }
-                // The registers are free again: fetch the next 32 columns while this slab is stored.
-                if (c + 32 < HALF_N) {
-                    tmem_ld32_issue(tmem_d + c + 32, raw);
-                } else {
-                    // Last TMEM read of this warp for the tile: hand the accumulator back before the stores.
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.tmem_empty[acc]), 0));
-                        else mbar_arrive(&ss.tmem_empty[acc]);
-                    }
-                }
-                __syncwarp();
-                if (col0 >= args.n) continue;  // warp-uniform: nothing of this slab lies inside the matrix
-                // Each store instruction of the warp writes four 128-byte row segments.
-                const int rsub = lane >> 3, cc = lane & 7;
-                if (fast) {
-                    float* p = out_base + static_cast<int64_t>(m0 + lg * 32 + rsub) * args.ep.ldd + col0 + cc * 4;
-                    const int64_t step = static_cast<int64_t>(args.ep.ldd) * 4;
+                float2 q1[4], q2[4];
 #pragma unroll
-                    for (int it8 = 0; it8 < 8; ++it8) {
-                        const int r = it8 * 4 + rsub;
-                        *reinterpret_cast<float4*>(p + it8 * step) = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
-                    }
-                } else {
-#pragma unroll 1
-                    for (int it8 = 0; it8 < 8; ++it8) {
-                        const int r = it8 * 4 + rsub;
-                        const int grow = m0 + lg * 32 + r, gcol = col0 + cc * 4;
-                        if (grow < args.m && gcol < args.n) {
-                            float4 val = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
-                            float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
-                            if (vec_ok && gcol + 4 <= args.n) {
-                                if (args.ep.accumulate) {
-                                    float4 o = *reinterpret_cast<const float4*>(p);
-                                    val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
-                                }
-                                *reinterpret_cast<float4*>(p) = val;
+                for (int u = 0; u < 4; ++u) q1[u] = q2[u] = make_float2(0.f, 0.f);
+                const float2 bm2 = make_float2(bm, bm);
+                uint32_t raw[32];
+                tmem_ld32_issue(tmem_d, raw);
+#pragma unroll
+                for (int c = 0; c < HALF_N; c += 32) {
+                    const int col0 = n0 + cbase + c;
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        // Packed f32x2 arithmetic: one instruction per two values.
+                        float2 lo = __fadd2_rn(make_float2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1])), bm2);
+                        float2 hi = __fadd2_rn(make_float2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3])), bm2);
+                        if (bias_n) {
+                            const int col = col0 + 4 * i;
+                            if (col + 0 < args.n) lo.x += bias_n[col + 0];
+                            if (col + 1 < args.n) lo.y += bias_n[col + 1];
+                            if (col + 2 < args.n) hi.x += bias_n[col + 2];
+                            if (col + 3 < args.n) hi.y += bias_n[col + 3];
+                        }
+                        if (relu) { lo.x = fmaxf(lo.x, 0.f); lo.y = fmaxf(lo.y, 0.f); hi.x = fmaxf(hi.x, 0.f); hi.y = fmaxf(hi.y, 0.f); }
+                        if constexpr (STATS) {
+                            const int col = col0 + 4 * i;
+                            if (fast || col + 3 < args.n) {
+                                // four independent chains each: the adds of one chunk do not wait on one another
+                                q1[i & 3] = __fadd2_rn(q1[i & 3], __fadd2_rn(lo, hi));
+                                q2[i & 3] = __ffma2_rn(lo, lo, q2[i & 3]);
+                                q2[(i + 2) & 3] = __ffma2_rn(hi, hi, q2[(i + 2) & 3]);
                             } else {
-                                const float e[4] = {val.x, val.y, val.z, val.w};
-                                for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
+                                const float e[4] = {lo.x, lo.y, hi.x, hi.y};
+                                for (int j = 0; j < 4; ++j)
+                                    if (col + j < args.n) { q1[0].x += e[j]; q2[0].x += e[j] * e[j]; }
+                            }
+                        }
+                        const float4 r = make_float4(lo.x, lo.y, hi.x, hi.y);
+                        *reinterpret_cast<float4*>(stage + lane * 32 + ((i ^ sw) << 2)) = r;
+                    }
+                    // The registers are free again: fetch the next 32 columns while this slab is stored.
+                    if (c + 32 < HALF_N) {
+                        tmem_ld32_issue(tmem_d + c + 32, raw);
+                    } else {
+                        // Last TMEM read of this warp for the tile: hand the accumulator back before the stores.
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            if constexpr (CTAS == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&ss.tmem_empty[acc]), 0));
+                            else mbar_arrive(&ss.tmem_empty[acc]);
+                        }
+                    }
+                    __syncwarp();
+                    if (col0 >= args.n) continue;  // warp-uniform: nothing of this slab lies inside the matrix
+                    // Each store instruction of the warp writes four 128-byte row segments.
+                    const int rsub = lane >> 3, cc = lane & 7;
+                    if (fast) {
+                        float* p = out_base + static_cast<int64_t>(m0 + lg * 32 + rsub) * args.ep.ldd + col0 + cc * 4;
+                        const int64_t step = static_cast<int64_t>(args.ep.ldd) * 4;
+#pragma unroll
+                        for (int it8 = 0; it8 < 8; ++it8) {
+                            const int r = it8 * 4 + rsub;
+                            *reinterpret_cast<float4*>(p + it8 * step) = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int it8 = 0; it8 < 8; ++it8) {
+                            const int r = it8 * 4 + rsub;
+                            const int grow = m0 + lg * 32 + r, gcol = col0 + cc * 4;
+                            if (grow < args.m && gcol < args.n) {
+                                float4 val = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                                float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
+                                if (vec_ok && gcol + 4 <= args.n) {
+                                    if (args.ep.accumulate) {
+                                        float4 o = *reinterpret_cast<const float4*>(p);
+                                        val.x += o.x; val.y += o.y; val.z += o.z; val.w += o.w;
+                                    }
+                                    *reinterpret_cast<float4*>(p) = val;
+                                } else {
+                                    const float e[4] = {val.x, val.y, val.z, val.w};
+                                    for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = args.ep.accumulate ? p[j] + e[j] : e[j];
+                                }
                             }
                         }
                     }
+                    __syncwarp();
                 }
-                __syncwarp();
-            }
+                if constexpr (STATS) {
+                    const float2 p1 = __fadd2_rn(__fadd2_rn(q1[0], q1[1]), __fadd2_rn(q1[2], q1[3]));
+                    const float2 p2 = __fadd2_rn(__fadd2_rn(q2[0], q2[1]), __fadd2_rn(q2[2], q2[3]));
+                    st1 += p1.x + p1.y;
+                    st2 += p2.x + p2.y;
+                }
+            };
+            if (row_stats) drain(std::true_type{});
+            else drain(std::false_type{});
         }
+        if (row_stats) flush_stats();
     }
     if (!ok) {
         atomicExch(args.error_flag, 1);
@@ -531,8 +587,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
     __syncthreads();
     if constexpr (CTAS == 2) cluster_sync_all();  // neither CTA frees TMEM or leaves while its peer may still signal or write it
     if (warp == 1) {
-        if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
-        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
 

@@ -23,7 +23,7 @@
 
 int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
                                 float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
-                                float* save_rstd, float* y_left, float* y_right);
+                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums);
 int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                 const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                                 float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right);
@@ -60,6 +60,7 @@ struct Layer {
     bool dy_shift_fused = false;  // this block's BN/ReLU/pool backward writes the trainer's dy_shift
     float* x_shift[2] = {nullptr, nullptr};
     float *w_fwd = nullptr, *w_dgrad = nullptr, *dw_taps = nullptr;
+    double* stat_sums = nullptr;  // [cout][2]: sum and sum of squares of conv_out, accumulated by the convolution's epilogue
     float* out_act = nullptr;   // layer output
     int64_t out_elems = 0;      // per-sample size of the layer output
     bool relu_bwd_done = false;
@@ -159,11 +160,16 @@ struct OpTimer {
 };
 
 // D[batch][m][n] = A x B through the tensor cores, or the CUDA-core tiles when TMA cannot read an operand.
-int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int64_t span_batch = 0) {
+int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int64_t span_batch = 0,
+         bool* used_tc = nullptr) {
     const int mode = t->matmul_mode;
+    if (used_tc) *used_tc = false;
     if (mode != WB_MM_FP32 && static_cast<int64_t>(m) * n * k >= (1 << 15)) {
         int s = wb_tc_gemm(t->be, A, B, batch, m, n, k, ep, mode, 0, span_batch);
-        if (s != WB_ERR_UNSUPPORTED) return s;
+        if (s != WB_ERR_UNSUPPORTED) {
+            if (used_tc) *used_tc = true;
+            return s;
+        }
     }
     WB_REQUIRE(span_batch == 0 && !ep.accumulate, WB_ERR_UNSUPPORTED, "trainer: no CUDA-core path for this contraction");
     // CUDA-core path: describe the operands as [B, M, K] x [B, K, N] views.
@@ -331,6 +337,7 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
                 if (!first_conv) max_dcols = std::max(max_dcols, batch * L.cin * 9 * hw);
             }
             A(dev_alloc_t(t, batch * L.cout * hw, &L.conv_out));
+            A(dev_alloc_t(t, 2 * static_cast<int64_t>(L.cout), &L.stat_sums));
             A(dev_alloc_t(t, batch * L.out_elems, &L.out_act));
             A(dev_alloc_t(t, L.cout, &L.running_mean));
             A(dev_alloc_t(t, L.cout, &L.running_var));
@@ -472,6 +479,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
         if (L.kind == L_CONV) {
             // F::conv2d_ext (crates/weta-nn/src/functional.rs:84-106): im2col, W[O, C*9] x cols[n], + bias[O,1]
             const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
+            bool have_sums = false;  // the tensor-core epilogue filled L.stat_sums
             if (L.implicit) {
                 const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
                 if (!L.x_shift_fused) {
@@ -480,7 +488,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 }
                 WB_TRY(wb_conv3_weight_reorder(b, 0, t->theta + L.off_w, L.w_fwd, L.cout, L.cin));
                 const float* x3[3] = {L.x_shift[0], act, L.x_shift[1]};
-                { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(wb_conv3_fwd(b, geo, x3, L.w_fwd, t->theta + L.off_b, L.conv_out)); }
+                WB_CHECK_CUDA(cudaMemsetAsync(L.stat_sums, 0, 2 * sizeof(double) * L.cout, b->stream));
+                { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(wb_conv3_fwd(b, geo, x3, L.w_fwd, t->theta + L.off_b, L.conv_out, L.stat_sums)); }
+                have_sums = true;
             } else {
             WbView xv{};
             xv.data = const_cast<float*>(act); xv.dtype = WB_F32; xv.ndim = 4;
@@ -499,7 +509,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             }
             WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
             tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
-            { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep)); }
+            ep.row_stats = L.stat_sums;  // rows are output channels: the batch-norm sums come with the store
+            WB_CHECK_CUDA(cudaMemsetAsync(L.stat_sums, 0, 2 * sizeof(double) * L.cout, b->stream));
+            { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(gemm(t, Aw, Bc, B, L.cout, static_cast<int>(hw), static_cast<int>(ck), ep, 0, &have_sums)); }
             }
             // BatchNorm2d (train) -> ReLU -> MaxPool2d(2)
             {
@@ -509,7 +521,8 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 Layer* next = (i + 1 < nl && t->layers[i + 1].kind == L_CONV && t->layers[i + 1].x_shift_fused) ? &t->layers[i + 1] : nullptr;
                 WB_TRY(wb_bn_relu_pool_fwd_shifted(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
                                                    L.running_mean, L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd,
-                                                   next ? next->x_shift[0] : nullptr, next ? next->x_shift[1] : nullptr));
+                                                   next ? next->x_shift[0] : nullptr, next ? next->x_shift[1] : nullptr,
+                                                   have_sums ? L.stat_sums : nullptr));
             }
             act = L.out_act;
         } else if (L.kind == L_LINEAR) {
