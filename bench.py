@@ -252,12 +252,21 @@ def main():
         "L5.linear_fwd_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden), "L5.linear_wgrad_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden),
         "L5.linear_dgrad_gemm": ("tensor", 2.0 * batch * cfg.classes * cfg.hidden),
         "L0.im2col": ("hbm", in1 * 10), "L1.im2col": ("hbm", in2 * 10), "L1.col2im": ("hbm", in2 * 10),
-        # BN+ReLU+pool: forward reads x twice (statistics, apply) and writes x/4; backward reads x and dy/4 twice and writes dx
-        "L0.bn_relu_pool_fwd": ("hbm", act1 * 2.25), "L1.bn_relu_pool_fwd": ("hbm", act2 * 2.25),
-        "L0.bn_relu_pool_bwd": ("hbm", act1 * 3.5), "L1.bn_relu_pool_bwd": ("hbm", act2 * 3.5),
+        # BN+ReLU+pool forward: the statistics come from the convolution's epilogue, so x is read once and x/4 written;
+        # block 0 also writes the two column-shifted copies of its output that block 1's implicit GEMM reads.
+        # Backward reads x and dy/4 twice (sums, then dx) and writes dx; block 1 also writes dx's two shifted copies.
+        "L0.bn_relu_pool_fwd": ("hbm", act1 * 1.75), "L1.bn_relu_pool_fwd": ("hbm", act2 * 1.25),
+        "L0.bn_relu_pool_bwd": ("hbm", act1 * 3.5), "L1.bn_relu_pool_bwd": ("hbm", act2 * 5.5),
         "L2.dropout_fwd": ("hbm", 8.0 * batch * fc_in), "L2.dropout_bwd": ("hbm", 8.0 * batch * fc_in),
         "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
         "L6.adam": ("hbm", 28.0 * tr.arena_len),
+    }
+    # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures summarised under
+    # profiles/, taken at batch 512 because a full-size step is too large to capture; every one of these ops
+    # streams its tensors once per image, so the traffic is scaled by batch / 512.
+    ncu_traffic_batch512 = {
+        "L0.bn_relu_pool_bwd": 903.5e6, "L1.bn_relu_pool_bwd": 691.0e6, "L0.bn_relu_pool_fwd": 426.0e6, "L1.bn_relu_pool_fwd": 150.3e6,
+        "L1.conv_fwd_gemm": 299.1e6, "L1.conv_wgrad_gemm": 339.9e6, "L1.conv_dgrad_gemm": 455.3e6,
     }
     shares = {k: round(v[1] / total_ms, 4) for k, v in sorted(op_times.items(), key=lambda kv: -kv[1][1])}
     top_name, (top_calls, top_ms) = max(op_times.items(), key=lambda kv: kv[1][1])
@@ -272,7 +281,10 @@ def main():
     if top_name in per_op:
         o = per_op[top_name]
         roofline = {"kernel": top_name, "bound": o["bound"], "achieved": o["achieved"], "peak": tf32_peak if o["bound"] == "tensor" else peaks["hbm_gbs"],
-                    "unit": o["unit"], "frac": o["frac"], "traffic": None, "avg_ms_per_launch": o["avg_ms"], "launches": top_calls,
+                    "unit": o["unit"], "frac": o["frac"],
+                    "traffic": ncu_traffic_batch512[top_name] * batch / 512.0 if top_name in ncu_traffic_batch512 else None,
+                    "traffic_note": "bytes per launch: ncu dram read+write at batch 512, scaled by batch/512",
+                    "algorithmic": work[top_name][1], "avg_ms_per_launch": o["avg_ms"], "launches": top_calls,
                     "peak_note": (f"{peaks['source']} sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate)" if o["bound"] == "tensor"
                                   else f"{peaks['source']} copy bandwidth")}
     else:

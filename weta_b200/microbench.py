@@ -181,6 +181,26 @@ def main():
         rec(f"conv2d dX+dW+db {mname}", timeit(conv_bwd), flops=2 * fl, note="trait-call sequence of its backward")
     be.set_matmul_mode(0)
     be.gemm_check()
+
+    # ---- whole training steps of the two small named models (host batch in, loss out) ------------
+    from .core import manual_seed
+    from .trainer import FusedTrainer, cnn_specs, mlp_specs
+    from .workloads import MNIST_CNN, mlp_batch, synthetic_batch
+
+    def step_rate(name, specs, batch, in_shape, xy, mode):
+        manual_seed(42)
+        tr = FusedTrainer(be, specs, batch, in_shape, lr=1e-3, matmul_mode=mode)
+        tr.init_from_global_rng()
+        x = np.ascontiguousarray(xy[0].numpy(), dtype=np.float32)
+        y = np.ascontiguousarray(xy[1].numpy(), dtype=np.int64)
+        ms = timeit(lambda: tr.step_host(x.ctypes.data, y.ctypes.data), iters=50, warm=10)
+        results[name] = {"ms": round(ms, 4), "samples_per_s": round(batch / ms * 1e3, 1), "batch": batch}
+        print(name, results[name], flush=True)
+        tr.close()
+
+    for mode, mname in ((0, "3xtf32"), (1, "tf32")):
+        step_rate(f"mlp 784-512-256-10 train step, batch 128, {mname}", mlp_specs(), 128, (784, 1, 1), mlp_batch(128, 0, be), mode)
+        step_rate(f"cnn-mnist-422k train step, batch 64, {mname}", cnn_specs(MNIST_CNN), 64, (1, 28, 28), synthetic_batch(MNIST_CNN, 64, 0, 0, be), mode)
     results["_peaks"] = {"hbm_gbs": hbm_peak, "tf32_tflops": tf32_peak, "source": src}
     if args.out:
         os.makedirs(os.path.dirname(os.path.abspath(args.out)), exist_ok=True)
