@@ -229,6 +229,22 @@ int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int6
 int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                         const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                         float* dgamma, float* dbeta, float* dbias_conv);
+/* F::linear (crates/weta-nn/src/functional.rs:54-60): y[n, out] = x[n, in] * weight[out, in]^T + bias (bias may be
+ * NULL; relu != 0 applies ReLU in the same pass), in the backend's matmul mode.  Backward (MatmulBw,
+ * crates/weta-autograd/src/ops.rs:821-827, and the bias's sum over the batch, ops.rs:46-58): dweight[out, in] =
+ * dy^T x, dbias[out] = sum_n dy, dx[n, in] = dy * weight; any of the three outputs may be NULL. */
+int wb_linear_fwd(WbBackend* b, const float* x, const float* weight, const float* bias, int64_t n, int64_t in, int64_t out, int relu,
+                  float* y);
+int wb_linear_bwd(WbBackend* b, const float* x, const float* weight, const float* dy, int64_t n, int64_t in, int64_t out, float* dx,
+                  float* dweight, float* dbias);
+/* F::max_pool2d (functional.rs:121-130) over `planes` = N*C contiguous [h, w] planes, square kernel, no padding:
+ * y[planes, oh, ow] with weta's max rule (a NaN wins).  Backward (ops.rs:305-314): positions equal to their
+ * window's maximum share its gradient equally; overlapping windows add. */
+int wb_maxpool2d_fwd(WbBackend* b, const float* x, int64_t planes, int64_t h, int64_t w, int64_t kernel, int64_t stride, float* y);
+int wb_maxpool2d_bwd(WbBackend* b, const float* x, const float* dy, int64_t planes, int64_t h, int64_t w, int64_t kernel, int64_t stride,
+                     float* dx);
+/* UnaryBw for ReLU (ops.rs:85): dx = dy * step(y); y is the ReLU's input or output. */
+int wb_relu_bwd(WbBackend* b, const float* dy, const float* y, float* dx, int64_t n);
 /* 3x3, stride 1, padding 1 convolution over contiguous NCHW f32 tensors as an implicit GEMM on the
  * tensor cores (TF32 operands, f32 accumulation; no im2col matrix in memory).  Forward replaces the
  * chain F::conv2d_ext builds (crates/weta-nn/src/functional.rs:84-106: im2col -> matmul -> add bias,

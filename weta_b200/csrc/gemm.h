@@ -32,4 +32,8 @@ int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const
 int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float* const x3[3], float* dwr, float* dweight);
 int wb_conv3_dgrad(WbBackend* b, const WbConv3& g, const float* const dy3[3], const float* wt, float* dx);
 
+// Tensor cores first, CUDA-core tiles otherwise (dense.cu).
+int wb_gemm_dispatch(WbBackend* be, int mode, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep,
+                     int64_t span_batch, bool* used_tc);
+
 int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);

@@ -162,41 +162,7 @@ struct OpTimer {
 // D[batch][m][n] = A x B through the tensor cores, or the CUDA-core tiles when TMA cannot read an operand.
 int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep, int64_t span_batch = 0,
          bool* used_tc = nullptr) {
-    const int mode = t->matmul_mode;
-    if (used_tc) *used_tc = false;
-    if (mode != WB_MM_FP32 && static_cast<int64_t>(m) * n * k >= (1 << 15)) {
-        int s = wb_tc_gemm(t->be, A, B, batch, m, n, k, ep, mode, 0, span_batch);
-        if (s != WB_ERR_UNSUPPORTED) {
-            if (used_tc) *used_tc = true;
-            return s;
-        }
-    }
-    WB_REQUIRE(span_batch == 0 && !ep.accumulate, WB_ERR_UNSUPPORTED, "trainer: no CUDA-core path for this contraction");
-    // CUDA-core path: describe the operands as [B, M, K] x [B, K, N] views.
-    WbView a{}, b{};
-    a.data = const_cast<float*>(A.ptr); a.dtype = WB_F32; a.ndim = 3; a.offset = 0;
-    a.shape[0] = batch; a.shape[1] = m; a.shape[2] = k;
-    a.stride[0] = A.batch_stride; a.stride[1] = A.mn_major ? 1 : A.ld; a.stride[2] = A.mn_major ? A.ld : 1;
-    b.data = const_cast<float*>(B.ptr); b.dtype = WB_F32; b.ndim = 3; b.offset = 0;
-    b.shape[0] = batch; b.shape[1] = k; b.shape[2] = n;
-    b.stride[0] = B.batch_stride; b.stride[1] = B.mn_major ? B.ld : 1; b.stride[2] = B.mn_major ? 1 : B.ld;
-    WB_REQUIRE(ep.ldd == n && (batch == 1 || ep.batch_stride_d == static_cast<int64_t>(m) * n), WB_ERR_UNSUPPORTED,
-               "trainer: CUDA-core path needs a dense output");
-    WB_TRY(wb_matmul_simt(t->be, &a, &b, ep.out));
-    if (ep.bias_n || ep.bias_m || ep.relu) {
-        // bias / ReLU as one broadcast add (+ relu) over the dense result
-        WbView o{}, bias{};
-        o.data = ep.out; o.dtype = WB_F32; o.ndim = 3; o.shape[0] = batch; o.shape[1] = m; o.shape[2] = n;
-        o.stride[0] = static_cast<int64_t>(m) * n; o.stride[1] = n; o.stride[2] = 1;
-        if (ep.bias_n || ep.bias_m) {
-            bias = o;
-            bias.data = const_cast<float*>(ep.bias_n ? ep.bias_n : ep.bias_m);
-            bias.stride[0] = 0; bias.stride[1] = ep.bias_m ? 1 : 0; bias.stride[2] = ep.bias_n ? 1 : 0;
-            WB_TRY(wb_binary_into(t->be, WB_ADD, &o, &bias, ep.out));
-        }
-        if (ep.relu) WB_TRY(wb_unary_into(t->be, WB_RELU, 0.0, 0.0, &o, ep.out));
-    }
-    return WB_OK;
+    return wb_gemm_dispatch(t->be, t->matmul_mode, A, B, batch, m, n, k, ep, span_batch, used_tc);
 }
 
 // dst[j] = sum_i src[i][j] over a dense [rows, cols] matrix (a bias gradient, crates/weta-autograd/src/ops.rs:46-58).

@@ -182,6 +182,15 @@ def main():
     be.set_matmul_mode(0)
     be.gemm_check()
 
+    # ---- comparator, not weta: cuBLAS TF32 through torch.matmul on the same shapes ------------------
+    torch.backends.cuda.matmul.allow_tf32 = True
+    for nsz in ((512,) if args.quick else (512, 4096)):
+        ta = torch.randn(nsz, nsz, device="cuda")
+        tb = torch.randn(nsz, nsz, device="cuda")
+        with torch.cuda.stream(stream):
+            ms = timeit(lambda: torch.matmul(ta, tb))
+        rec(f"comparator (not weta): cuBLAS TF32 torch.matmul {nsz}^3", ms, flops=2.0 * nsz ** 3)
+
     # ---- whole training steps of the two small named models (host batch in, loss out) ------------
     from .core import manual_seed
     from .trainer import FusedTrainer, cnn_specs, mlp_specs

@@ -72,6 +72,11 @@ def _declare(lib):
         "wb_bn_relu_pool_fwd": ([P, P, i64, i64, i64, i64, P, P, P, P, f64, f64, P, P, P], i32),
         "wb_bn_relu_pool_bwd": ([P, P, P, i64, i64, i64, i64, P, P, P, P, P, P, P, P], i32),
         "wb_adam_step": ([P, P, P, P, P, i64, i64, f64, f64, f64, f64, f64, i32, f64], i32),
+        "wb_linear_fwd": ([P, P, P, P, i64, i64, i64, i32, P], i32),
+        "wb_linear_bwd": ([P, P, P, P, i64, i64, i64, P, P, P], i32),
+        "wb_maxpool2d_fwd": ([P, P, i64, i64, i64, i64, i64, P], i32),
+        "wb_maxpool2d_bwd": ([P, P, P, i64, i64, i64, i64, i64, P], i32),
+        "wb_relu_bwd": ([P, P, P, P, i64], i32),
         "wb_conv3x3_fwd": ([P, P, P, P, i64, i64, i64, i64, i64, P], i32),
         "wb_conv3x3_bwd": ([P, P, P, P, i64, i64, i64, i64, i64, P, P], i32),
     }
