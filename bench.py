@@ -244,7 +244,9 @@ def main():
     act1, act2 = 4.0 * batch * cfg.c1 * hw1, 4.0 * batch * cfg.c2 * hw2      # bytes of each conv output
     in1, in2 = 4.0 * batch * cfg.in_ch * hw1, 4.0 * batch * cfg.c1 * hw2     # bytes of each conv input
     work = {  # per launch, per rank: ("tensor", algorithmic 2*M*N*K flops) or ("hbm", algorithmic bytes moved)
-        "L0.conv_fwd_gemm": ("tensor", 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1), "L0.conv_wgrad_gemm": ("tensor", 2.0 * batch * cfg.c1 * cfg.in_ch * 9 * hw1),
+        # conv1 contracts over 27 values per output: its two GEMMs are bound by writing / reading the 128-channel
+        # activation (act1) plus the 27-row im2col matrix (9 x the input), not by the tensor cores
+        "L0.conv_fwd_gemm": ("hbm", act1 + 9.0 * in1), "L0.conv_wgrad_gemm": ("hbm", act1 + 9.0 * in1),
         "L1.conv_fwd_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2), "L1.conv_wgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
         "L1.conv_dgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
         "L3.linear_fwd_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in), "L3.linear_wgrad_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in),

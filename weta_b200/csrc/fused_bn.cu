@@ -454,98 +454,129 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
 // (dx_right[y][x] = dx[y][x+1]), zeros shifted in; the neighbour values come from the adjacent lanes, so
 // w / 4 must divide 32.
 template <bool WRITE_DX, bool SHIFT>
-__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, float* __restrict__ dx_left,
-                                                                         float* __restrict__ dx_right, const float* __restrict__ x,
-                                                                         const float* __restrict__ dyp, const float* __restrict__ mean,
-                                                                         const float* __restrict__ rstd, const float* __restrict__ gamma,
-                                                                         const float* __restrict__ beta, const float* __restrict__ dgamma,
-                                                                         const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
-                                                                         int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
-                                                                         FastDiv div_owp) {
-    const int c = blockIdx.x;
-    const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
-    float k1 = 0.f, k2 = 0.f, gr = 0.f;
-    if (WRITE_DX) { k1 = dbeta[c] * inv_count; k2 = dgamma[c] * inv_count; gr = g * r; }
+__global__ void __launch_bounds__(THREADS, 4) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, float* __restrict__ dx_left,
+                                                                            float* __restrict__ dx_right, const float* __restrict__ x,
+                                                                            const float* __restrict__ dyp, const float* __restrict__ mean,
+                                                                            const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                                            const float* __restrict__ beta, const float* __restrict__ dgamma,
+                                                                            const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
+                                                                            int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
+                                                                            FastDiv div_owp, int slabs) {
+    // Work items are (channel, slab of images) pairs, many more than blocks, walked round-robin: every SM stays
+    // equally loaded whatever the channel count.  The two windows a thread owns are computed side by side in
+    // packed f32x2 arithmetic (.x = left window, .y = right window).
     const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
     const uint32_t owp = static_cast<uint32_t>(ow >> 1), pairs = static_cast<uint32_t>(oh) * owp;
-    const int64_t per = (n_img + gridDim.y - 1) / gridDim.y;
-    const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);
-    const uint32_t items = static_cast<uint32_t>(n1 - n0) * pairs;
+    const int64_t per = (n_img + slabs - 1) / slabs;
     const int64_t xstride = static_cast<int64_t>(c_total) * h * w, gstride = static_cast<int64_t>(c_total) * pooled;
-    const float* xslab = x + (n0 * c_total + c) * h * w;
-    const float* gslab = dyp + (n0 * c_total + c) * pooled;
-    float* dslab = WRITE_DX ? dx + (n0 * c_total + c) * h * w : nullptr;
-    double s1 = 0.0, s2 = 0.0;
-    float a1 = 0.f, a2 = 0.f;
-    int flushed = 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ double red[2][THREADS / 32];
+    for (int item = blockIdx.x; item < c_total * slabs; item += gridDim.x) {
+        const int c = item / slabs, sl = item - c * slabs;
+        const float m = __ldg(mean + c), r = __ldg(rstd + c), g = __ldg(gamma + c), b = __ldg(beta + c);
+        float k1 = 0.f, k2 = 0.f, gr = 0.f;
+        if (WRITE_DX) { k1 = __ldg(dbeta + c) * inv_count; k2 = __ldg(dgamma + c) * inv_count; gr = g * r; }
+        const float2 negm2 = make_float2(-m, -m), r2 = make_float2(r, r), g2 = make_float2(g, g), b2 = make_float2(b, b);
+        const float2 negk1 = make_float2(-k1, -k1), negk2 = make_float2(-k2, -k2), gr2 = make_float2(gr, gr);
+        const int64_t n0 = min(n_img, static_cast<int64_t>(sl) * per), n1 = min(n_img, n0 + per);
+        const uint32_t items = static_cast<uint32_t>(n1 - n0) * pairs;
+        const int64_t slab_off = (n0 * c_total + c) * h * w;
+        const float* xslab = x + slab_off;
+        const float* gslab = dyp + (n0 * c_total + c) * pooled;
+        double s1 = 0.0, s2 = 0.0;
+        float2 acc1 = make_float2(0.f, 0.f), acc2 = make_float2(0.f, 0.f);
+        int flushed = 0;
 #pragma unroll 2
-    for (uint32_t base = threadIdx.x & ~31u; base < items; base += THREADS) {
-        const uint32_t j = base + (threadIdx.x & 31u);
-        const bool valid = j < items;
-        float da[4] = {0.f, 0.f, 0.f, 0.f}, db[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t oxp = 0;
-        int64_t o = 0;
-        if (valid) {
-            const uint32_t n = div_pairs.div(j), i = j - n * pairs;
-            const uint32_t oy = div_owp.div(i);
-            oxp = i - oy * owp;
-            o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
-            const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
-            const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
-            const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
-            const float va[4] = {r0.x, r0.y, r1.x, r1.y}, vb[4] = {r0.z, r0.w, r1.z, r1.w};
-            float ga[4], gb[4], xa[4], xb[4];
-            pool_window_grads(va, m, r, g, b, gy.x, ga, xa);
-            pool_window_grads(vb, m, r, g, b, gy.y, gb, xb);
-            if (WRITE_DX) {
+        for (uint32_t base = threadIdx.x & ~31u; base < items; base += THREADS) {
+            const uint32_t j = base + lane;
+            const bool valid = j < items;
+            float2 d[4];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    da[k] = gr * (ga[k] - k1 - xa[k] * k2);
-                    db[k] = gr * (gb[k] - k1 - xb[k] * k2);
-                    a1 += da[k] + db[k];
-                }
-                *reinterpret_cast<float4*>(dslab + o) = make_float4(da[0], da[1], db[0], db[1]);
-                *reinterpret_cast<float4*>(dslab + o + w) = make_float4(da[2], da[3], db[2], db[3]);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    a1 += ga[k] + gb[k];
-                    a2 += ga[k] * xa[k] + gb[k] * xb[k];
-                }
-            }
-        }
-        if (WRITE_DX && SHIFT) {
-            float p0 = __shfl_up_sync(0xffffffffu, db[1], 1), p1 = __shfl_up_sync(0xffffffffu, db[3], 1);
-            float n0v = __shfl_down_sync(0xffffffffu, da[0], 1), n1v = __shfl_down_sync(0xffffffffu, da[2], 1);
+            for (int k = 0; k < 4; ++k) d[k] = make_float2(0.f, 0.f);
+            uint32_t oxp = 0;
+            int64_t o = 0;
             if (valid) {
-                if (oxp == 0) p0 = p1 = 0.f;
-                if (oxp == owp - 1) n0v = n1v = 0.f;
-                const int64_t so = (n0 * c_total + c) * h * w + o;
-                *reinterpret_cast<float4*>(dx_left + so) = make_float4(p0, da[0], da[1], db[0]);
-                *reinterpret_cast<float4*>(dx_left + so + w) = make_float4(p1, da[2], da[3], db[2]);
-                *reinterpret_cast<float4*>(dx_right + so) = make_float4(da[1], db[0], db[1], n0v);
-                *reinterpret_cast<float4*>(dx_right + so + w) = make_float4(da[3], db[2], db[3], n1v);
+                const uint32_t n = div_pairs.div(j), i = j - n * pairs;
+                const uint32_t oy = div_owp.div(i);
+                oxp = i - oy * owp;
+                o = n * xstride + static_cast<int64_t>(2 * oy) * w + 4 * oxp;
+                const float4 r0 = *reinterpret_cast<const float4*>(xslab + o);
+                const float4 r1 = *reinterpret_cast<const float4*>(xslab + o + w);
+                const float2 gy = *reinterpret_cast<const float2*>(gslab + n * gstride + oy * ow + 2 * oxp);
+                // window positions k = 0..3: (row 0, col 0), (row 0, col 1), (row 1, col 0), (row 1, col 1)
+                const float2 v[4] = {make_float2(r0.x, r0.z), make_float2(r0.y, r0.w), make_float2(r1.x, r1.z), make_float2(r1.y, r1.w)};
+                float2 xh[4], act[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    xh[k] = __fmul2_rn(__fadd2_rn(v[k], negm2), r2);
+                    const float2 pre = __ffma2_rn(xh[k], g2, b2);
+                    act[k] = make_float2(fmaxf(pre.x, 0.f), fmaxf(pre.y, 0.f));
+                }
+                // Ties share the gradient (1/count each); a window whose maximum is 0 lies at or below the ReLU
+                // threshold everywhere and receives nothing.
+                const float bx = fmaxf(fmaxf(act[0].x, act[1].x), fmaxf(act[2].x, act[3].x));
+                const float by = fmaxf(fmaxf(act[0].y, act[1].y), fmaxf(act[2].y, act[3].y));
+                const int cx = (act[0].x == bx) + (act[1].x == bx) + (act[2].x == bx) + (act[3].x == bx);
+                const int cy = (act[0].y == by) + (act[1].y == by) + (act[2].y == by) + (act[3].y == by);
+                const float ix = cx == 1 ? 1.f : (cx == 2 ? 0.5f : (cx == 3 ? (1.f / 3.f) : 0.25f));
+                const float iy = cy == 1 ? 1.f : (cy == 2 ? 0.5f : (cy == 3 ? (1.f / 3.f) : 0.25f));
+                const float sx = bx > 0.f ? ix * gy.x : 0.f, sy = by > 0.f ? iy * gy.y : 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 go = make_float2(act[k].x == bx ? sx : 0.f, act[k].y == by ? sy : 0.f);
+                    if (WRITE_DX) {
+                        d[k] = __fmul2_rn(gr2, __ffma2_rn(xh[k], negk2, __fadd2_rn(go, negk1)));
+                        acc1 = __fadd2_rn(acc1, d[k]);
+                    } else {
+                        acc1 = __fadd2_rn(acc1, go);
+                        acc2 = __ffma2_rn(go, xh[k], acc2);
+                    }
+                }
+                if (WRITE_DX) {
+                    *reinterpret_cast<float4*>(dx + slab_off + o) = make_float4(d[0].x, d[1].x, d[0].y, d[1].y);
+                    *reinterpret_cast<float4*>(dx + slab_off + o + w) = make_float4(d[2].x, d[3].x, d[2].y, d[3].y);
+                }
+            }
+            if (WRITE_DX && SHIFT) {
+                float p0 = __shfl_up_sync(0xffffffffu, d[1].y, 1), p1 = __shfl_up_sync(0xffffffffu, d[3].y, 1);
+                float q0 = __shfl_down_sync(0xffffffffu, d[0].x, 1), q1 = __shfl_down_sync(0xffffffffu, d[2].x, 1);
+                if (valid) {
+                    if (oxp == 0) p0 = p1 = 0.f;
+                    if (oxp == owp - 1) q0 = q1 = 0.f;
+                    const int64_t so = slab_off + o;
+                    *reinterpret_cast<float4*>(dx_left + so) = make_float4(p0, d[0].x, d[1].x, d[0].y);
+                    *reinterpret_cast<float4*>(dx_left + so + w) = make_float4(p1, d[2].x, d[3].x, d[2].y);
+                    *reinterpret_cast<float4*>(dx_right + so) = make_float4(d[1].x, d[0].y, d[1].y, q0);
+                    *reinterpret_cast<float4*>(dx_right + so + w) = make_float4(d[3].x, d[2].y, d[3].y, q1);
+                }
+            }
+            if (++flushed == 32) {  // keep the f32 partial sums short
+                s1 += static_cast<double>(acc1.x) + static_cast<double>(acc1.y);
+                s2 += static_cast<double>(acc2.x) + static_cast<double>(acc2.y);
+                acc1 = acc2 = make_float2(0.f, 0.f);
+                flushed = 0;
             }
         }
-        if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
-    }
-    s1 += a1;
-    s2 += a2;
-    __shared__ double r1s[THREADS], r2s[THREADS];
-    r1s[threadIdx.x] = s1;
-    r2s[threadIdx.x] = s2;
-    __syncthreads();
-    for (int s = THREADS / 2; s > 0; s >>= 1) {
-        if (threadIdx.x < s) { r1s[threadIdx.x] += r1s[threadIdx.x + s]; r2s[threadIdx.x] += r2s[threadIdx.x + s]; }
-        __syncthreads();
-    }
-    if (threadIdx.x == 0 && part) {
-        if (WRITE_DX) {
-            part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = r1s[0];  // sum of dx: the conv bias gradient
-        } else {
-            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2] = r1s[0];
-            part[(static_cast<int64_t>(c) * gridDim.y + blockIdx.y) * 2 + 1] = r2s[0];
+        s1 += static_cast<double>(acc1.x) + static_cast<double>(acc1.y);
+        s2 += static_cast<double>(acc2.x) + static_cast<double>(acc2.y);
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) {
+            s1 += __shfl_down_sync(0xffffffffu, s1, sh);
+            s2 += __shfl_down_sync(0xffffffffu, s2, sh);
         }
+        if (lane == 0) { red[0][warp] = s1; red[1][warp] = s2; }
+        __syncthreads();
+        if (threadIdx.x == 0 && part) {
+            double t1 = 0.0, t2 = 0.0;
+            for (int q = 0; q < THREADS / 32; ++q) { t1 += red[0][q]; t2 += red[1][q]; }
+            if (WRITE_DX) {
+                part[item] = t1;  // sum of dx: the conv bias gradient
+            } else {
+                part[static_cast<int64_t>(item) * 2] = t1;
+                part[static_cast<int64_t>(item) * 2 + 1] = t2;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -769,23 +800,39 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
     WB_REQUIRE((dx_left == nullptr) == (dx_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_bwd: give both shifted outputs or neither");
     WbProfileScope ps(b, "bn_relu_pool_bwd");
-    int splits = stat_splits(b, bn_relu_pool_bwd_pair_kernel<true, false>, static_cast<int>(c), n, h * w);
-    void* s = nullptr;
-    WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 3 * sizeof(double), &s));
-    double* part = static_cast<double*>(s);
-    double* bias_part = part + static_cast<size_t>(c) * splits * 2;
-    dim3 grid(static_cast<unsigned>(c), splits);
     const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dx_left) |
                                         reinterpret_cast<uintptr_t>(dx_right)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(dy_pooled) & 7) == 0;
     WB_REQUIRE(!dx_left || (pairs && 32 % (w / 4) == 0), WB_ERR_UNSUPPORTED,
                "wb_bn_relu_pool_bwd: shifted outputs need w / 4 in {1, 2, 4, 8, 16, 32} and 16-byte aligned buffers");
+    // Paired kernels: a flat grid of one resident wave whose blocks walk (channel, slab) items, about eight per block.
+    // Scalar kernels: grid (channels, slabs), one slab per block.
+    int splits = stat_splits(b, bn_relu_pool_bwd_pair_kernel<true, false>, static_cast<int>(c), n, h * w);
+    int flat_blocks = 0;
+    if (pairs) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, bn_relu_pool_bwd_pair_kernel<true, true>, THREADS, 0) != cudaSuccess || per_sm < 1) {
+            (void)cudaGetLastError();
+            per_sm = 3;
+        }
+        flat_blocks = per_sm * b->sm_count;
+        const int64_t want = (8 * static_cast<int64_t>(flat_blocks) + c - 1) / c;
+        int64_t slabs = std::max<int64_t>(splits, std::min<int64_t>(want, n));
+        const int64_t per = (n + slabs - 1) / slabs;
+        splits = static_cast<int>((n + per - 1) / per);  // no slab is empty
+        flat_blocks = static_cast<int>(std::min<int64_t>(flat_blocks, c * splits));
+    }
+    void* s = nullptr;
+    WB_TRY(wb_scratch(b, static_cast<size_t>(c) * splits * 3 * sizeof(double), &s));
+    double* part = static_cast<double*>(s);
+    double* bias_part = part + static_cast<size_t>(c) * splits * 2;
+    dim3 grid(static_cast<unsigned>(c), splits);
     const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
     const FastDiv div_pairs(static_cast<uint32_t>(std::max<int64_t>(1, (h / 2) * (w / 4)))), div_owp(static_cast<uint32_t>(std::max<int64_t>(1, w / 4)));
     if (pairs)
-        bn_relu_pool_bwd_pair_kernel<false, false><<<grid, THREADS, 0, b->stream>>>(nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr,
-                                                                            nullptr, n, static_cast<int>(c), static_cast<int>(h),
-                                                                            static_cast<int>(w), inv_count, part, div_pairs, div_owp);
+        bn_relu_pool_bwd_pair_kernel<false, false><<<flat_blocks, THREADS, 0, b->stream>>>(
+            nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr, nullptr, n, static_cast<int>(c), static_cast<int>(h),
+            static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits);
     else
         bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
                                                                       static_cast<int>(h), static_cast<int>(w), part);
@@ -793,15 +840,13 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
     if (pairs && dx_left)
-        bn_relu_pool_bwd_pair_kernel<true, true><<<grid, THREADS, 0, b->stream>>>(dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma,
-                                                                                 beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
-                                                                                 static_cast<int>(w), inv_count,
-                                                                                 dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
+        bn_relu_pool_bwd_pair_kernel<true, true><<<flat_blocks, THREADS, 0, b->stream>>>(
+            dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
+            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits);
     else if (pairs)
-        bn_relu_pool_bwd_pair_kernel<true, false><<<grid, THREADS, 0, b->stream>>>(dx, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma,
-                                                                                  beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
-                                                                                  static_cast<int>(w), inv_count,
-                                                                                  dbias_conv ? bias_part : nullptr, div_pairs, div_owp);
+        bn_relu_pool_bwd_pair_kernel<true, false><<<flat_blocks, THREADS, 0, b->stream>>>(
+            dx, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
+            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits);
     else
         bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
                                                                    static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
