@@ -302,6 +302,12 @@ int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* us
 int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds);
 /* Adam over the whole arena; grad_scale = 1/world after a summing all-reduce, else 1. */
 int wb_trainer_adam_step(WbTrainer* t, double grad_scale);
+/* The same update range by range, on another backend handle's stream (same device), for callers that overlap
+ * the optimizer with backward: wb_trainer_begin_step advances and returns the step count, which every
+ * wb_trainer_adam_range call of that step passes.  The ranges of one step must tile the arena exactly once.
+ * No counterpart in the reference (its optimizer walks the parameter list after backward). */
+int64_t wb_trainer_begin_step(WbTrainer* t);
+int wb_trainer_adam_range(WbTrainer* t, WbBackend* on, int64_t offset, int64_t len, int64_t step, double grad_scale);
 /* One whole step from host memory: upload batch, forward/backward/Adam, download the loss, wait. */
 int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,
                          float* host_loss);

@@ -203,6 +203,97 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile(TO* __restrict__ out, co
     }
 }
 
+// Four-wide variant of ew_tile for 4-byte element types: 128-bit global loads along P for the transposed operands
+// and 128-bit global loads / stores along L for everything else; the 4 x 4 transposition happens through the same
+// padded shared-memory tile with scalar accesses (at most two lanes per bank).  Needs every size, stride and offset
+// involved to be a multiple of 4 elements and 16-byte aligned base pointers (checked by the launcher).
+template <class TI, class TO, int NOPS, class F>
+__global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, const TI* __restrict__ a, const TI* __restrict__ b, Plan p,
+                                                         int pd, int tmode_a, int tmode_b, uint32_t tiles_p, uint32_t tiles_l, F f) {
+    static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "ew_tile4 is for 4-byte elements");
+    extern __shared__ __align__(16) unsigned char tile_raw[];
+    TI(*sm)[TILE][TILE + 1] = reinterpret_cast<TI(*)[TILE][TILE + 1]>(tile_raw);  // sm[o][p][l]
+    const int L = p.nd - 1;
+    uint32_t bid = blockIdx.x;
+    const uint32_t tl = bid % tiles_l;
+    bid /= tiles_l;
+    const uint32_t tp = bid % tiles_p;
+    bid /= tiles_p;
+    int64_t oa = p.off[0], ob = p.off[1], oo = 0, s = p.size[L], ostride_p = 0;
+    for (int d = L - 1; d >= 0; --d) {
+        const uint32_t sz = static_cast<uint32_t>(p.size[d]);
+        if (d == pd) {
+            ostride_p = s;
+        } else {
+            const uint32_t q = bid / sz, c = bid - q * sz;
+            bid = q;
+            oa += c * p.st[0][d];
+            if (NOPS > 1) ob += c * p.st[1][d];
+            oo += c * s;
+        }
+        s *= sz;
+    }
+    const int64_t p0 = static_cast<int64_t>(tp) * TILE, l0 = static_cast<int64_t>(tl) * TILE;
+    const int64_t szp = p.size[pd], szl = p.size[L];
+    const int64_t sap = p.st[0][pd], sal = p.st[0][L], sbp = p.st[1][pd], sbl = p.st[1][L];
+    using V4 = Pack<TI, 4>;
+    // Stage transposed operands: a thread loads 4 consecutive P positions of one L row (the operand's unit-stride dim is P).
+    auto stage = [&](const TI* __restrict__ src, int64_t base, int64_t sl, int o) {
+#pragma unroll
+        for (int k = 0; k < (TILE * TILE / 4) / TILE_THREADS; ++k) {
+            const int idx = threadIdx.x + k * TILE_THREADS;
+            const int lj = idx / (TILE / 4), p4 = idx % (TILE / 4);
+            const int64_t pi = p0 + 4 * p4, li = l0 + lj;
+            if (pi < szp && li < szl) {
+                const V4 v = *reinterpret_cast<const V4*>(src + base + pi + li * sl);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sm[o][4 * p4 + i][lj] = v.v[i];
+            }
+        }
+    };
+    if (tmode_a) stage(a, oa, sal, 0);
+    if constexpr (NOPS > 1) {
+        if (tmode_b) stage(b, ob, sbl, 1);
+    }
+    __syncthreads();
+    // Compute: a thread produces 4 consecutive L positions of one P row.
+#pragma unroll
+    for (int k = 0; k < (TILE * TILE / 4) / TILE_THREADS; ++k) {
+        const int idx = threadIdx.x + k * TILE_THREADS;
+        const int pj = idx / (TILE / 4), l4 = idx % (TILE / 4);
+        const int64_t pi = p0 + pj, li = l0 + 4 * l4;
+        if (pi >= szp || li >= szl) continue;
+        V4 x, y;
+        if (tmode_a) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x.v[i] = sm[0][pj][4 * l4 + i];
+        } else if (sal == 1) {
+            x = *reinterpret_cast<const V4*>(a + oa + pi * sap + li);
+        } else {  // broadcast along L
+            const TI v = a[oa + pi * sap];
+            x.v[0] = x.v[1] = x.v[2] = x.v[3] = v;
+        }
+        Pack<TO, 4> r;
+        if constexpr (NOPS > 1) {
+            if (tmode_b) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) y.v[i] = sm[1][pj][4 * l4 + i];
+            } else if (sbl == 1) {
+                y = *reinterpret_cast<const V4*>(b + ob + pi * sbp + li);
+            } else {
+                const TI v = b[ob + pi * sbp];
+                y.v[0] = y.v[1] = y.v[2] = y.v[3] = v;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i], y.v[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i]);
+        }
+        *reinterpret_cast<Pack<TO, 4>*>(out + oo + pi * ostride_p + li) = r;
+    }
+}
+
 // ---- host-side launcher -------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -274,8 +365,39 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
                     attr_done = true;
                 }
             }
-            kern<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
-                                                                                 static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), f);
+            // 128-bit variant: 4-byte elements, every size / stride / offset a multiple of 4 where a vector is formed
+            bool v4 = false;
+            if constexpr (sizeof(TI) == 4 && sizeof(TO) == 4) {
+                v4 = wp.size[pd] % 4 == 0 && wp.size[L] % 4 == 0 && aligned16(out);
+                const TI* ptrs[2] = {a, b};
+                for (int o = 0; o < NOPS && v4; ++o) {
+                    v4 = aligned16(ptrs[o]) && wp.off[o] % 4 == 0;
+                    for (int d = 0; d <= L && v4; ++d) {
+                        const int64_t sd = wp.st[o][d];
+                        // the dim the vector runs along has stride 1 (or 0 for a broadcast read along L); all others step by multiples of 4
+                        const bool vec_dim = tmode[o] ? d == pd : d == L;
+                        if (vec_dim) v4 = sd == 1 || (!tmode[o] && sd == 0);
+                        else v4 = sd % 4 == 0;
+                    }
+                }
+            }
+            if (v4) {
+                if constexpr (sizeof(TI) == 4 && sizeof(TO) == 4) {
+                    auto kern4 = ew_tile4<TI, TO, NOPS, F>;
+                    if (tile_smem > 48 * 1024) {
+                        static bool attr4_done = false;
+                        if (!attr4_done) {
+                            WB_CHECK_CUDA(cudaFuncSetAttribute(kern4, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem)));
+                            attr4_done = true;
+                        }
+                    }
+                    kern4<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
+                                                                                          static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), f);
+                }
+            } else {
+                kern<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
+                                                                                     static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), f);
+            }
             WB_LAUNCH_OK(be);
             return WB_OK;
         }

@@ -628,6 +628,21 @@ extern "C" int wb_trainer_adam_step(WbTrainer* t, double grad_scale) {
                         grad_scale);
 }
 
+// Adam over one range of the arena, issued on another backend handle's stream (same device): a data-parallel
+// caller updates a bucket as soon as its gradient sum has arrived, while backward continues on the trainer's
+// stream.  wb_trainer_begin_step advances and returns the step count t that every range of one step passes.
+extern "C" int64_t wb_trainer_begin_step(WbTrainer* t) { return ++t->t; }
+
+extern "C" int wb_trainer_adam_range(WbTrainer* t, WbBackend* on, int64_t offset, int64_t len, int64_t step, double grad_scale) {
+    WB_REQUIRE(t && on, WB_ERR_INVALID, "wb_trainer_adam_range: null pointer");
+    WB_REQUIRE(on->ordinal == t->be->ordinal, WB_ERR_INVALID, "wb_trainer_adam_range: the stream's backend is on another device");
+    WB_REQUIRE(offset >= 0 && len >= 0 && offset + len <= t->n_params && step >= 1, WB_ERR_INVALID, "wb_trainer_adam_range: bad range");
+    if (len == 0) return WB_OK;
+    const WbAdamConfig& a = t->adam;
+    return wb_adam_step(on, t->theta + offset, t->grad + offset, t->m + offset, t->v + offset, len, step, a.lr, a.beta1, a.beta2, a.eps,
+                        a.weight_decay, a.decoupled, grad_scale);
+}
+
 // The call a user makes per step: host batch in, loss out.  Copies the batch from (pinned) host
 // memory, runs forward/backward/Adam and reads the loss back; waits for the stream.
 extern "C" int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,

@@ -72,6 +72,8 @@ def _declare(lib):
         "wb_bn_relu_pool_fwd": ([P, P, i64, i64, i64, i64, P, P, P, P, f64, f64, P, P, P], i32),
         "wb_bn_relu_pool_bwd": ([P, P, P, i64, i64, i64, i64, P, P, P, P, P, P, P, P], i32),
         "wb_adam_step": ([P, P, P, P, P, i64, i64, f64, f64, f64, f64, f64, i32, f64], i32),
+        "wb_trainer_begin_step": ([P], i64),
+        "wb_trainer_adam_range": ([P, P, i64, i64, i64, f64], i32),
         "wb_linear_fwd": ([P, P, P, P, i64, i64, i64, i32, P], i32),
         "wb_linear_bwd": ([P, P, P, P, i64, i64, i64, P, P, P], i32),
         "wb_maxpool2d_fwd": ([P, P, i64, i64, i64, i64, i64, P], i32),
@@ -271,7 +273,8 @@ class DataParallelTrainer:
 
     The reference has no multi-GPU path; this adds the one exchange a data-parallel step needs.
     Gradients are summed with NCCL (`torch.distributed`) on a side stream as soon as a bucket of the
-    arena is final, while backward continues on the compute stream; Adam then applies 1/world.
+    arena is final, and that bucket's Adam update (with 1/world) follows on a third stream, both while
+    backward continues on the compute stream; the next step waits for the last update.
     BatchNorm statistics stay per rank, as they would in the reference (it has no SyncBN).
     """
 
@@ -284,6 +287,11 @@ class DataParallelTrainer:
         self.world = world_size
         self.stream = compute_stream
         self.comm_stream = torch.cuda.Stream() if world_size > 1 else None
+        self.adam_stream = torch.cuda.Stream() if world_size > 1 else None
+        # a second handle on the same device whose kernels go to the optimizer stream
+        self.adam_backend = B200Backend(trainer.be.ordinal, self.adam_stream.cuda_stream) if world_size > 1 else None
+        self.step_t = 0
+        self.covered = 0
         self.works = []
         self.grad_view = torch.as_tensor(_DevicePtr(trainer.grads_ptr(), trainer.arena_len), device=f"cuda:{trainer.be.ordinal}")
         self.bucketer = GradBucketer(self._all_reduce_range, bucket_elems)
@@ -297,19 +305,28 @@ class DataParallelTrainer:
         ev.record(self.stream)                   # everything queued so far, i.e. this bucket's gradients
         self.comm_stream.wait_event(ev)
         with torch.cuda.stream(self.comm_stream):
-            self.works.append(self.dist.all_reduce(self.grad_view[start:start + length], op=self.dist.ReduceOp.SUM, async_op=True))
+            work = self.dist.all_reduce(self.grad_view[start:start + length], op=self.dist.ReduceOp.SUM, async_op=True)
+        with torch.cuda.stream(self.adam_stream):
+            work.wait()  # orders the optimizer stream after this bucket's sum
+            tr = self.tr
+            tr.be.check(tr.lib.wb_trainer_adam_range(tr.handle, self.adam_backend.handle, start, length, self.step_t, 1.0 / self.world))
+        self.works.append(work)
+        self.covered += length
 
     def forward_backward_step(self, seeds=None):
-        """forward, backward with overlapped all-reduce, Adam.  Inputs must already be staged."""
+        """forward, backward with overlapped all-reduce and per-bucket Adam.  Inputs must already be staged."""
+        if self.world == 1:
+            self.tr.forward_backward(seeds)
+            self.tr.adam_step(1.0)
+            return
+        self.step_t = self.tr.lib.wb_trainer_begin_step(self.tr.handle)
+        self.covered = 0
         self.tr.forward_backward(seeds)
-        if self.world > 1:
-            self.bucketer.flush()
-            with self.torch.cuda.stream(self.comm_stream):
-                for w in self.works:
-                    w.wait()
-            self.works.clear()
-            self.stream.wait_stream(self.comm_stream)
-        self.tr.adam_step(1.0 / self.world)
+        self.bucketer.flush()
+        if self.covered != self.tr.arena_len:
+            raise RuntimeError(f"gradient buckets covered {self.covered} of {self.tr.arena_len} arena elements")
+        self.works.clear()
+        self.stream.wait_stream(self.adam_stream)  # the next step reads the updated parameters
 
     def step_host(self, x_pinned, y_pinned, seeds=None) -> float:
         """One step from pinned host tensors: upload, forward/backward (+ all-reduce), Adam, loss read-back."""
