@@ -154,6 +154,57 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __
     if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;
 }
 
+// The same with 128-bit accesses: cols a multiple of 4 (so is dz_pitch), rows 16-byte aligned; lane l holds the
+// float4 groups l, l + 32, ... of its row (Q of them).
+template <int Q>
+__global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+                                                                   int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
+                                                                   float* __restrict__ row_loss, float gscale) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4* zr = reinterpret_cast<const float4*>(z + row * cols);
+    const int groups = cols >> 2;
+    float4 v[Q];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < Q; ++k) {
+        const int q = lane + 32 * k;
+        v[k] = q < groups ? zr[q] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        mx = fmaxf(fmaxf(mx, fmaxf(v[k].x, v[k].y)), fmaxf(v[k].z, v[k].w));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < Q; ++k)
+        if (lane + 32 * k < groups) s += (expf(v[k].x - mx) + expf(v[k].y - mx)) + (expf(v[k].z - mx) + expf(v[k].w - mx));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    const float lse = logf(s) + mx;
+    const int64_t y = labels[row];
+#pragma unroll
+    for (int k = 0; k < Q; ++k) {
+        const int q = lane + 32 * k;
+        if (q < groups) {
+            const int c = 4 * q;
+            const float4 p = make_float4(expf(v[k].x - lse), expf(v[k].y - lse), expf(v[k].z - lse), expf(v[k].w - lse));
+            if (probs) reinterpret_cast<float4*>(probs + row * cols)[q] = p;
+            if (dz)
+                reinterpret_cast<float4*>(dz + row * dz_pitch)[q] =
+                    make_float4((p.x - (c == y ? 1.f : 0.f)) * gscale, (p.y - (c + 1 == y ? 1.f : 0.f)) * gscale,
+                                (p.z - (c + 2 == y ? 1.f : 0.f)) * gscale, (p.w - (c + 3 == y ? 1.f : 0.f)) * gscale);
+            if (row_loss && y >= c && y < c + 4) {
+                const int j = static_cast<int>(y) - c;
+                const float zy = j == 0 ? v[k].x : (j == 1 ? v[k].y : (j == 2 ? v[k].z : v[k].w));
+                row_loss[row] = -(zy - lse);
+            }
+        }
+    }
+    if (row_loss && lane == 0 && (y < 0 || y >= cols)) row_loss[row] = 0.f;
+    if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;
+}
+
 // mean of row_loss in a fixed order (one block; rows is a batch size).
 __global__ void __launch_bounds__(THREADS) mean_kernel(const float* __restrict__ v, int64_t n, float* __restrict__ out) {
     __shared__ double part[THREADS];
@@ -176,11 +227,7 @@ struct AdamK {
     int first, decoupled, has_wd, scale_grad;
 };
 
-__global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta, const float* __restrict__ grad, float* __restrict__ m,
-                                                        float* __restrict__ v, int64_t n, AdamK k) {
-    int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
-    if (i >= n) return;
-    float g = grad[i], th = theta[i];
+__device__ __forceinline__ void adam_one(float& th, float g, float& mi, float& vi, const AdamK& k) {
     if (k.scale_grad) g = g * k.gscale;
     if (k.has_wd) {
         if (k.decoupled) th = th * k.decay_mul + 0.f;
@@ -188,13 +235,40 @@ __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta
     }
     float gm = g * k.omb1 + 0.f;
     float gv = (g * g) * k.omb2 + 0.f;
-    float mn = k.first ? gm : (m[i] * k.b1 + 0.f) + gm;
-    float vn = k.first ? gv : (v[i] * k.b2 + 0.f) + gv;
+    float mn = k.first ? gm : (mi * k.b1 + 0.f) + gm;
+    float vn = k.first ? gv : (vi * k.b2 + 0.f) + gv;
     float den = (sqrtf(vn) * k.inv_sqrt_bc2 + 0.f) * 1.f + k.eps;
     th = th - ((mn / den) * k.step_size + 0.f);
-    theta[i] = th;
-    m[i] = mn;
-    v[i] = vn;
+    mi = mn;
+    vi = vn;
+}
+
+// One thread per four elements (128-bit accesses); the last, partial group is done element by element.
+__global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta, const float* __restrict__ grad, float* __restrict__ m,
+                                                        float* __restrict__ v, int64_t n, AdamK k, int vec) {
+    const int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
+    if (i >= n) return;
+    if (vec && i + 4 <= n) {
+        float4 th = *reinterpret_cast<const float4*>(theta + i);
+        const float4 g = *reinterpret_cast<const float4*>(grad + i);
+        float4 mi = k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(m + i);
+        float4 vi = k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(v + i);
+        adam_one(th.x, g.x, mi.x, vi.x, k);
+        adam_one(th.y, g.y, mi.y, vi.y, k);
+        adam_one(th.z, g.z, mi.z, vi.z, k);
+        adam_one(th.w, g.w, mi.w, vi.w, k);
+        *reinterpret_cast<float4*>(theta + i) = th;
+        *reinterpret_cast<float4*>(m + i) = mi;
+        *reinterpret_cast<float4*>(v + i) = vi;
+    } else {
+        for (int64_t j = i; j < n && j < i + 4; ++j) {
+            float th = theta[j], mi = k.first ? 0.f : m[j], vi = k.first ? 0.f : v[j];
+            adam_one(th, grad[j], mi, vi, k);
+            theta[j] = th;
+            m[j] = mi;
+            v[j] = vi;
+        }
+    }
 }
 
 // Smallest 53-bit k whose uniform value (f32)((double)k * 2^-53) exceeds f32(p); 2^53 if none does.
@@ -280,7 +354,11 @@ int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labe
     const unsigned grid = static_cast<unsigned>((threads + THREADS - 1) / THREADS);
     const float gscale = static_cast<float>(upstream * (1.0 / static_cast<double>(rows)));
     const int ic = static_cast<int>(cols), ip = static_cast<int>(dz_pitch);
-    if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    const bool v4 = cols % 4 == 0 && dz_pitch % 4 == 0 &&
+                    ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(probs) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0;
+    if (v4 && cols > 32 && cols <= 128) softmax_ce_reg4_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    else if (v4 && cols > 128 && cols <= 1024) softmax_ce_reg4_kernel<8><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    else if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
     else if (cols <= 128) softmax_ce_reg_kernel<4><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
     else if (cols <= 1024) softmax_ce_reg_kernel<32><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
     else softmax_ce_kernel<<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
@@ -319,7 +397,10 @@ extern "C" int wb_adam_step(WbBackend* b, float* theta, const float* grad, float
     k.decoupled = decoupled;
     k.has_wd = weight_decay != 0.0;
     k.scale_grad = grad_scale != 1.0;
-    adam_kernel<<<static_cast<unsigned>((n + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(theta, grad, m, v, n, k);
+    const int vec = ((reinterpret_cast<uintptr_t>(theta) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
+                      reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+    const int64_t groups = (n + 3) / 4;
+    adam_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(theta, grad, m, v, n, k, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
