@@ -292,7 +292,11 @@ float* wb_trainer_grads(WbTrainer* t);
 float* wb_trainer_exp_avg(WbTrainer* t);
 float* wb_trainer_exp_avg_sq(WbTrainer* t);
 float* wb_trainer_input(WbTrainer* t);       /* staged batch: f32 [batch, in_c*in_h*in_w] */
-int64_t* wb_trainer_labels(WbTrainer* t);    /* staged labels: i64 [batch] */
+int64_t* wb_trainer_labels(WbTrainer* t);
+/* Reads the following steps' batch from caller-owned device buffers instead (the slots of a double-buffered
+ * upload); NULL, NULL restores the trainer's own staging buffers.  No counterpart in the reference, which uploads
+ * each batch synchronously (`Tensor::to`, crates/weta-tensor/src/tensor.rs:235-240). */
+int wb_trainer_set_input(WbTrainer* t, float* x, int64_t* y);    /* staged labels: i64 [batch] */
 float* wb_trainer_loss_ptr(WbTrainer* t);    /* device scalar written by forward_backward */
 int wb_trainer_num_tensors(const WbTrainer* t);
 int wb_trainer_tensor_range(const WbTrainer* t, int index, int64_t* offset, int64_t* len);

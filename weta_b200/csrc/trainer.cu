@@ -75,8 +75,10 @@ struct WbTrainer {
     std::vector<Layer> layers;
     int64_t n_params = 0;
     float *theta = nullptr, *grad = nullptr, *m = nullptr, *v = nullptr;
-    float* x_in = nullptr;       // staged input  [B, in_elems]
+    float* x_in = nullptr;       // staged input  [B, in_elems]: the trainer's own buffer unless wb_trainer_set_input replaced it
     int64_t* y_in = nullptr;     // staged labels [B]
+    float* own_x_in = nullptr;
+    int64_t* own_y_in = nullptr;
     float* dlogits = nullptr;    // [B, dl_pitch]: rows padded to a multiple of 4 floats for TMA
     int64_t dl_pitch = 0;
     float* loss_dev = nullptr;
@@ -267,6 +269,8 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
     A(dev_alloc_t(t, t->n_params, &t->v));
     A(dev_alloc_t(t, batch * t->in_elems, &t->x_in));
     A(dev_alloc_t(t, batch, &t->y_in));
+    t->own_x_in = t->x_in;
+    t->own_y_in = t->y_in;
     t->dl_pitch = (t->classes + 3) / 4 * 4;
     A(dev_alloc_t(t, batch * t->dl_pitch, &t->dlogits));
     A(dev_alloc_t(t, 4, &t->loss_dev));
@@ -393,6 +397,15 @@ extern "C" float* wb_trainer_exp_avg(WbTrainer* t) { return t->m; }
 extern "C" float* wb_trainer_exp_avg_sq(WbTrainer* t) { return t->v; }
 extern "C" float* wb_trainer_input(WbTrainer* t) { return t->x_in; }
 extern "C" int64_t* wb_trainer_labels(WbTrainer* t) { return t->y_in; }
+// Makes the next steps read their batch from caller-owned device buffers ([B, in_elems] f32 and [B] i64), e.g. the
+// slots of a double-buffered upload pipeline; null pointers restore the trainer's own staging buffers.
+extern "C" int wb_trainer_set_input(WbTrainer* t, float* x, int64_t* y) {
+    WB_REQUIRE(t && ((x == nullptr) == (y == nullptr)), WB_ERR_INVALID, "wb_trainer_set_input: give both buffers or neither");
+    WB_REQUIRE(!x || (reinterpret_cast<uintptr_t>(x) & 15) == 0, WB_ERR_INVALID, "wb_trainer_set_input: the image buffer must be 16-byte aligned");
+    t->x_in = x ? x : t->own_x_in;
+    t->y_in = y ? y : t->own_y_in;
+    return WB_OK;
+}
 extern "C" float* wb_trainer_loss_ptr(WbTrainer* t) { return t->loss_dev; }
 extern "C" int wb_trainer_num_tensors(const WbTrainer* t) { return static_cast<int>(t->param_table.size()); }
 

@@ -72,6 +72,7 @@ def _declare(lib):
         "wb_bn_relu_pool_fwd": ([P, P, i64, i64, i64, i64, P, P, P, P, f64, f64, P, P, P], i32),
         "wb_bn_relu_pool_bwd": ([P, P, P, i64, i64, i64, i64, P, P, P, P, P, P, P, P], i32),
         "wb_adam_step": ([P, P, P, P, P, i64, i64, f64, f64, f64, f64, f64, i32, f64], i32),
+        "wb_trainer_set_input": ([P, P, P], i32),
         "wb_trainer_begin_step": ([P], i64),
         "wb_trainer_adam_range": ([P, P, i64, i64, i64, f64], i32),
         "wb_linear_fwd": ([P, P, P, P, i64, i64, i64, i32, P], i32),
@@ -335,3 +336,56 @@ class DataParallelTrainer:
         be.check(be.lib.wb_upload_async(be.handle, y_pinned.data_ptr(), ctypes.c_void_p(tr.labels_ptr()), y_pinned.numel() * 8))
         self.forward_backward_step(seeds)
         return tr.loss()
+
+
+class PrefetchingStepper:
+    """Feeds host batches to a DataParallelTrainer with the upload of batch i+1 overlapped with step i.
+
+    Two device slots; `submit` enqueues the host-to-device copy of one pinned batch on a copy stream, `step` runs one
+    training step on the oldest submitted batch and returns its loss (a device-to-host read that waits for the
+    step).  The copy into a slot waits for the step that last read it; the step waits for its slot's copy.
+    """
+
+    def __init__(self, dp: DataParallelTrainer):
+        import torch
+
+        self.torch, self.dp = torch, dp
+        tr = dp.tr
+        dev = f"cuda:{tr.be.ordinal}"
+        n_in = tr.batch * int(np.prod(tr.in_shape))
+        self.slots = [(torch.empty(n_in, dtype=torch.float32, device=dev), torch.empty(tr.batch, dtype=torch.int64, device=dev)) for _ in range(2)]
+        self.copy_stream = torch.cuda.Stream()
+        self.ready = [torch.cuda.Event() for _ in range(2)]
+        self.consumed = [torch.cuda.Event() for _ in range(2)]
+        for ev in self.consumed:
+            ev.record(dp.stream)
+        self.submitted = 0
+        self.stepped = 0
+
+    def submit(self, x_pinned, y_pinned):
+        if self.submitted - self.stepped >= 2:
+            raise RuntimeError("both slots hold batches that have not been stepped yet")
+        slot = self.submitted % 2
+        with self.torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.consumed[slot])
+            self.slots[slot][0].copy_(x_pinned, non_blocking=True)
+            self.slots[slot][1].copy_(y_pinned, non_blocking=True)
+            self.ready[slot].record(self.copy_stream)
+        self.submitted += 1
+
+    def step(self, seeds=None) -> float:
+        if self.stepped >= self.submitted:
+            raise RuntimeError("no submitted batch to step on")
+        slot = self.stepped % 2
+        tr = self.dp.tr
+        self.dp.stream.wait_event(self.ready[slot])
+        x, y = self.slots[slot]
+        tr.be.check(tr.lib.wb_trainer_set_input(tr.handle, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr())))
+        self.dp.forward_backward_step(seeds)
+        self.consumed[slot].record(self.dp.stream)
+        self.stepped += 1
+        return tr.loss()
+
+    def close(self):
+        tr = self.dp.tr
+        tr.be.check(tr.lib.wb_trainer_set_input(tr.handle, None, None))
