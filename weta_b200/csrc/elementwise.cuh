@@ -11,6 +11,7 @@
 // All arithmetic is done by a functor, so each op compiles to straight-line code.
 #pragma once
 
+#include <atomic>
 #include "common.h"
 
 namespace ew {
@@ -359,10 +360,11 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
             constexpr size_t tile_smem = sizeof(TI) * NOPS * TILE * (TILE + 1);
             auto kern = ew_tile<TI, TO, NOPS, F>;
             if (tile_smem > 48 * 1024) {
-                static bool attr_done = false;  // one flag per instantiation
-                if (!attr_done) {
+                static std::atomic<uint64_t> attr_done{0};  // one flag per instantiation and device ordinal
+                const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
+                if (!(attr_done.load(std::memory_order_acquire) & bit)) {
                     WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem)));
-                    attr_done = true;
+                    attr_done.fetch_or(bit, std::memory_order_release);
                 }
             }
             // 128-bit variant: 4-byte elements, every size / stride / offset a multiple of 4 where a vector is formed
@@ -385,10 +387,11 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
                 if constexpr (sizeof(TI) == 4 && sizeof(TO) == 4) {
                     auto kern4 = ew_tile4<TI, TO, NOPS, F>;
                     if (tile_smem > 48 * 1024) {
-                        static bool attr4_done = false;
-                        if (!attr4_done) {
+                        static std::atomic<uint64_t> attr4_done{0};
+                        const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
+                        if (!(attr4_done.load(std::memory_order_acquire) & bit)) {
                             WB_CHECK_CUDA(cudaFuncSetAttribute(kern4, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem)));
-                            attr4_done = true;
+                            attr4_done.fetch_or(bit, std::memory_order_release);
                         }
                     }
                     kern4<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],

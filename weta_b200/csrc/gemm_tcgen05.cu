@@ -8,6 +8,8 @@
 // (matmul_simt.cu) for f64, tiny problems and layouts TMA cannot describe.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "tc_gemm.cuh"
 #include "gemm.h"
 
@@ -134,10 +136,12 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
     constexpr size_t smem = sizeof(SS) + 1024;
     static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
     auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS>;
-    static bool attr_done = false;
-    if (!attr_done) {
+    // The attribute belongs to the device's context: one flag per device ordinal and instantiation.
+    static std::atomic<uint64_t> attr_done{0};
+    const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
+    if (!(attr_done.load(std::memory_order_acquire) & bit)) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        attr_done = true;
+        attr_done.fetch_or(bit, std::memory_order_release);
     }
     if (CTAS == 1) {
         kern<<<grid, tc::THREADS, smem, be->stream>>>(args);
