@@ -83,6 +83,9 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
 
 
+WORKLOAD = "data-parallel wide CNN train step (conv3-128, conv128-256, fc16384-1024-10; BN, ReLU, maxpool, dropout 0.25)"
+
+
 def cpu_reference_run(steps: int, warmup: int, sample_batch: int):
     """The reference's CPU path (the oracle restating weta-cpu, driven op by op like the reference's
     own autograd would) on a bounded sample of the workload, with every host thread."""
@@ -113,7 +116,10 @@ def run_reference(args):
     r = cpu_reference_run(steps, warmup, args.cpu_batch)
     line = {"impl": "reference", "metric": METRIC, "value": r["value"], "unit": "samples/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
             "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": "wide CNN 3x32x32 (conv128-conv256-fc1024), CPU sample", "global_batch": args.cpu_batch},
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": args.global_batch, "image": "3x32x32", "optimizer": "Adam lr 1e-3",
+                       "sample": f"each step is one optimizer step on a {args.cpu_batch}-sample batch of this workload (a bounded sample: a full "
+                                 f"{args.global_batch}-sample step takes minutes on the host cores); samples/s is what is compared"},
             "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": r["value"], "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -318,7 +324,7 @@ def main():
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (TF32 contractions)",
         "data": "synthetic",
-        "config": {"workload": "data-parallel wide CNN train step (conv3-128, conv128-256, fc16384-1024-10; BN, ReLU, maxpool, dropout 0.25)",
+        "config": {"workload": WORKLOAD,
                    "global_batch": gb, "per_gpu_batch": batch, "image": "3x32x32", "params": cfg.num_params(), "optimizer": "Adam lr 1e-3",
                    "parallelism": f"dp{world}", "l2": "per-step working set is several GB, far larger than the 126 MB L2; two batches alternate",
                    "step": "upload/stage + forward + cross-entropy + backward + all-reduce + Adam",
