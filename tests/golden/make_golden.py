@@ -16,7 +16,9 @@ from safetensors.numpy import load_file
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/weta")
+    root = sys.argv[1]
     src = os.path.join(root, "crates/weta/tests/fixtures/reference.safetensors")
     tensors = load_file(src)
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_fixture.npz")
