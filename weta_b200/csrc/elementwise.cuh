@@ -205,15 +205,18 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile(TO* __restrict__ out, co
 }
 
 // Four-wide variant of ew_tile for 4-byte element types: 128-bit global loads along P for the transposed operands
-// and 128-bit global loads / stores along L for everything else; the 4 x 4 transposition happens through the same
-// padded shared-memory tile with scalar accesses (at most two lanes per bank).  Needs every size, stride and offset
-// involved to be a multiple of 4 elements and 16-byte aligned base pointers (checked by the launcher).
+// and 128-bit global loads / stores along L for everything else.  The tile sits in shared memory as sm[p][64] with
+// the 16-byte group g = l / 4 of row p stored at group g ^ ((p / 4) & 7): the scalar stores of the staging phase (a
+// warp covers 8 float4 columns of P by 4 rows of L) and the 128-bit loads of the compute phase are both free of bank
+// conflicts.  Needs every size, stride and offset involved to be a multiple of 4 elements and 16-byte aligned base
+// pointers (checked by the launcher).
 template <class TI, class TO, int NOPS, class F>
 __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, const TI* __restrict__ a, const TI* __restrict__ b, Plan p,
                                                          int pd, int tmode_a, int tmode_b, uint32_t tiles_p, uint32_t tiles_l, F f) {
     static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "ew_tile4 is for 4-byte elements");
+    static_assert(TILE == 64 && TILE_THREADS == 256, "the lane mappings below assume a 64 x 64 tile and 8 warps");
     extern __shared__ __align__(16) unsigned char tile_raw[];
-    TI(*sm)[TILE][TILE + 1] = reinterpret_cast<TI(*)[TILE][TILE + 1]>(tile_raw);  // sm[o][p][l]
+    TI(*sm)[TILE][TILE] = reinterpret_cast<TI(*)[TILE][TILE]>(tile_raw);  // sm[o][p][swizzled l]
     const int L = p.nd - 1;
     uint32_t bid = blockIdx.x;
     const uint32_t tl = bid % tiles_l;
@@ -238,17 +241,19 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, c
     const int64_t szp = p.size[pd], szl = p.size[L];
     const int64_t sap = p.st[0][pd], sal = p.st[0][L], sbp = p.st[1][pd], sbl = p.st[1][L];
     using V4 = Pack<TI, 4>;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // Stage transposed operands: a thread loads 4 consecutive P positions of one L row (the operand's unit-stride dim is P).
     auto stage = [&](const TI* __restrict__ src, int64_t base, int64_t sl, int o) {
 #pragma unroll
-        for (int k = 0; k < (TILE * TILE / 4) / TILE_THREADS; ++k) {
-            const int idx = threadIdx.x + k * TILE_THREADS;
-            const int lj = idx / (TILE / 4), p4 = idx % (TILE / 4);
+        for (int k = 0; k < 4; ++k) {
+            const int u = k * 8 + warp;                                   // 32 units of 4 L rows x 8 float4 columns
+            const int lj = 4 * (u >> 1) + (lane >> 3), p4 = 8 * (u & 1) + (lane & 7);
             const int64_t pi = p0 + 4 * p4, li = l0 + lj;
             if (pi < szp && li < szl) {
                 const V4 v = *reinterpret_cast<const V4*>(src + base + pi + li * sl);
+                const int col = 4 * ((lj >> 2) ^ (p4 & 7)) + (lj & 3);    // (p / 4) & 7 == p4 & 7 for p = 4 * p4 + i
 #pragma unroll
-                for (int i = 0; i < 4; ++i) sm[o][4 * p4 + i][lj] = v.v[i];
+                for (int i = 0; i < 4; ++i) sm[o][4 * p4 + i][col] = v.v[i];
             }
         }
     };
@@ -264,10 +269,10 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, c
         const int pj = idx / (TILE / 4), l4 = idx % (TILE / 4);
         const int64_t pi = p0 + pj, li = l0 + 4 * l4;
         if (pi >= szp || li >= szl) continue;
+        const int col = 4 * (l4 ^ ((pj >> 2) & 7));
         V4 x, y;
         if (tmode_a) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x.v[i] = sm[0][pj][4 * l4 + i];
+            x = *reinterpret_cast<const V4*>(&sm[0][pj][col]);
         } else if (sal == 1) {
             x = *reinterpret_cast<const V4*>(a + oa + pi * sap + li);
         } else {  // broadcast along L
@@ -277,8 +282,7 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, c
         Pack<TO, 4> r;
         if constexpr (NOPS > 1) {
             if (tmode_b) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) y.v[i] = sm[1][pj][4 * l4 + i];
+                y = *reinterpret_cast<const V4*>(&sm[1][pj][col]);
             } else if (sbl == 1) {
                 y = *reinterpret_cast<const V4*>(b + ob + pi * sbp + li);
             } else {

@@ -37,6 +37,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default=None)
     ap.add_argument("--quick", action="store_true", help="smaller shapes (for a profiler capture)")
+    ap.add_argument("--once", action="store_true", help="launch every op once instead of timing loops (for a profiler capture)")
     args = ap.parse_args()
     import torch
 
@@ -48,6 +49,8 @@ def main():
     results = {}
 
     def timeit(fn, iters=20, warm=5):
+        if args.once:
+            iters, warm = 1, 0
         for _ in range(warm):
             fn()
         be.synchronize()
