@@ -167,12 +167,60 @@ int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, i
     return wb_gemm_dispatch(t->be, t->matmul_mode, A, B, batch, m, n, k, ep, span_batch, used_tc);
 }
 
+// Column sums in two fixed-order stages: part[slab][j] over a slab of rows (a warp reads 32 adjacent columns of
+// one row, eight rows in flight per block), then the slabs in ascending order.
+__global__ void __launch_bounds__(256) column_sum_slabs(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int64_t per,
+                                                        float* __restrict__ part) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.y) * per, r1 = min(rows, r0 + per);
+    float acc = 0.f;
+    if (col < cols)
+        for (int64_t r = r0 + warp; r < r1; r += 8) acc += src[r * pitch + col];
+    __shared__ float red[8][33];
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < cols) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += red[w][lane];
+        part[static_cast<int64_t>(blockIdx.y) * cols + col] = t;
+    }
+}
+
+__global__ void __launch_bounds__(256) column_sum_finish(const float* __restrict__ part, int slabs, int64_t cols, float* __restrict__ dst) {
+    const int64_t col = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (col >= cols) return;
+    float t = 0.f;
+    for (int s = 0; s < slabs; ++s) t += part[static_cast<int64_t>(s) * cols + col];
+    dst[col] = t;
+}
+
 // dst[j] = sum_i src[i][j] over a dense [rows, cols] matrix (a bias gradient, crates/weta-autograd/src/ops.rs:46-58).
+// Small matrices go through Backend::reduce (the reference's summation order); tall ones are split over row slabs so
+// the whole GPU takes part (same result every run, order differs from the sequential sum by rounding only).
 int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, int64_t pitch, float* dst) {
-    WbView v{};
-    v.data = const_cast<float*>(src); v.dtype = WB_F32; v.ndim = 2;
-    v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = pitch; v.stride[1] = 1;
-    return wb_reduce_into(t->be, WB_SUM, &v, 0, dst);
+    if (rows < 256 || cols <= 0) {
+        WbView v{};
+        v.data = const_cast<float*>(src); v.dtype = WB_F32; v.ndim = 2;
+        v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = pitch; v.stride[1] = 1;
+        return wb_reduce_into(t->be, WB_SUM, &v, 0, dst);
+    }
+    WbBackend* b = t->be;
+    const int64_t col_blocks = (cols + 31) / 32;
+    int64_t slabs = std::max<int64_t>(1, std::min<int64_t>(rows / 64, (4 * static_cast<int64_t>(b->sm_count) + col_blocks - 1) / col_blocks));
+    slabs = std::min<int64_t>(slabs, 1024);
+    const int64_t per = (rows + slabs - 1) / slabs;
+    slabs = (rows + per - 1) / per;
+    void* scratch = nullptr;
+    WB_TRY(wb_scratch(b, static_cast<size_t>(slabs) * cols * sizeof(float), &scratch));
+    column_sum_slabs<<<dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs)), 256, 0, b->stream>>>(src, rows, cols, pitch, per,
+                                                                                                                     static_cast<float*>(scratch));
+    WB_LAUNCH_OK(b);
+    column_sum_finish<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, b->stream>>>(static_cast<const float*>(scratch), static_cast<int>(slabs),
+                                                                                      cols, dst);
+    WB_LAUNCH_OK(b);
+    return WB_OK;
 }
 
 int relu_bwd_inplace(WbTrainer* t, float* g, const float* y, int64_t n) {
