@@ -314,3 +314,45 @@ def test_bucket_callback_covers_the_arena(gpu):
     assert sum(n for _, n in seen) == tr.arena_len
     assert all(seen[i][0] + seen[i][1] == seen[i + 1][0] for i in range(len(seen) - 1))
     tr.close()
+
+
+def test_prefetching_stepper_matches_synchronous_steps(gpu):
+    """The double-buffered upload path (batch i+1 copied while step i runs, trainer reading from the slot buffers)
+    gives bit-identical losses to uploading each batch and stepping in turn."""
+    import torch
+
+    from weta_b200.backend import B200Backend
+    from weta_b200.trainer import DataParallelTrainer, PrefetchingStepper
+
+    cfg = CnnConfig("tiny", 3, 8, 8, 16, 32)
+    batch, steps = 32, 5
+    host = []
+    for s in range(steps):
+        x, y = synthetic_batch(cfg, batch, s, 0, gpu)
+        hx = torch.from_numpy(np.ascontiguousarray(x.numpy(), dtype=np.float32).reshape(-1)).pin_memory()
+        hy = torch.from_numpy(np.ascontiguousarray(y.numpy(), dtype=np.int64).reshape(-1)).pin_memory()
+        host.append((hx, hy))
+
+    def run(prefetch):
+        stream = torch.cuda.Stream()
+        be = B200Backend(0, stream=stream.cuda_stream)
+        manual_seed(7)
+        tr = FusedTrainer(be, cnn_specs(cfg), batch, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=FP32)
+        tr.init_from_global_rng()
+        dp = DataParallelTrainer(tr, stream, 1)
+        losses = []
+        if prefetch:
+            st = PrefetchingStepper(dp)
+            st.submit(*host[0])
+            for s in range(steps):
+                if s + 1 < steps:
+                    st.submit(*host[s + 1])
+                losses.append(st.step())
+            st.close()
+        else:
+            for s in range(steps):
+                losses.append(dp.step_host(*host[s]))
+        tr.close()
+        return losses
+
+    assert run(True) == run(False)
