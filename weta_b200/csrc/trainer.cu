@@ -52,7 +52,7 @@ struct Layer {
     float* save_rstd = nullptr;
     float* cols = nullptr;      // [B, cin*9, h*w]
     float* conv_out = nullptr;  // [B, cout, h, w]
-    float* w_pad = nullptr;     // [cout, round_up(cin*9, 4)]: weight rows re-pitched to 16 bytes when cin*9 is not a multiple of 4
+    float* w_pad = nullptr;     // [cout, round_up(cin*9, 32)]: zero-padded copy of the weight when cin*9 is not a multiple of 4 (TMA needs a 16-byte pitch)
     // Implicit-GEMM path (no cols / dcols): the input shifted one column right / left, the weight as
     // [O][tap][C] and [C][flipped tap][O], and the weight gradient as the kernel writes it ([tap][C][O]).
     bool implicit = false;
@@ -351,7 +351,12 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
                 }
             } else {
                 A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
-                if ((L.cin * 9) % 4 != 0) A(dev_alloc_t(t, static_cast<int64_t>(L.cout) * ((L.cin * 9 + 3) / 4 * 4), &L.w_pad));
+                if ((L.cin * 9) % 4 != 0) {
+                    // rows padded with zeros to a whole number of 32-float K blocks: TMA then never fetches a partial row
+                    const int64_t padded = static_cast<int64_t>(L.cout) * ((L.cin * 9 + 31) / 32 * 32);
+                    A(dev_alloc_t(t, padded, &L.w_pad));
+                    if (s == WB_OK && cudaMemsetAsync(L.w_pad, 0, padded * sizeof(float), b->stream) != cudaSuccess) s = WB_ERR_CUDA;
+                }
                 if (!first_conv) max_dcols = std::max(max_dcols, batch * L.cin * 9 * hw);
             }
             A(dev_alloc_t(t, batch * L.cout * hw, &L.conv_out));
@@ -527,12 +532,13 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             { OpTimer tm(t, i, "im2col"); WB_TRY(wb_im2col_into(b, &xv, &cp, L.cols)); }
             WbGemmOperand Aw{t->theta + L.off_w, L.cout, ck, ck, 0, false};
             if (L.w_pad) {
-                // TMA needs a 16-byte row pitch: copy the [O, C*9] weight into rows of round_up(C*9, 4) floats.
-                const int64_t ckp = (ck + 3) / 4 * 4;
+                // TMA needs a 16-byte row pitch: copy the [O, C*9] weight into zero-padded rows of round_up(C*9, 32) floats.
+                const int64_t ckp = (ck + 31) / 32 * 32;
                 WB_CHECK_CUDA(cudaMemcpy2DAsync(L.w_pad, ckp * sizeof(float), t->theta + L.off_w, ck * sizeof(float), ck * sizeof(float), L.cout,
                                                 cudaMemcpyDeviceToDevice, b->stream));
                 Aw.ptr = L.w_pad;
                 Aw.ld = ckp;
+                Aw.k = ckp;  // the padding columns are zeros; B's rows past C*9 are zero-filled by TMA
             }
             WbGemmOperand Bc{L.cols, hw, ck, hw, ck * hw, true};
             tc::Epilogue ep{L.conv_out, hw, L.cout * hw, nullptr, t->theta + L.off_b, 0, 0};
