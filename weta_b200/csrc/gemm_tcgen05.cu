@@ -130,12 +130,12 @@ __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, 
     lo[i] = v - h;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8>
 int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
-    using SS = tc::SharedStorage<BN, STAGES, CTAS>;
+    using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW>;
     constexpr size_t smem = sizeof(SS) + 1024;
     static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
-    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS>;
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW>;
     // The attribute belongs to the device's context: one flag per device ordinal and instantiation.
     static std::atomic<uint64_t> attr_done{0};
     const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
@@ -144,12 +144,12 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
         attr_done.fetch_or(bit, std::memory_order_release);
     }
     if (CTAS == 1) {
-        kern<<<grid, tc::THREADS, smem, be->stream>>>(args);
+        kern<<<grid, tc::threads_for(EPW), smem, be->stream>>>(args);
     } else {
         // Clusters of two CTAs (an MMA pair); grid.x is even.
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(tc::THREADS);
+        cfg.blockDim = dim3(tc::threads_for(EPW));
         cfg.dynamicSmemBytes = smem;
         cfg.stream = be->stream;
         cudaLaunchAttribute attr{};
@@ -232,6 +232,10 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             else if (!amn && bmn) status = launch_tc<256, 6, false, true, 2>(be, st, args, grid);
             else if (amn && !bmn) status = launch_tc<256, 6, true, false, 2>(be, st, args, grid);
             else status = launch_tc<256, 6, true, true, 2>(be, st, args, grid);
+        } else if (BN == 256 && args.k_blocks * args.num_segments <= 2 && !amn) {
+            // One or two K blocks per tile: the epilogue is the whole cost, so it gets 16 warps and the ring 2 stages.
+            if (!bmn) status = launch_tc<256, 2, false, false, 1, 16>(be, st, args, grid);
+            else status = launch_tc<256, 2, false, true, 1, 16>(be, st, args, grid);
         } else if (BN == 256) {
             if (!amn && !bmn) status = launch_tc<256, 4, false, false, 1>(be, st, args, grid);
             else if (!amn && bmn) status = launch_tc<256, 4, false, true, 1>(be, st, args, grid);

@@ -26,8 +26,9 @@ namespace tc {
 constexpr int BM = 128;
 constexpr int BK = 32;                 // 32 tf32 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 8;              // K per tcgen05.mma for tf32
-constexpr int EPI_WARPS = 8;
-constexpr int THREADS = 64 + 32 * EPI_WARPS;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+// warp 0: TMA, warp 1: MMA + TMEM owner, then EPW epilogue warps (8, or 16 for contractions of one or two K blocks,
+// whose time is the epilogue's instruction stream)
+constexpr int threads_for(int epw) { return 64 + 32 * epw; }
 constexpr uint32_t SPIN_LIMIT = 1u << 26;
 
 struct Segment {
@@ -204,14 +205,14 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 
-template <int BN, int STAGES, int CTAS>
+template <int BN, int STAGES, int CTAS, int EPW>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
     alignas(1024) float a[STAGES][BM * BK];
     alignas(1024) float b[STAGES][BN / CTAS * BK];  // a CTA of a pair holds half of the tile's B rows
     // Epilogue staging, one 32 x 32 slab per epilogue warp; 16-byte chunk j of row r sits at chunk j ^ (r & 7),
     // so the row-per-lane writes and the row-segment reads are both free of bank conflicts without padding.
-    alignas(128) float stage[EPI_WARPS][32 * 32];
+    alignas(128) float stage[EPW][32 * 32];
     alignas(8) uint64_t full[STAGES];
     uint64_t empty[STAGES];
     uint64_t tmem_full[4];   // one pair of barriers per TMEM accumulator: 512 / BN of them
@@ -235,10 +236,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // each CTA stores its own BM rows of the result.  Barriers: `full` and `tmem_empty` are the leader's (the peer's
 // loads and epilogue warps signal them remotely), `empty` and `tmem_full` exist in both CTAs and the leader's
 // commits signal each of them.
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS>
-__global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW>
+__global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using SS = SharedStorage<BN, STAGES, CTAS>;
+    using SS = SharedStorage<BN, STAGES, CTAS, EPW>;
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
     constexpr int TILE_M = BM * CTAS;   // output rows per tile
@@ -256,7 +257,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         }
         for (int a = 0; a < NACC; ++a) {
             mbar_init(&ss.tmem_full[a], 1);
-            mbar_init(&ss.tmem_empty[a], EPI_WARPS * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
+            mbar_init(&ss.tmem_empty[a], EPW * CTAS);  // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -429,11 +430,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tf32_kernel(const __grid_cons
         }
     } else {
         // ---- epilogue warps ---------------------------------------------------------------------
-        // A warp may read the TMEM lanes 32*(warp % 4) .. +31 only; the two warps that share a lane group
-        // take one half of the tile's columns each.
+        // A warp may read the TMEM lanes 32*(warp % 4) .. +31 only; the EPW / 4 warps that share a lane group
+        // take an equal share of the tile's columns each.
         const int lg = warp & 3;
         const int half = (warp - 2) >> 2;
-        constexpr int HALF_N = BN / 2;
+        constexpr int HALF_N = BN / (EPW / 4);
         float* stage = &ss.stage[warp - 2][0];
         const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) &&
                             (args.ep.batch_stride_d % 4 == 0) && (args.split_stride_d % 4 == 0);
