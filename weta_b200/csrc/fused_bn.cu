@@ -454,7 +454,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
 // (dx_right[y][x] = dx[y][x+1]), zeros shifted in; the neighbour values come from the adjacent lanes, so
 // w / 4 must divide 32.
 template <bool WRITE_DX, bool SHIFT>
-__global__ void __launch_bounds__(THREADS, 4) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, float* __restrict__ dx_left,
+__global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float* __restrict__ dx, float* __restrict__ dx_left,
                                                                             float* __restrict__ dx_right, const float* __restrict__ x,
                                                                             const float* __restrict__ dyp, const float* __restrict__ mean,
                                                                             const float* __restrict__ rstd, const float* __restrict__ gamma,
