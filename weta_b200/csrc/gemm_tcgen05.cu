@@ -130,12 +130,12 @@ __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, 
     lo[i] = v - h;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8, int MT = 1>
 int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
-    using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW>;
+    using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW, MT>;
     constexpr size_t smem = sizeof(SS) + 1024;
     static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
-    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW>;
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW, MT>;
     // The attribute belongs to the device's context: one flag per device ordinal and instantiation.
     static std::atomic<uint64_t> attr_done{0};
     const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
@@ -180,12 +180,14 @@ bool pair_mode(int m, int BN) {
 // Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
 // the persistent kernel, split-K finish.  `args` arrives with its tensor maps, k_blocks and mode fields set.
 int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool pair, bool amn, bool bmn,
-              const tc::Epilogue& ep, int force_splits) {
+              const tc::Epilogue& ep, int force_splits, bool two_blocks = false) {
     args.m = m;
     args.n = n;
     args.error_flag = st->error_flag;
     // pair: CTA pairs on 256-row tiles; the caller sized the B tensor map's box for it (BN / 2 rows per CTA).
-    const int tile_m = pair ? 2 * tc::BM : tc::BM;
+    // two_blocks: a single CTA owns two 128-row blocks that share every B box (256-wide tiles, long contractions).
+    two_blocks = two_blocks && !pair && BN == 256;
+    const int tile_m = (pair || two_blocks) ? 2 * tc::BM : tc::BM;
     const int workers = pair ? be->sm_count / 2 : be->sm_count;  // CTAs or CTA pairs that walk the tile list
     const int tiles_m = (m + tile_m - 1) / tile_m, tiles_n = (n + BN - 1) / BN;
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
@@ -232,6 +234,12 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             else if (!amn && bmn) status = launch_tc<256, 6, false, true, 2>(be, st, args, grid);
             else if (amn && !bmn) status = launch_tc<256, 6, true, false, 2>(be, st, args, grid);
             else status = launch_tc<256, 6, true, true, 2>(be, st, args, grid);
+        } else if (two_blocks) {
+            // 3 x 64 KB ring: two A row blocks and one 256-row B box per K block.
+            if (!amn && !bmn) status = launch_tc<256, 3, false, false, 1, 8, 2>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<256, 3, false, true, 1, 8, 2>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<256, 3, true, false, 1, 8, 2>(be, st, args, grid);
+            else status = launch_tc<256, 3, true, true, 1, 8, 2>(be, st, args, grid);
         } else if (BN == 256 && args.k_blocks * args.num_segments <= 2 && !amn) {
             // One or two K blocks per tile: the epilogue is the whole cost, so it gets 16 warps and the ring 2 stages.
             if (!bmn) status = launch_tc<256, 2, false, false, 1, 16>(be, st, args, grid);
@@ -278,7 +286,14 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     // stage; 128 x 128 otherwise.  (128-wide tiles for one-K-block contractions, with four accumulators in
     // flight, measured slower than 256-wide ones.)
     const int BN = n > 128 ? 256 : 128;
-    const bool pair = pair_mode(m, BN);
+    // 256 x 256 tiles come in two forms: a CTA pair, or one CTA with two row blocks (better sustained rate: 641 /
+    // 681 / 532 against 583 / 645 / 475 TFLOP/s on 4096^3 NN / NT / TN; but its epilogue does not overlap the next
+    // tile).  The single-CTA form is taken when the contraction is long and there are enough tiles to fill the GPU
+    // without split-K.
+    const int64_t kb_total = (static_cast<int64_t>(k) + tc::BK - 1) / tc::BK * (span_batch > 0 ? span_batch : 1);
+    const int64_t big_tiles = static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * grid_batch;
+    const bool two_blocks = pair_mode(m, BN) && kb_total >= 64 && big_tiles >= be->sm_count;
+    const bool pair = pair_mode(m, BN) && !two_blocks;
     const int b_box = pair ? BN / 2 : BN;  // B rows one CTA loads per K block
     tc::Args args{};
     void *hi_a = nullptr, *hi_b = nullptr;
@@ -327,7 +342,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     }
     args.batched_a = A.batch_stride != 0;
     args.batched_b = B.batch_stride != 0;
-    int status = run_tiles(be, st, args, m, n, grid_batch, BN, pair, A.mn_major, B.mn_major, ep, force_splits);
+    int status = run_tiles(be, st, args, m, n, grid_batch, BN, pair, A.mn_major, B.mn_major, ep, force_splits, two_blocks);
     if (hi_a) wb_arena_free(be, hi_a, ka);
     if (hi_b) wb_arena_free(be, hi_b, kb);
     return status;
@@ -381,15 +396,16 @@ int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const 
     args.conv_cb = static_cast<int>(ch / tc::BM);
     args.batched_a = 1;
     args.batched_b = 1;
-    // Rows come in blocks of BM = 128 (tap, channel block).  Paired CTAs take two blocks per tile; with an odd block
-    // count (9 for 128 channels) half a tile would idle for the whole contraction, and handing the odd block to a
-    // second launch makes that launch re-read all of dY for a ninth of the work: both measured slower than
-    // single-CTA tiles, which are used then.
+    // Rows come in blocks of BM = 128 (tap, channel block).  One CTA takes two blocks per tile, sharing every dY box
+    // between them (the last tile of an odd block count - 9 blocks for 128 channels - holds one block and skips
+    // the second block's loads and MMAs).  Measured on the 128 -> 256 channel layer at batch 4096: 0.97 ms, against
+    // 1.22 ms for one block per CTA and 1.40 ms for CTA pairs (whose odd block idles half a tile for the whole
+    // contraction; handing the odd block to a second launch re-reads all of dY for a ninth of the work).
     const int blocks = static_cast<int>(9 * ch / tc::BM);
-    const bool pair = pair_mode(blocks * tc::BM, BN) && blocks % 2 == 0;
+    const bool pair = false;
     WbGemmOperand B{a, m, hw, hw, static_cast<int64_t>(m) * hw, false};
     WB_TRY(make_map(st, B, batch, pair ? BN / 2 : BN, &args.seg[0].b));
-    return run_tiles(be, st, args, blocks * tc::BM, m, 1, BN, pair, false, false, ep, 0);
+    return run_tiles(be, st, args, blocks * tc::BM, m, 1, BN, pair, false, false, ep, 0, /*two_blocks=*/pair_mode(blocks * tc::BM, BN));
 }
 
 // Reads the device-side error flag the GEMM kernels raise when a bounded wait runs out.

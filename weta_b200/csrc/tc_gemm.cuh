@@ -205,10 +205,10 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 
-template <int BN, int STAGES, int CTAS, int EPW>
+template <int BN, int STAGES, int CTAS, int EPW, int MT>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
-    alignas(1024) float a[STAGES][BM * BK];
+    alignas(1024) float a[STAGES][MT * BM * BK];   // MT row blocks of BM rows, one after the other
     alignas(1024) float b[STAGES][BN / CTAS * BK];  // a CTA of a pair holds half of the tile's B rows
     // Epilogue staging, one 32 x 32 slab per epilogue warp; 16-byte chunk j of row r sits at chunk j ^ (r & 7),
     // so the row-per-lane writes and the row-segment reads are both free of bank conflicts without padding.
@@ -236,13 +236,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // each CTA stores its own BM rows of the result.  Barriers: `full` and `tmem_empty` are the leader's (the peer's
 // loads and epilogue warps signal them remotely), `empty` and `tmem_full` exist in both CTAs and the leader's
 // commits signal each of them.
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW>
+// MT = 2 (single CTAs only): one CTA owns a (2*BM) x BN tile as two BM-row blocks that share every B box - the
+// same third fewer operand bytes per flop as a CTA pair, inside one SM.  Both TMEM accumulators belong to the one
+// tile, so its epilogue does not overlap the next tile's MMAs: used for contractions whose tiles run long.
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT>
 __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using SS = SharedStorage<BN, STAGES, CTAS, EPW>;
+    using SS = SharedStorage<BN, STAGES, CTAS, EPW, MT>;
+    static_assert(MT == 1 || (CTAS == 1 && BN == 256), "two row blocks per CTA: single CTAs with 256-wide tiles");
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
-    constexpr int TILE_M = BM * CTAS;   // output rows per tile
+    constexpr int TILE_M = BM * CTAS * MT;   // output rows per tile
     constexpr int NACC = 512 / BN;      // accumulators in TMEM (all 512 columns), used round-robin: 2 or 4 tiles in flight
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -299,7 +303,6 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
             // Walks this CTA's (tile, segment, K block) sequence and fills the shared-memory ring.  (Asking L2 to
             // fetch boxes further ahead with cp.async.bulk.prefetch.tensor was tried and made every contraction
             // slower: the kernel is bound by the bytes the SM pulls through L2, and a prefetch pulls them twice.)
-            constexpr uint32_t stage_bytes = (BM * BK + B_ROWS * BK) * sizeof(float);  // this CTA's share of a stage
             struct Cursor { int t, sg, kb, m0, n0, batch, split, kb_begin, kb_end; };
             auto start = [&](Cursor& c, int t) {
                 c.t = t;
@@ -315,6 +318,8 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                     if (++c.sg >= args.num_segments) start(c, c.t + tile_step);
                 }
             };
+            // Row blocks of the tile that hold rows of the matrix (the last tile of an odd block count has one).
+            auto blocks_of = [&](const Cursor& c) { return (MT == 2 && c.m0 + BM < args.m) ? 2 : 1; };
             // One K block of operands into ring slot s.
             auto issue = [&](const int s, const Cursor& c) {
                 const CUtensorMap* ma = &args.seg[c.sg].a;
@@ -342,24 +347,28 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                     // are zero-filled by TMA, which is the padding.  A's columns are ordered (tap, channel).
                     const int cb = kb / 9, tap = kb - cb * 9;
                     const int ky = tap / 3, kx = tap - ky * 3;
-                    copy(&ss.a[s][0], ma, (tap * args.conv_cb + cb) * BK, m0, 0);
+                    for (int sub = 0; sub < blocks_of(c); ++sub) copy(&ss.a[s][sub * BM * BK], ma, (tap * args.conv_cb + cb) * BK, m0 + sub * BM, 0);
                     const CUtensorMap* mx = &args.seg[kx].b;
                     const int x0 = n0 + (ky - 1) * args.conv_w;
 #pragma unroll
                     for (int ch = 0; ch < B_ROWS / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mx, x0 + ch * 32, cb * 32, batch);
                 } else if (args.conv_mode == 2) {
                     // M tile = tap * conv_cb + channel block of BM; K block = 32 pixels of image kz.
-                    const int mbi = m0 / BM;
-                    const int tap = mbi / args.conv_cb, cb = mbi - tap * args.conv_cb;
-                    const int ky = tap / 3, kx = tap - ky * 3;
-                    copy(&ss.a[s][0], &args.seg[kx].a, k0 + (ky - 1) * args.conv_w, cb * BM, kz);
+                    for (int sub = 0; sub < blocks_of(c); ++sub) {
+                        const int mbi = m0 / BM + sub;
+                        const int tap = mbi / args.conv_cb, cb = mbi - tap * args.conv_cb;
+                        const int ky = tap / 3, kx = tap - ky * 3;
+                        copy(&ss.a[s][sub * BM * BK], &args.seg[kx].a, k0 + (ky - 1) * args.conv_w, cb * BM, kz);
+                    }
                     copy(&ss.b[s][0], mb, k0, n0, kz);
                 } else {
-                    if constexpr (A_MN) {
+                    for (int sub = 0; sub < blocks_of(c); ++sub) {
+                        if constexpr (A_MN) {
 #pragma unroll
-                        for (int ch = 0; ch < BM / 32; ++ch) copy(&ss.a[s][ch * 32 * BK], ma, m0 + ch * 32, k0, za);
-                    } else {
-                        copy(&ss.a[s][0], ma, k0, m0, za);
+                            for (int ch = 0; ch < BM / 32; ++ch) copy(&ss.a[s][sub * BM * BK + ch * 32 * BK], ma, m0 + sub * BM + ch * 32, k0, za);
+                        } else {
+                            copy(&ss.a[s][sub * BM * BK], ma, k0, m0 + sub * BM, za);
+                        }
                     }
                     if constexpr (B_MN) {
 #pragma unroll
@@ -375,7 +384,8 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
-                if (rank == 0) mbar_expect_tx(&ss.full[s], stage_bytes * CTAS);  // the leader's barrier counts both CTAs' bytes
+                if (rank == 0)  // the leader's barrier counts both CTAs' bytes
+                    mbar_expect_tx(&ss.full[s], static_cast<uint32_t>((blocks_of(cur) * BM * BK + B_ROWS * BK) * sizeof(float)) * CTAS);
                 issue(s, cur);
                 next(cur);
             }
@@ -383,7 +393,7 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             // ---- MMA issuer (the leader CTA of a pair) ----------------------------------------
-            constexpr uint32_t idesc = make_idesc(TILE_M, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+            constexpr uint32_t idesc = make_idesc(BM * CTAS, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
             // A completion is signalled in this CTA and, for a pair, at the same barrier of the peer.
             auto commit = [&](uint64_t* bar) {
                 if constexpr (CTAS == 2) {
@@ -397,10 +407,13 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
             for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
                 int m0, n0, batch, split, kb_begin, kb_end;
                 decode(t, m0, n0, batch, split, kb_begin, kb_end);
-                const int acc = tile_iter % NACC;
-                const uint32_t use = static_cast<uint32_t>(tile_iter / NACC);
-                // Wait until the epilogue has drained this accumulator (passes at once on first use).
+                // MT == 1: the tiles take the accumulators in turn.  MT == 2: row block `sub` of every tile uses accumulator `sub`.
+                const int acc = MT == 2 ? 0 : tile_iter % NACC;
+                const uint32_t use = static_cast<uint32_t>(MT == 2 ? tile_iter : tile_iter / NACC);
+                const int nsub = (MT == 2 && m0 + BM < args.m) ? 2 : 1;  // row blocks that hold rows of the matrix
+                // Wait until the epilogue has drained the accumulator(s) (passes at once on first use).
                 if (!mbar_wait(&ss.tmem_empty[acc], (use & 1) ^ 1)) { ok = false; break; }
+                if (MT == 2 && !mbar_wait(&ss.tmem_empty[1], (use & 1) ^ 1)) { ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
                 const int iters = (kb_end - kb_begin) * args.num_segments;
@@ -409,23 +422,28 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&ss.full[s], ph)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_base = smem_u32(&ss.a[s][0]), b_base = smem_u32(&ss.b[s][0]);
+                    const uint32_t b_base = smem_u32(&ss.b[s][0]);
+                    for (int sub = 0; sub < nsub; ++sub) {
+                        const uint32_t a_base = smem_u32(&ss.a[s][sub * BM * BK]);
+                        const uint32_t d = tmem_d + static_cast<uint32_t>(sub * BN);
 #pragma unroll
-                    for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-                        // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8 elements is +32 B
-                        //          inside the swizzle row.
-                        // MN-major: each K index is a 128 B row of 32 consecutive M/N elements; rows come in
-                        //          groups of 4 (512 B apart, SBO), 32-element M/N blocks are 32*BK*4 B apart (LBO);
-                        //          a K step of 8 is two groups = +1024 B.
-                        uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
-                        uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
-                        if constexpr (CTAS == 2) umma_tf32_pair(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
-                        else umma_tf32(tmem_d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+                            // K-major: rows of 128 B, 8-row groups 1024 B apart (SBO); a K step of 8 elements is +32 B
+                            //          inside the swizzle row.
+                            // MN-major: each K index is a 128 B row of 32 consecutive M/N elements; rows come in
+                            //          groups of 4 (512 B apart, SBO), 32-element M/N blocks are 32*BK*4 B apart (LBO);
+                            //          a K step of 8 is two groups = +1024 B.
+                            uint64_t ad = A_MN ? make_smem_desc(a_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(a_base + ks * 32, 16, 1024, 2);
+                            uint64_t bd = B_MN ? make_smem_desc(b_base + ks * 1024, 32 * BK * 4, 512, 1) : make_smem_desc(b_base + ks * 32, 16, 1024, 2);
+                            if constexpr (CTAS == 2) umma_tf32_pair(d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                            else umma_tf32(d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        }
                     }
                     commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
                 }
                 if (!ok) break;
                 commit(&ss.tmem_full[acc]);  // accumulator complete once every MMA above has retired
+                if (MT == 2) commit(&ss.tmem_full[1]);
             }
         }
     } else {
@@ -453,11 +471,12 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
         };
         int tile_iter = 0;
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
-            int m0, n0, batch, split, kb_begin, kb_end;
-            decode(t, m0, n0, batch, split, kb_begin, kb_end);
-            m0 += rank * BM;  // this CTA's rows of the tile
-            const int acc = tile_iter % NACC;
-            const uint32_t use = static_cast<uint32_t>(tile_iter / NACC);
+            int tile_m0, n0, batch, split, kb_begin, kb_end;
+            decode(t, tile_m0, n0, batch, split, kb_begin, kb_end);
+          for (int sub = 0; sub < MT && ok; ++sub) {
+            const int m0 = tile_m0 + rank * BM + sub * BM;  // this CTA's (this row block's) rows of the tile
+            const int acc = MT == 2 ? sub : tile_iter % NACC;
+            const uint32_t use = static_cast<uint32_t>(MT == 2 ? tile_iter : tile_iter / NACC);
             if (!mbar_wait(&ss.tmem_full[acc], use & 1)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int cbase = half * HALF_N;
@@ -575,6 +594,7 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
             };
             if (row_stats) drain(std::true_type{});
             else drain(std::false_type{});
+          }
         }
         if (row_stats) flush_stats();
     }
