@@ -285,7 +285,7 @@ def main():
     # streams its tensors once per image, so the traffic is scaled by batch / 512.
     ncu_traffic_batch512 = {
         "L0.bn_relu_pool_bwd": 908.4e6, "L1.bn_relu_pool_bwd": 699.0e6, "L0.bn_relu_pool_fwd": 425.2e6, "L1.bn_relu_pool_fwd": 150.3e6,
-        "L1.conv_fwd_gemm": 298.5e6, "L1.conv_wgrad_gemm": 339.5e6, "L1.conv_dgrad_gemm": 454.0e6,
+        "L1.conv_fwd_gemm": 298.7e6, "L1.conv_wgrad_gemm": 363.2e6, "L1.conv_dgrad_gemm": 454.8e6,
         "L0.conv_fwd_gemm": 269.6e6, "L0.conv_wgrad_gemm": 330.1e6,
     }
     shares = {k: round(v[1] / timed_ops_ms, 4) for k, v in sorted(op_times.items(), key=lambda kv: -kv[1][1])}
