@@ -78,3 +78,39 @@ def test_shapes_outside_the_rules_are_refused(gpu):
     s = gpu.alloc(1 << 16, DType.F32)
     for n, c, h, wd, o in ((1, 64, 8, 8, 32), (1, 128, 7, 7, 32), (1, 128, 8, 8, 24)):
         assert gpu.lib.wb_conv3x3_fwd(gpu.handle, s.ptr, s.ptr, None, n, c, h, wd, o, s.ptr) == 2  # WB_ERR_UNSUPPORTED
+
+
+def test_full_size_layer_equals_the_trait_chain_on_the_gpu(gpu):
+    """The wide CNN's second convolution at its full per-GPU size ([4096,128,16,16] -> 256 channels), integer-valued
+    operands: the implicit GEMM must equal, bit for bit, im2col -> matmul -> add and its backward run through the
+    trait ops on the same GPU (every partial sum is an integer below 2^24, so TF32 and f32 products are both exact)."""
+    _declare(gpu.lib)
+    n, c, h, wd, o = 4096, 128, 16, 16, 256
+    rng = np.random.default_rng(5)
+    # small images of integers generated on the host once and tiled over the batch with a per-image sign pattern
+    base = rng.integers(-2, 3, (64, c, h, wd)).astype(np.float32)
+    x = np.ascontiguousarray(np.tile(base, (n // 64, 1, 1, 1)) * np.where(np.arange(n) % 3 == 0, -1.0, 1.0).astype(np.float32)[:, None, None, None])
+    w = rng.integers(-1, 2, (o, c, 3, 3)).astype(np.float32)
+    bias = rng.integers(-4, 5, (o,)).astype(np.float32)
+    gbase = rng.integers(-1, 2, (64, o, h, wd)).astype(np.float32)
+    dy = np.ascontiguousarray(np.tile(gbase, (n // 64, 1, 1, 1)))
+    xt, wt, bt, gt = (Tensor.from_numpy(a, gpu) for a in (x, w, bias, dy))
+    ys, dxs, dws = gpu.alloc(n * o * h * wd, DType.F32), gpu.alloc(x.size, DType.F32), gpu.alloc(w.size, DType.F32)
+    gpu.check(gpu.lib.wb_conv3x3_fwd(gpu.handle, xt.storage.ptr, wt.storage.ptr, bt.storage.ptr, n, c, h, wd, o, ys.ptr))
+    gpu.check(gpu.lib.wb_conv3x3_bwd(gpu.handle, xt.storage.ptr, wt.storage.ptr, gt.storage.ptr, n, c, h, wd, o, dxs.ptr, dws.ptr))
+    gpu.gemm_check()
+    y_i = Tensor(ys, Layout.contiguous([n, o, h, wd]), DType.F32, gpu)
+    dx_i = Tensor(dxs, Layout.contiguous([n, c, h, wd]), DType.F32, gpu)
+    dw_i = Tensor(dws, Layout.contiguous([o, c, 3, 3]), DType.F32, gpu)
+    # the trait chain (3xTF32 matmul by default), compared on the device: max |difference| must be exactly 0
+    y_e = xt.conv2d(wt, bt, 1, 1)
+    assert float(y_e.sub(y_i).abs().max().numpy()) == 0.0
+    del y_e
+    cols = xt.im2col(P3)
+    g3 = gt.reshape([n, o, h * wd])
+    dx_e = wt.reshape([o, c * 9]).t().matmul(g3).col2im(P3, (c, h, wd))
+    assert float(dx_e.sub(dx_i).abs().max().numpy()) == 0.0
+    del dx_e
+    # weight gradient: sums reach 4096 * 256 = 2^20 products of magnitude <= 2: still exact in f32
+    dw_e = g3.matmul(cols.transpose(1, 2)).sum_dims([0]).reshape([o, c, 3, 3])
+    assert float(dw_e.sub(dw_i).abs().max().numpy()) == 0.0
