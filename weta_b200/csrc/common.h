@@ -154,3 +154,17 @@ struct WbIterPlan {
 
 // Builds the collapsed plan of `nops` operand views that share one shape.
 void wb_make_plan(const WbView* const* ops, int nops, WbIterPlan* plan);
+
+// Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
+struct FastDiv {
+    uint32_t d, s;
+    uint64_t mul;
+    __host__ FastDiv() : d(1), s(0), mul(1ull << 32) {}
+    __host__ explicit FastDiv(uint32_t div) : d(div) {
+        s = 0;
+        while ((1ull << s) < div) ++s;
+        mul = ((1ull << (32 + s)) + div - 1) / div;
+    }
+    __device__ __forceinline__ uint32_t div(uint32_t n) const { return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> (32 + s)); }
+};
+

@@ -71,13 +71,15 @@ __global__ void __launch_bounds__(THREADS) col2im_kernel(T* __restrict__ out, co
 // Same gather, four consecutive output columns per thread and 32-bit index arithmetic: one 128-bit
 // store per thread, the nine shifted reads of each pixel come from L1/L2.
 __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ out, const float* __restrict__ x, int h, int w,
-                                                           uint32_t groups) {
+                                                           uint32_t groups, FastDiv div_wq, FastDiv div_h) {
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
     const uint32_t wq = static_cast<uint32_t>(w) >> 2;
-    uint32_t xq = i % wq, t = i / wq;
-    uint32_t y = t % static_cast<uint32_t>(h);
-    t /= static_cast<uint32_t>(h);
+    uint32_t t = div_wq.div(i);
+    const uint32_t xq = i - t * wq;
+    const uint32_t t2 = div_h.div(t);
+    const uint32_t y = t - t2 * static_cast<uint32_t>(h);
+    t = t2;
     uint32_t k9 = t % 9u, nc = t / 9u;
     int ki = static_cast<int>(k9 / 3u), kj = static_cast<int>(k9 % 3u);
     int iy = static_cast<int>(y) + ki - 1;
@@ -85,10 +87,15 @@ __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ ou
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (iy >= 0 && iy < h) {
         const float* row = x + (static_cast<int64_t>(nc) * h + iy) * w;
+        if (kj == 1) {  // the unshifted tap: one aligned 128-bit load
+            const float4 q = *reinterpret_cast<const float4*>(row + ix0);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            int ix = ix0 + k;
-            if (ix >= 0 && ix < w) v[k] = row[ix];
+            for (int k = 0; k < 4; ++k) {
+                int ix = ix0 + k;
+                if (ix >= 0 && ix < w) v[k] = row[ix];
+            }
         }
     }
     *reinterpret_cast<float4*>(out + static_cast<int64_t>(i) * 4) = make_float4(v[0], v[1], v[2], v[3]);
@@ -157,11 +164,11 @@ extern "C" int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams*
     if (total == 0) return WB_OK;
     WbProfileScope ps(b, "im2col");
     if (same_conv3(*cp) && x->dtype == WB_F32 && wb_is_contiguous(*x) && p.w % 4 == 0 && total / 4 < (int64_t(1) << 31) &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(static_cast<const float*>(x->data) + x->offset) & 15) == 0) {
         int64_t groups = total / 4;
         im2col3_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
             static_cast<float*>(out), static_cast<const float*>(x->data) + x->offset, static_cast<int>(p.h), static_cast<int>(p.w),
-            static_cast<uint32_t>(groups));
+            static_cast<uint32_t>(groups), FastDiv(static_cast<uint32_t>(p.w / 4)), FastDiv(static_cast<uint32_t>(p.h)));
         WB_LAUNCH_OK(b);
         return WB_OK;
     }

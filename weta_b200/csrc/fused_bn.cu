@@ -242,18 +242,6 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_dx_kernel(float* __restrict__ 
 }
 
 // ---- conv block tail: BN -> ReLU -> 2x2 max pool, one pass each way ------------------------------
-// Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
-struct FastDiv {
-    uint32_t d, s;
-    uint64_t mul;
-    __host__ FastDiv() : d(1), s(0), mul(1ull << 32) {}
-    __host__ explicit FastDiv(uint32_t div) : d(div) {
-        s = 0;
-        while ((1ull << s) < div) ++s;
-        mul = ((1ull << (32 + s)) + div - 1) / div;
-    }
-    __device__ __forceinline__ uint32_t div(uint32_t n) const { return static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> (32 + s)); }
-};
 
 // Forward, w % 8 == 0: one thread per four pooled values of a row (two float4 loads from each of two input
 // rows, one float4 store).  SHIFT also writes the pooled tensor shifted one column right (left[y][x] = y[y][x-1])
