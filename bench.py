@@ -90,8 +90,9 @@ def cpu_reference_run(steps: int, warmup: int, sample_batch: int):
     """The reference's CPU path (the oracle restating weta-cpu, driven op by op like the reference's
     own autograd would) on a bounded sample of the workload, with every host thread."""
     from oracle.cpu_backend import OracleBackend
-    from weta_b200 import nn
-    from weta_b200.workloads import WIDE_CNN, build_cnn, primitive_train_step, synthetic_batch
+    from oracle.mirror import nn
+    from oracle.mirror.models import build_cnn, primitive_train_step, synthetic_batch
+    from weta_b200.workloads import WIDE_CNN
 
     be = OracleBackend()
     model = build_cnn(WIDE_CNN, be, 42)

@@ -188,7 +188,8 @@ int wb_gemm_check(WbBackend* b);
 
 /* F::dropout in training mode (crates/weta-nn/src/functional.rs:64-74): y = x * mask with
  * mask_i = (rand_f32(seed)_i > p) / (1 - p), the mask regenerated from the seed (never stored);
- * values are bit-identical to the four-call chain random -> gt_scalar -> mul_scalar -> mul. */
+ * values are bit-identical to the four-call chain random -> gt_scalar -> mul_scalar -> mul.  p = 0 gives y = x,
+ * p = 1 gives y = x * 0 (functional.rs:66-71). */
 int wb_dropout_fwd(WbBackend* b, const float* x, float* y, int64_t n, double p, uint64_t seed);
 /* Its backward, dx = dy * mask, optionally times step(relu_out) (ReLU backward, autograd ops.rs:85). */
 int wb_dropout_relu_bwd(WbBackend* b, const float* dy, const float* relu_out, float* dx, int64_t n, double p, uint64_t seed);
@@ -210,8 +211,10 @@ int wb_bn2d_apply(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw
  * or with the device's memory fully budgeted elsewhere): it takes no backend handle, runs on the current
  * device and the given cudaStream_t, and keeps its partial sums in a fixed 512 KiB array inside the library
  * instead of arena scratch.  Limit: c <= 32768 channels (else WB_ERR_INVALID).  The first call on a device
- * resolves the array's address, so issue it before any stream capture.  Calls share the array: calls that
- * overlap on the GPU race; keep them on one stream or order them yourself. */
+ * resolves the array's address and may load the library's device code (which takes device memory): make one
+ * warm-up call per device at start-up, outside the no-allocation context and before any stream capture; two
+ * host threads racing on that first call store the same address, which is harmless.  Calls share the array:
+ * calls that overlap on the GPU race; keep them on one stream or order them yourself. */
 int wb_bn2d_stats_noalloc(void* cuda_stream, const float* x, int64_t n, int64_t c, int64_t hw, double eps, double momentum,
                           float* mean, float* rstd, float* running_mean, float* running_var);
 int wb_bn2d_fwd(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t hw, const float* gamma, const float* beta,
@@ -302,7 +305,8 @@ int wb_trainer_num_tensors(const WbTrainer* t);
 int wb_trainer_tensor_range(const WbTrainer* t, int index, int64_t* offset, int64_t* len);
 int wb_trainer_bn_buffers(WbTrainer* t, int conv_index, float** running_mean, float** running_var, int64_t* channels);
 int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* user);
-/* Forward, mean cross-entropy and backward on the staged batch; one seed per dropout layer in forward order. */
+/* Forward, mean cross-entropy and backward on the staged batch; one seed per dropout layer with 0 < p < 1, in forward
+ * order (p = 0 and p = 1 need no mask and, as in crates/weta-nn/src/functional.rs:66-71, consume no seed). */
 int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds);
 /* Adam over the whole arena; grad_scale = 1/world after a summing all-reduce, else 1. */
 int wb_trainer_adam_step(WbTrainer* t, double grad_scale);
@@ -321,6 +325,68 @@ int wb_trainer_read_loss(WbTrainer* t, float* host_loss);
  * the report waits for the stream and returns lines "label calls total_ms". */
 int wb_trainer_set_timing(WbTrainer* t, int on);
 const char* wb_trainer_timing_report(WbTrainer* t);
+
+/* ---- data-parallel training step ---------------------------------------------------------------
+ * No counterpart in the reference: its backends are per-ordinal singletons with no gradient exchange
+ * (crates/weta-cuda/src/lib.rs:129-146).  One process (or host thread) per GPU, every rank a full replica built
+ * from the same seeds, the batch sharded by samples; BatchNorm statistics stay per rank (the reference has no
+ * SyncBN).  The one exchange sits between backward and Adam::step (crates/weta-optim/src/lib.rs:210-239): the
+ * gradient arena is cut into buckets of whole layers, and as soon as backward has finished a bucket its exchange
+ * and its optimizer update run on side streams while backward continues. */
+#define WB_DP_ID_BYTES 128
+typedef struct WbDpId { char bytes[WB_DP_ID_BYTES]; } WbDpId;
+typedef enum WbDpMode {
+    WB_DP_AUTO = 0,      /* PEER when the ranks can map each other's memory, else SHARDED; WETA_B200_DP_MODE overrides */
+    WB_DP_ALLREDUCE = 1, /* ncclAllReduce per bucket, Adam over the whole bucket on every rank */
+    WB_DP_SHARDED = 2,   /* ncclReduceScatter -> Adam on this rank's 1/world of the bucket -> ncclAllGather of the parameters */
+    WB_DP_PEER = 3       /* this library's kernel: peer loads of every replica's gradient shard over NVLink, sum in rank
+                            order, Adam, peer stores of the new parameters into every replica (arenas shared by CUDA IPC) */
+} WbDpMode;
+typedef struct WbDp WbDp;
+/* Rank 0 makes the id and hands its bytes to the other ranks over any host channel (ncclGetUniqueId). */
+int wb_dp_unique_id(WbDpId* out);
+/* Collective: every rank calls it with the same id, world, mode and bucket_elems (<= 0: 2^20), after wb_trainer_init.
+ * world == 1 needs no id and no NCCL.  The trainer's bucket callback is taken over by the handle. */
+int wb_dp_create(WbTrainer* t, const WbDpId* id, int rank, int world, int mode, int64_t bucket_elems, WbDp** out);
+int wb_dp_destroy(WbDp* dp);
+int wb_dp_mode(const WbDp* dp);   /* the mode in use (AUTO resolved; the same on every rank) */
+int wb_dp_world(const WbDp* dp);
+int wb_dp_num_buckets(const WbDp* dp);
+int wb_dp_bucket(const WbDp* dp, int index, int64_t* offset, int64_t* len);
+/* One step on the staged batch (wb_trainer_input / wb_trainer_labels / wb_trainer_set_input): forward, loss,
+ * backward with every bucket's exchange + update queued behind it; the next step waits for the last update.
+ * Asynchronous; wb_dp_wait or wb_trainer_read_loss waits. */
+int wb_dp_step(WbDp* dp, const uint64_t* dropout_seeds, int n_seeds);
+/* Double-buffered input: wb_dp_submit queues the upload of one batch from PINNED host memory into one of two device
+ * slots on a copy stream (at most two batches ahead of the steps); wb_dp_step_submitted steps on the oldest submitted
+ * batch and, when host_loss is given, reads the loss back and waits.  Replaces the per-batch `Tensor::to`
+ * (crates/weta-tensor/src/tensor.rs:235-240) and `loss.item()` of crates/weta/examples/mnist_cnn.rs:63-73. */
+int wb_dp_submit(WbDp* dp, const float* pinned_x, const int64_t* pinned_y);
+int wb_dp_step_submitted(WbDp* dp, const uint64_t* dropout_seeds, int n_seeds, float* host_loss);
+/* Waits for everything queued so far.  timeout_ms > 0: a host watchdog polls completion, the status word of the
+ * bounded device-side waits and ncclCommGetAsyncError; on expiry the communicator is aborted and WB_ERR_TIMEOUT
+ * returned, so a rank whose peer never joined gets an error instead of a hang.  timeout_ms <= 0: no limit. */
+int wb_dp_wait(WbDp* dp, int timeout_ms);
+int wb_dp_set_timing(WbDp* dp, int on);
+const char* wb_dp_timing_report(WbDp* dp); /* "bucket_work calls total_ms": device time of the side-stream work */
+/* Pure host logic (no device needed): how per-layer arena ranges, in arena order, merge into buckets of at least
+ * min_elems elements.  Returns the number of buckets (which may exceed max_buckets; only that many are written). */
+int wb_dp_plan_buckets(const int64_t* range_off, const int64_t* range_len, int n, int64_t min_elems, int64_t* bucket_off, int64_t* bucket_len,
+                       int max_buckets);
+/* The watchdog loop by itself: polls `poll(user)` (0 = finished, 1 = still running, other = failed) every interval_us
+ * until it finishes or timeout_ms have passed (0 = no limit); WB_OK, WB_ERR_TIMEOUT or WB_ERR_CUDA. */
+typedef int (*wb_poll_fn)(void* user);
+int wb_watchdog_wait(wb_poll_fn poll, void* user, int timeout_ms, int interval_us);
+/* The PEER-mode kernel as an operation of its own: sums `world` (<= 8) gradient buffers element-wise in index order,
+ * runs Adam step t (as wb_adam_step, grad_scale applied to the sum) on elements [offset, offset + len) of the parameters
+ * in thetas[self] with the caller's m / v, and stores the new parameters into all `world` parameter buffers.  Buffers
+ * may be local or peer mappings; all 16-byte aligned, offset and len multiples of 4. */
+int wb_reduce_adam_broadcast(WbBackend* b, const float* const* grads, float* const* thetas, int world, int self, int64_t offset, int64_t len,
+                             float* m, float* v, int64_t t, double lr, double beta1, double beta2, double eps, double weight_decay, int decoupled,
+                             double grad_scale);
+/* Exercises the bounded device-side wait of the PEER mode on one GPU: polls a flag word that nothing sets (unless
+ * preset != 0) for timeout_ms (1..5000), then returns WB_ERR_TIMEOUT with the context still usable. */
+int wb_dp_selftest_wait(WbBackend* b, int timeout_ms, int preset);
 
 #ifdef __cplusplus
 }

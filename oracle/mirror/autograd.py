@@ -1,4 +1,4 @@
-"""Reverse-mode autograd over `Tensor`, emitting the primitive sequences of `weta-autograd`.
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: reverse-mode autograd over `Tensor`, emitting the primitive sequences of `weta-autograd`.
 
 Each backward rule below issues the tensor ops of the corresponding rule in
 crates/weta-autograd/src/ops.rs (cited per rule), visited in reverse creation order like
@@ -13,7 +13,7 @@ from typing import Callable, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .core import BinaryOp, DType, Im2ColParams, UnaryOp
+from weta_b200.core import BinaryOp, DType, Im2ColParams, UnaryOp
 from .tensor import Tensor
 
 _seq = itertools.count()

@@ -1,4 +1,4 @@
-"""Layers, functional ops, the named models and the optimizers, in primitive mode.
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: layers, functional ops, the named models and the optimizers, in primitive mode.
 
 Everything here is written in `Var`/`Tensor` ops in the order the reference writes them
 (crates/weta-nn/src/functional.rs, crates/weta-nn/src/layers.rs, crates/weta-optim/src/lib.rs),
@@ -12,7 +12,7 @@ import math
 from typing import List, Optional, Sequence
 
 from .autograd import Var, no_grad
-from .core import DType, Im2ColParams
+from weta_b200.core import DType, Im2ColParams
 from .tensor import Tensor
 
 

@@ -1,4 +1,4 @@
-"""A strided tensor over a backend, with the composite ops of `weta-tensor`.
+"""TEST INFRASTRUCTURE, NOT PRODUCT CODE: a strided tensor over a backend object, with the composite ops of `weta-tensor`.
 
 This is the call-site mirror of crates/weta-tensor/src/tensor.rs: every method issues the same
 sequence of backend primitives the reference issues (one `reduce` per axis, highest axis first;
@@ -12,7 +12,7 @@ from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .core import (BinaryOp, Distribution, DType, Im2ColParams, Layout, ReduceOp, UnaryOp, broadcast_shapes,
+from weta_b200.core import (BinaryOp, Distribution, DType, Im2ColParams, Layout, ReduceOp, UnaryOp, broadcast_shapes,
                    global_rng, resolve_shape)
 
 

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from weta_b200.core import DType, Im2ColParams, Layout
-from weta_b200.tensor import Tensor
+from oracle.mirror.tensor import Tensor
 from weta_b200.trainer import _declare
 
 pytestmark = pytest.mark.gpu

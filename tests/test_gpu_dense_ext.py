@@ -3,10 +3,10 @@ definitions (crates/weta-nn/src/functional.rs:54-60, 121-130; crates/weta-autogr
 import numpy as np
 import pytest
 
-from weta_b200 import nn
-from weta_b200.autograd import Var
+from oracle.mirror import nn
+from oracle.mirror.autograd import Var
 from weta_b200.core import DType, Layout
-from weta_b200.tensor import Tensor, allclose
+from oracle.mirror.tensor import Tensor, allclose
 from weta_b200.trainer import _declare
 
 pytestmark = pytest.mark.gpu

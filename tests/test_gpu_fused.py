@@ -6,12 +6,14 @@ import ctypes
 import numpy as np
 import pytest
 
-from weta_b200 import core, nn
-from weta_b200.autograd import Var
+from weta_b200 import core
+from oracle.mirror import nn
+from oracle.mirror.autograd import Var
 from weta_b200.core import Distribution, DType, manual_seed
-from weta_b200.tensor import Tensor, allclose
+from oracle.mirror.tensor import Tensor, allclose
 from weta_b200.trainer import FusedTrainer, _declare, cnn_specs, mlp_specs
-from weta_b200.workloads import MNIST_CNN, CnnConfig, build_cnn, mlp_batch, primitive_train_step, synthetic_batch
+from weta_b200.workloads import MNIST_CNN, CnnConfig
+from oracle.mirror.models import build_cnn, mlp_batch, primitive_train_step, synthetic_batch
 
 pytestmark = pytest.mark.gpu
 RNG = np.random.default_rng(7)

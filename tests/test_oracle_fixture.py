@@ -3,9 +3,9 @@ crates/weta/tests/reference.rs."""
 import numpy as np
 import pytest
 
-from weta_b200 import nn
-from weta_b200.autograd import Var
-from weta_b200.tensor import Tensor
+from oracle.mirror import nn
+from oracle.mirror.autograd import Var
+from oracle.mirror.tensor import Tensor
 
 
 def close(name, got, want):

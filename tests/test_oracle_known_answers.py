@@ -3,9 +3,9 @@ import numpy as np
 
 from weta_b200.core import (DType, Distribution, Im2ColParams, Layout, Pcg, broadcast_shapes, resolve_shape,
                             splitmix64)
-from weta_b200.tensor import Tensor
-from weta_b200.autograd import Var
-from weta_b200 import nn
+from oracle.mirror.tensor import Tensor
+from oracle.mirror.autograd import Var
+from oracle.mirror import nn
 
 
 def T(be, a, dtype=np.float32):

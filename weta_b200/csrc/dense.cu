@@ -170,5 +170,6 @@ extern "C" int wb_maxpool2d_bwd(WbBackend* b, const float* x, const float* dy, i
 
 extern "C" int wb_relu_bwd(WbBackend* b, const float* dy, const float* y, float* dx, int64_t n) {
     // dx = dy * step(y): UnaryBw for ReLU; y may be the ReLU's input or its output (same sign test)
+    WB_REQUIRE(y, WB_ERR_INVALID, "wb_relu_bwd: y (the ReLU's input or output) is null");
     return wb_dropout_relu_bwd(b, dy, y, dx, n, 0.0, 0);
 }

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cmath>
 
+#include "adam.cuh"
 #include "common.h"
 
 namespace {
@@ -37,11 +38,11 @@ constexpr uint64_t GOLDEN = 0x9E3779B97F4A7C15ull;
 // mask = ((u > f32(p)) ? 1 : 0) * f32(1/(1-p)) + 0 = (k >= kmin) ? scale : 0;  y = x * mask.  With
 // relu_src != null the incoming value is additionally multiplied by step(relu_src) (ReLU backward folded in).
 __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ relu_src,
-                                                           int64_t n, uint64_t kmin, float scale, uint64_t seed) {
+                                                           int64_t n, uint64_t kmin, float scale, uint64_t seed, int vec) {
     int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
     uint64_t z = seed + (static_cast<uint64_t>(i) + 1) * GOLDEN;
-    if (i + 4 <= n) {
+    if (vec && i + 4 <= n) {  // vec: every buffer is 16-byte aligned (checked by the host)
         float4 v = *reinterpret_cast<const float4*>(x + i);
         float in[4] = {v.x, v.y, v.z, v.w}, out[4];
         float rs[4] = {1.f, 1.f, 1.f, 1.f};
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y,
         }
         *reinterpret_cast<float4*>(y + i) = make_float4(out[0], out[1], out[2], out[3]);
     } else {
-        for (int64_t j = i; j < n; ++j) {
+        for (int64_t j = i; j < n && j < i + 4; ++j) {
             float mask = mix_tail(z) >= kmin ? scale : 0.f;
             z += GOLDEN;
             float g = x[j] * mask;
@@ -220,29 +221,7 @@ __global__ void __launch_bounds__(THREADS) mean_kernel(const float* __restrict__
 }
 
 // ---- Adam ---------------------------------------------------------------------------------------
-// crates/weta-optim/src/lib.rs:210-239 as one pass; every f32 rounding of the primitive chain is kept
-// (each `mul_scalar` is x*s + 0, `add_scalar(eps)` is x*1 + eps).
-struct AdamK {
-    float b1, omb1, b2, omb2, inv_sqrt_bc2, eps, step_size, wd, decay_mul, gscale;
-    int first, decoupled, has_wd, scale_grad;
-};
-
-__device__ __forceinline__ void adam_one(float& th, float g, float& mi, float& vi, const AdamK& k) {
-    if (k.scale_grad) g = g * k.gscale;
-    if (k.has_wd) {
-        if (k.decoupled) th = th * k.decay_mul + 0.f;
-        else g = g + (th * k.wd + 0.f);
-    }
-    float gm = g * k.omb1 + 0.f;
-    float gv = (g * g) * k.omb2 + 0.f;
-    float mn = k.first ? gm : (mi * k.b1 + 0.f) + gm;
-    float vn = k.first ? gv : (vi * k.b2 + 0.f) + gv;
-    float den = (sqrtf(vn) * k.inv_sqrt_bc2 + 0.f) * 1.f + k.eps;
-    th = th - ((mn / den) * k.step_size + 0.f);
-    mi = mn;
-    vi = vn;
-}
-
+// crates/weta-optim/src/lib.rs:210-239 as one pass: AdamK and adam_one in adam.cuh.
 // One thread per four elements (128-bit accesses); the last, partial group is done element by element.
 __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta, const float* __restrict__ grad, float* __restrict__ m,
                                                         float* __restrict__ v, int64_t n, AdamK k, int vec) {
@@ -272,9 +251,11 @@ __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta
 }
 
 // Smallest 53-bit k whose uniform value (f32)((double)k * 2^-53) exceeds f32(p); 2^53 if none does.
-// p <= 0 keeps everything (the reference returns x unchanged for p = 0).
+// p <= 0 keeps everything (the reference returns x unchanged for p = 0); p = 1 keeps nothing (the reference
+// returns x * 0, crates/weta-nn/src/functional.rs:66-71).
 uint64_t dropout_threshold(double p) {
     if (p <= 0.0) return 0;
+    if (p >= 1.0) return 1ull << 53;
     const float pf = static_cast<float>(p);
     uint64_t lo = 0, hi = 1ull << 53;  // invariant: u(lo - 1) <= pf (or lo == 0), u(hi) > pf (or hi == 2^53)
     while (lo < hi) {
@@ -286,52 +267,43 @@ uint64_t dropout_threshold(double p) {
     return lo;
 }
 
-double powi(double a, int n) {  // f64::powi (compiler-rt __powidf2)
-    double r = 1.0;
-    int b = n;
-    while (true) {
-        if (b & 1) r *= a;
-        b /= 2;
-        if (b == 0) break;
-        a *= a;
-    }
-    return r;
-}
 
 }  // namespace
 
 // ---- entry points -------------------------------------------------------------------------------
 extern "C" int wb_dropout_fwd(WbBackend* b, const float* x, float* y, int64_t n, double p, uint64_t seed) {
     WB_REQUIRE(b && x && y, WB_ERR_INVALID, "wb_dropout_fwd: null pointer");
-    WB_REQUIRE(p >= 0.0 && p < 1.0, WB_ERR_INVALID, "dropout probability has to be in [0, 1), got %g", p);
+    WB_REQUIRE(p >= 0.0 && p <= 1.0, WB_ERR_INVALID, "dropout probability has to be in [0, 1], got %g", p);
     if (n == 0) return WB_OK;
     WbProfileScope ps(b, "dropout");
     int64_t threads = (n + 3) / 4;
-    bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
-    WB_REQUIRE(aligned, WB_ERR_INVALID, "wb_dropout_fwd: buffers must be 16-byte aligned");
+    const int vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        y, x, nullptr, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+        y, x, nullptr, n, dropout_threshold(p), p < 1.0 ? static_cast<float>(1.0 / (1.0 - p)) : 0.f, seed, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
 
 extern "C" int wb_dropout_relu_bwd(WbBackend* b, const float* dy, const float* relu_out, float* dx, int64_t n, double p, uint64_t seed) {
     WB_REQUIRE(b && dy && dx, WB_ERR_INVALID, "wb_dropout_relu_bwd: null pointer");
+    WB_REQUIRE(p >= 0.0 && p <= 1.0, WB_ERR_INVALID, "dropout probability has to be in [0, 1], got %g", p);
     if (n == 0) return WB_OK;
     WbProfileScope ps(b, "dropout_bwd");
     int64_t threads = (n + 3) / 4;
+    const int vec = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(relu_out)) & 15) == 0;
     dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        dx, dy, relu_out, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+        dx, dy, relu_out, n, dropout_threshold(p), p < 1.0 ? static_cast<float>(1.0 / (1.0 - p)) : 0.f, seed, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
 
 extern "C" int wb_dropout_mask(WbBackend* b, float* mask, int64_t n, double p, uint64_t seed) {
     WB_REQUIRE(b && mask, WB_ERR_INVALID, "wb_dropout_mask: null pointer");
+    WB_REQUIRE(p >= 0.0 && p <= 1.0, WB_ERR_INVALID, "dropout probability has to be in [0, 1], got %g", p);
     if (n == 0) return WB_OK;
     WbProfileScope ps(b, "dropout_mask");
     dropout_mask_kernel<<<static_cast<unsigned>(((n + 3) / 4 + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-        mask, n, dropout_threshold(p), static_cast<float>(1.0 / (1.0 - p)), seed);
+        mask, n, dropout_threshold(p), p < 1.0 ? static_cast<float>(1.0 / (1.0 - p)) : 0.f, seed);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -381,22 +353,7 @@ extern "C" int wb_adam_step(WbBackend* b, float* theta, const float* grad, float
     WB_REQUIRE(t >= 1, WB_ERR_INVALID, "wb_adam_step: step counts from 1");
     if (n == 0) return WB_OK;
     WbProfileScope ps(b, "adam_step");
-    double bc1 = 1.0 - powi(beta1, static_cast<int>(t)), bc2 = 1.0 - powi(beta2, static_cast<int>(t));
-    AdamK k;
-    k.b1 = static_cast<float>(beta1);
-    k.omb1 = static_cast<float>(1.0 - beta1);
-    k.b2 = static_cast<float>(beta2);
-    k.omb2 = static_cast<float>(1.0 - beta2);
-    k.inv_sqrt_bc2 = static_cast<float>(1.0 / std::sqrt(bc2));
-    k.eps = static_cast<float>(eps);
-    k.step_size = static_cast<float>(lr / bc1);
-    k.wd = static_cast<float>(weight_decay);
-    k.decay_mul = static_cast<float>(1.0 - lr * weight_decay);
-    k.gscale = static_cast<float>(grad_scale);
-    k.first = t == 1;
-    k.decoupled = decoupled;
-    k.has_wd = weight_decay != 0.0;
-    k.scale_grad = grad_scale != 1.0;
+    const AdamK k = wb_adam_constants(t, lr, beta1, beta2, eps, weight_decay, decoupled, grad_scale);
     const int vec = ((reinterpret_cast<uintptr_t>(theta) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
                       reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     const int64_t groups = (n + 3) / 4;

@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(THREADS) bn_stats_kernel(const float* __restri
     const int64_t n0 = min(n_img, static_cast<int64_t>(blockIdx.y) * per), n1 = min(n_img, n0 + per);  // n1 >= n0, empty slab allowed
     const int64_t plane_stride = static_cast<int64_t>(c_total) * hw;
     const float* slab = x + (n0 * c_total + c) * hw;
-    if ((hw & 3) == 0) {
+    if ((hw & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {  // planes are whole float4s and x starts on one
         const uint32_t q = static_cast<uint32_t>(hw >> 2), items = static_cast<uint32_t>(n1 - n0) * q;  // host checks the range
         float a1 = 0.f, a2 = 0.f;
         int flushed = 0;
@@ -124,8 +124,9 @@ __global__ void __launch_bounds__(THREADS) bn_apply_kernel(float* __restrict__ y
     float m = mean[c], r = rstd[c], g = gamma ? gamma[c] : 1.f, b = beta ? beta[c] : 0.f;
     const float* src = x + plane * hw;
     float* dst = y + plane * hw;
+    const bool vec = (hw & 3) == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     for (int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4; i < hw; i += static_cast<int64_t>(gridDim.x) * THREADS * 4) {
-        if (i + 4 <= hw && (hw & 3) == 0) {
+        if (vec && i + 4 <= hw) {
             float4 v = *reinterpret_cast<const float4*>(src + i);
             float o[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -634,7 +635,11 @@ double* g_noalloc_ptr[MAX_DEVICES] = {};
 // CURRENT device and the given stream, using only the fixed scratch array above: no cudaMalloc, no
 // cudaFree, no backend handle.  It fits c channels when 2*c <= WB_NOALLOC_SCRATCH_DOUBLES (c <= 32768);
 // larger inputs are rejected with WB_ERR_INVALID.  The first call on each device looks up the array's
-// address (cudaGetSymbolAddress); make that first call before starting any stream capture.  All calls on a
+// address (cudaGetSymbolAddress) and, with CUDA's lazy module loading, may be the call that loads this
+// library's device code, which itself takes device memory: make one warm-up call per device at start-up,
+// outside the context that must not allocate and before starting any stream capture.  Two host threads
+// that make the first call at once both store the same address into the per-device slot, which is
+// harmless.  x may start at any float (an unaligned start takes the scalar loads).  All calls on a
 // device share the one array: every slot a call reads is written by that call first, so nothing needs
 // clearing, but two calls that overlap on the GPU (different streams, or different host threads on
 // different streams) would overwrite each other's partial sums; run them on one stream or order them.

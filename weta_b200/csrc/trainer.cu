@@ -269,7 +269,7 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
         } else if (L.kind == L_DROPOUT) {
             L.p = specs[i].p;
             L.out_elems = flat;
-            if (!(L.p >= 0.0 && L.p < 1.0)) { delete t; wb_set_error("trainer: dropout probability must be in [0, 1)"); return WB_ERR_INVALID; }
+            if (!(L.p >= 0.0 && L.p <= 1.0)) { delete t; wb_set_error("trainer: dropout probability must be in [0, 1]"); return WB_ERR_INVALID; }
         } else {
             delete t;
             wb_set_error("trainer: unknown layer kind %d", L.kind);
@@ -279,9 +279,10 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
     }
     WB_REQUIRE(t->layers.back().kind == L_LINEAR, WB_ERR_INVALID, "trainer: the last layer must be linear (the logits)");
     t->classes = t->layers.back().out;
-    // Arena layout: last layer first.  Each range is padded to 4 elements so every tensor starts
-    // on a 16-byte boundary (TMA operands).
-    auto pad4 = [](int64_t n) { return (n + 3) / 4 * 4; };
+    // Arena layout: last layer first.  Each tensor is padded to 32 elements: every tensor starts on a 128-byte
+    // boundary (TMA operands need 16), and any run of whole tensors splits into 2, 4 or 8 equal shards that are
+    // themselves 16-byte aligned (the data-parallel step gives each rank one shard of every bucket).
+    auto pad4 = [](int64_t n) { return (n + 31) / 32 * 32; };
     int64_t off = 0;
     for (int i = n_layers - 1; i >= 0; --i) {
         Layer& L = t->layers[i];
@@ -484,6 +485,21 @@ extern "C" int wb_trainer_bn_buffers(WbTrainer* t, int conv_index, float** runni
     return WB_ERR_INVALID;
 }
 
+// Internal (dp.cu): the trainer's backend, batch geometry and per-layer arena ranges in arena order (last layer first).
+int wb_trainer_internal_info(WbTrainer* t, WbBackend** be, int64_t* batch, int64_t* in_elems, std::vector<std::pair<int64_t, int64_t>>* ranges) {
+    if (be) *be = t->be;
+    if (batch) *batch = t->batch;
+    if (in_elems) *in_elems = t->in_elems;
+    if (ranges) {
+        ranges->clear();
+        for (int i = static_cast<int>(t->layers.size()) - 1; i >= 0; --i)
+            if (t->layers[i].range_len > 0) ranges->push_back({t->layers[i].range_begin, t->layers[i].range_len});
+    }
+    return WB_OK;
+}
+
+const WbAdamConfig* wb_trainer_adam_config(const WbTrainer* t) { return &t->adam; }
+
 extern "C" int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* user) {
     t->cb = cb;
     t->cb_user = user;
@@ -498,7 +514,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
     WbBackend* b = t->be;
     const int64_t B = t->batch;
     int n_drop = 0;
-    for (const Layer& L : t->layers) n_drop += L.kind == L_DROPOUT;
+    // The reference draws a seed only when a mask is needed: F::dropout returns before Tensor::rand for p = 0 and
+    // p = 1 (crates/weta-nn/src/functional.rs:66-71), so those layers consume none.
+    for (const Layer& L : t->layers) n_drop += L.kind == L_DROPOUT && L.p > 0.0 && L.p < 1.0;
     WB_REQUIRE(n_seeds == n_drop && (n_drop == 0 || dropout_seeds), WB_ERR_INVALID, "trainer: expected %d dropout seeds, got %d", n_drop, n_seeds);
     const int nl = static_cast<int>(t->layers.size());
     // ---- forward ----------------------------------------------------------------------------
@@ -566,7 +584,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             { OpTimer tm(t, i, "linear_fwd_gemm"); WB_TRY(gemm(t, Ax, Bw, 1, static_cast<int>(B), L.out, L.in, ep)); }
             act = L.out_act;
         } else {
-            seed_of[i] = dropout_seeds[di++];
+            seed_of[i] = (L.p > 0.0 && L.p < 1.0) ? dropout_seeds[di++] : 0;
             { OpTimer tm(t, i, "dropout_fwd"); WB_TRY(wb_dropout_fwd(b, act, L.out_act, B * L.out_elems, L.p, seed_of[i])); }
             act = L.out_act;
         }

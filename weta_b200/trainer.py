@@ -120,7 +120,8 @@ class FusedTrainer:
         backend.check(self.lib.wb_trainer_create(backend.handle, arr, len(specs), batch, *in_shape, ctypes.byref(adam), matmul_mode,
                                                  ctypes.byref(out)))
         self.handle = out.value
-        self.n_dropout = sum(1 for s in specs if s[0] == DROPOUT)
+        # F::dropout draws a seed only when it needs a mask (crates/weta-nn/src/functional.rs:66-71)
+        self.n_dropout = sum(1 for s in specs if s[0] == DROPOUT and 0.0 < s[4] < 1.0)
         self.n_seeded = 2 * sum(1 for s in specs if s[0] in (CONV, LINEAR))
         self.arena_len = self.lib.wb_trainer_arena_len(self.handle)
         self._cb = None
@@ -227,165 +228,134 @@ class FusedTrainer:
         self.be.check(self.lib.wb_trainer_set_bucket_callback(self.handle, self._cb, None))
 
 
-class GradBucketer:
-    """Turns the trainer's per-layer "gradients final" notifications into a few large all-reduces.
-
-    Ranges arrive front to back over one flat arena (last layer first).  Adjacent ranges are merged
-    until `min_elems` have accumulated, then `reduce_fn(start, length)` is called for the merged
-    range; `flush()` sends whatever is left.  Pure host logic: the collective itself is injected.
-    """
-
-    def __init__(self, reduce_fn: Callable[[int, int], None], min_elems: int = 1 << 20):
-        self.reduce_fn = reduce_fn
-        self.min_elems = min_elems
-        self.start: Optional[int] = None
-        self.length = 0
-        self.issued: List[Tuple[int, int]] = []
-
-    def add(self, start: int, length: int):
-        if length <= 0:
-            return
-        if self.start is None:
-            self.start, self.length = start, length
-        elif start == self.start + self.length:
-            self.length += length
-        else:  # not adjacent: send what we have and start over
-            self.flush()
-            self.start, self.length = start, length
-        if self.length >= self.min_elems:
-            self.flush()
-
-    def flush(self):
-        if self.start is not None and self.length > 0:
-            self.reduce_fn(self.start, self.length)
-            self.issued.append((self.start, self.length))
-        self.start, self.length = None, 0
+class WbDpId(ctypes.Structure):
+    _fields_ = [("bytes", ctypes.c_uint8 * 128)]
 
 
-class _DevicePtr:
-    """Exposes a raw device range to torch through __cuda_array_interface__ (no copy)."""
+POLL_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)
+DP_AUTO, DP_ALLREDUCE, DP_SHARDED, DP_PEER = 0, 1, 2, 3
+DP_MODE_NAMES = {1: "allreduce", 2: "sharded", 3: "peer"}
 
-    def __init__(self, ptr: int, n: int, typestr: str = "<f4"):
-        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3, "strides": None}
+
+def _declare_dp(lib):
+    if getattr(lib, "_wb_dp_declared", False):
+        return
+    P, PP = ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)
+    i32, i64, f64 = ctypes.c_int, ctypes.c_int64, ctypes.c_double
+    I64P, U64P = ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_uint64)
+    sig = {
+        "wb_dp_unique_id": ([ctypes.POINTER(WbDpId)], i32),
+        "wb_dp_create": ([P, ctypes.POINTER(WbDpId), i32, i32, i32, i64, PP], i32),
+        "wb_dp_destroy": ([P], i32),
+        "wb_dp_mode": ([P], i32), "wb_dp_world": ([P], i32), "wb_dp_num_buckets": ([P], i32),
+        "wb_dp_bucket": ([P, i32, I64P, I64P], i32),
+        "wb_dp_step": ([P, U64P, i32], i32),
+        "wb_dp_submit": ([P, P, P], i32),
+        "wb_dp_step_submitted": ([P, U64P, i32, ctypes.POINTER(ctypes.c_float)], i32),
+        "wb_dp_wait": ([P, i32], i32),
+        "wb_dp_set_timing": ([P, i32], i32),
+        "wb_dp_timing_report": ([P], ctypes.c_char_p),
+        "wb_dp_plan_buckets": ([I64P, I64P, i32, i64, I64P, I64P, i32], i32),
+        "wb_watchdog_wait": ([POLL_FN, P, i32, i32], i32),
+        "wb_reduce_adam_broadcast": ([P, PP, PP, i32, i32, i64, i64, P, P, i64, f64, f64, f64, f64, f64, i32, f64], i32),
+        "wb_dp_selftest_wait": ([P, i32, i32], i32),
+    }
+    for name, (args, res) in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes, fn.restype = args, res
+    lib._wb_dp_declared = True
+
+
+def plan_buckets(lib, ranges: Sequence[Tuple[int, int]], min_elems: int) -> List[Tuple[int, int]]:
+    """How per-layer arena ranges (offset, length), in arena order, merge into exchange buckets (wb_dp_plan_buckets)."""
+    _declare_dp(lib)
+    n = len(ranges)
+    off = (ctypes.c_int64 * max(n, 1))(*[r[0] for r in ranges])
+    ln = (ctypes.c_int64 * max(n, 1))(*[r[1] for r in ranges])
+    bo, bl = (ctypes.c_int64 * max(n, 1))(), (ctypes.c_int64 * max(n, 1))()
+    nb = lib.wb_dp_plan_buckets(off, ln, n, min_elems, bo, bl, max(n, 1))
+    if nb < 0:
+        raise ValueError("wb_dp_plan_buckets: bad arguments")
+    return [(bo[i], bl[i]) for i in range(nb)]
+
+
+def watchdog_wait(lib, poll: Callable[[], int], timeout_ms: int, interval_us: int = 1000) -> int:
+    """Runs the library's host watchdog loop over `poll()` (0 = finished, 1 = still running, other = failed)."""
+    _declare_dp(lib)
+    cb = POLL_FN(lambda user: int(poll()))
+    return lib.wb_watchdog_wait(cb, None, timeout_ms, interval_us)
+
+
+def make_dp_id(lib) -> bytes:
+    """The 128-byte rendezvous id rank 0 creates and hands to the other ranks over any host channel."""
+    _declare_dp(lib)
+    out = WbDpId()
+    st = lib.wb_dp_unique_id(ctypes.byref(out))
+    if st != 0:
+        raise RuntimeError(f"wb_dp_unique_id: status {st}: {lib.wb_last_error().decode()}")
+    return ctypes.string_at(ctypes.addressof(out), 128)
 
 
 class DataParallelTrainer:
-    """Data-parallel wrapper: one process per GPU, every rank a full replica, the batch sharded.
+    """Handle on `WbDp` (include/weta_b200.h): the data-parallel form of the fused step.
 
-    The reference has no multi-GPU path; this adds the one exchange a data-parallel step needs.
-    Gradients are summed with NCCL (`torch.distributed`) on a side stream as soon as a bucket of the
-    arena is final, and that bucket's Adam update (with 1/world) follows on a third stream, both while
-    backward continues on the compute stream; the next step waits for the last update.
+    One process per GPU, every rank a full replica, the batch sharded.  The reference has no multi-GPU path; this adds
+    the one exchange a data-parallel step needs.  Streams, the NCCL communicator, the bucket plan, the peer-memory
+    kernel and the double-buffered upload all live behind the C ABI; this class only forwards calls.
     BatchNorm statistics stay per rank, as they would in the reference (it has no SyncBN).
     """
 
-    def __init__(self, trainer: FusedTrainer, compute_stream, world_size: int, bucket_elems: int = 1 << 20):
-        import torch
-        import torch.distributed as dist
-
-        self.torch, self.dist = torch, dist
+    def __init__(self, trainer: FusedTrainer, rank: int = 0, world_size: int = 1, dp_id: Optional[bytes] = None, mode: int = DP_AUTO,
+                 bucket_elems: int = 1 << 20):
         self.tr = trainer
-        self.world = world_size
-        self.stream = compute_stream
-        self.comm_stream = torch.cuda.Stream() if world_size > 1 else None
-        self.adam_stream = torch.cuda.Stream() if world_size > 1 else None
-        # a second handle on the same device whose kernels go to the optimizer stream
-        self.adam_backend = B200Backend(trainer.be.ordinal, self.adam_stream.cuda_stream) if world_size > 1 else None
-        self.step_t = 0
-        self.covered = 0
-        self.works = []
-        self.grad_view = torch.as_tensor(_DevicePtr(trainer.grads_ptr(), trainer.arena_len), device=f"cuda:{trainer.be.ordinal}")
-        self.bucketer = GradBucketer(self._all_reduce_range, bucket_elems)
-        base = trainer.grads_ptr()
+        self.lib = trainer.lib
+        _declare_dp(self.lib)
+        self.world, self.rank = world_size, rank
+        idp = None
         if world_size > 1:
-            trainer.set_bucket_callback(lambda ptr, n: self.bucketer.add((ptr - base) // 4, n))
-
-    def _all_reduce_range(self, start: int, length: int):
-        torch = self.torch
-        ev = torch.cuda.Event()
-        ev.record(self.stream)                   # everything queued so far, i.e. this bucket's gradients
-        self.comm_stream.wait_event(ev)
-        with torch.cuda.stream(self.comm_stream):
-            work = self.dist.all_reduce(self.grad_view[start:start + length], op=self.dist.ReduceOp.SUM, async_op=True)
-        with torch.cuda.stream(self.adam_stream):
-            work.wait()  # orders the optimizer stream after this bucket's sum
-            tr = self.tr
-            tr.be.check(tr.lib.wb_trainer_adam_range(tr.handle, self.adam_backend.handle, start, length, self.step_t, 1.0 / self.world))
-        self.works.append(work)
-        self.covered += length
-
-    def forward_backward_step(self, seeds=None):
-        """forward, backward with overlapped all-reduce and per-bucket Adam.  Inputs must already be staged."""
-        if self.world == 1:
-            self.tr.forward_backward(seeds)
-            self.tr.adam_step(1.0)
-            return
-        self.step_t = self.tr.lib.wb_trainer_begin_step(self.tr.handle)
-        self.covered = 0
-        self.tr.forward_backward(seeds)
-        self.bucketer.flush()
-        if self.covered != self.tr.arena_len:
-            raise RuntimeError(f"gradient buckets covered {self.covered} of {self.tr.arena_len} arena elements")
-        self.works.clear()
-        self.stream.wait_stream(self.adam_stream)  # the next step reads the updated parameters
-
-    def step_host(self, x_pinned, y_pinned, seeds=None) -> float:
-        """One step from pinned host tensors: upload, forward/backward (+ all-reduce), Adam, loss read-back."""
-        tr, be = self.tr, self.tr.be
-        be.check(be.lib.wb_upload_async(be.handle, x_pinned.data_ptr(), ctypes.c_void_p(tr.input_ptr()), x_pinned.numel() * 4))
-        be.check(be.lib.wb_upload_async(be.handle, y_pinned.data_ptr(), ctypes.c_void_p(tr.labels_ptr()), y_pinned.numel() * 8))
-        self.forward_backward_step(seeds)
-        return tr.loss()
-
-
-class PrefetchingStepper:
-    """Feeds host batches to a DataParallelTrainer with the upload of batch i+1 overlapped with step i.
-
-    Two device slots; `submit` enqueues the host-to-device copy of one pinned batch on a copy stream, `step` runs one
-    training step on the oldest submitted batch and returns its loss (a device-to-host read that waits for the
-    step).  The copy into a slot waits for the step that last read it; the step waits for its slot's copy.
-    """
-
-    def __init__(self, dp: DataParallelTrainer):
-        import torch
-
-        self.torch, self.dp = torch, dp
-        tr = dp.tr
-        dev = f"cuda:{tr.be.ordinal}"
-        n_in = tr.batch * int(np.prod(tr.in_shape))
-        self.slots = [(torch.empty(n_in, dtype=torch.float32, device=dev), torch.empty(tr.batch, dtype=torch.int64, device=dev)) for _ in range(2)]
-        self.copy_stream = torch.cuda.Stream()
-        self.ready = [torch.cuda.Event() for _ in range(2)]
-        self.consumed = [torch.cuda.Event() for _ in range(2)]
-        for ev in self.consumed:
-            ev.record(dp.stream)
-        self.submitted = 0
-        self.stepped = 0
-
-    def submit(self, x_pinned, y_pinned):
-        if self.submitted - self.stepped >= 2:
-            raise RuntimeError("both slots hold batches that have not been stepped yet")
-        slot = self.submitted % 2
-        with self.torch.cuda.stream(self.copy_stream):
-            self.copy_stream.wait_event(self.consumed[slot])
-            self.slots[slot][0].copy_(x_pinned, non_blocking=True)
-            self.slots[slot][1].copy_(y_pinned, non_blocking=True)
-            self.ready[slot].record(self.copy_stream)
-        self.submitted += 1
-
-    def step(self, seeds=None) -> float:
-        if self.stepped >= self.submitted:
-            raise RuntimeError("no submitted batch to step on")
-        slot = self.stepped % 2
-        tr = self.dp.tr
-        self.dp.stream.wait_event(self.ready[slot])
-        x, y = self.slots[slot]
-        tr.be.check(tr.lib.wb_trainer_set_input(tr.handle, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr())))
-        self.dp.forward_backward_step(seeds)
-        self.consumed[slot].record(self.dp.stream)
-        self.stepped += 1
-        return tr.loss()
+            assert dp_id is not None and len(dp_id) == 128, "more than one rank needs the 128-byte id made by rank 0"
+            idv = WbDpId()
+            ctypes.memmove(ctypes.addressof(idv), dp_id, 128)
+            idp = ctypes.byref(idv)
+        out = ctypes.c_void_p()
+        trainer.be.check(self.lib.wb_dp_create(trainer.handle, idp, rank, world_size, mode, bucket_elems, ctypes.byref(out)))
+        self.handle = out.value
+        self.mode = self.lib.wb_dp_mode(self.handle)
+        self.buckets = []
+        for i in range(self.lib.wb_dp_num_buckets(self.handle)):
+            off, ln = ctypes.c_int64(), ctypes.c_int64()
+            trainer.be.check(self.lib.wb_dp_bucket(self.handle, i, ctypes.byref(off), ctypes.byref(ln)))
+            self.buckets.append((off.value, ln.value))
 
     def close(self):
-        tr = self.dp.tr
-        tr.be.check(tr.lib.wb_trainer_set_input(tr.handle, None, None))
+        if self.handle:
+            self.lib.wb_dp_destroy(self.handle)
+            self.handle = None
+
+    def step(self, seeds=None):
+        """forward, backward with overlapped exchange and per-bucket Adam on the staged batch; asynchronous."""
+        tr = self.tr
+        seeds = tr.draw_dropout_seeds() if seeds is None else seeds
+        tr.be.check(self.lib.wb_dp_step(self.handle, seeds, tr.n_dropout))
+
+    def submit(self, x_ptr: int, y_ptr: int):
+        """Queues the upload of one batch from pinned host memory into the next device slot."""
+        self.tr.be.check(self.lib.wb_dp_submit(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr)))
+
+    def step_submitted(self, seeds=None, read_loss: bool = True) -> Optional[float]:
+        """One step on the oldest submitted batch; returns its loss (a device-to-host read that waits for the step)."""
+        tr = self.tr
+        seeds = tr.draw_dropout_seeds() if seeds is None else seeds
+        out = ctypes.c_float()
+        tr.be.check(self.lib.wb_dp_step_submitted(self.handle, seeds, tr.n_dropout, ctypes.byref(out) if read_loss else None))
+        return out.value if read_loss else None
+
+    def wait(self, timeout_ms: int = 0):
+        self.tr.be.check(self.lib.wb_dp_wait(self.handle, timeout_ms))
+
+    def set_timing(self, on: bool):
+        self.tr.be.check(self.lib.wb_dp_set_timing(self.handle, int(on)))
+
+    def timing_report(self) -> Tuple[int, float]:
+        _, calls, ms = self.lib.wb_dp_timing_report(self.handle).decode().split()
+        return int(calls), float(ms)

@@ -1,18 +1,15 @@
-"""The benchmark workloads: synthetic inputs and the primitive-mode training step.
+"""The benchmark workloads: model configurations and synthetic inputs drawn on the device.
 
 Synthetic data stands in for MNIST / CIFAR-10 (neither is available offline): tensors of the same
-shape and value range, drawn from the counter RNG so every backend sees identical inputs
-without any file moving.
+shape and value range, drawn from the counter RNG (`Backend::random`, crates/weta-core/src/backend.rs:97-105)
+so every backend sees identical inputs without any file moving.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Tuple
+from typing import Tuple
 
-from . import nn
-from .autograd import Var
-from .core import Distribution, DType, manual_seed
-from .tensor import Tensor
+from .core import Distribution, DType, Layout
 
 
 @dataclass(frozen=True)
@@ -46,35 +43,17 @@ MNIST_CNN = CnnConfig("cnn-mnist-422k", 1, 28, 32, 64, 128)
 WIDE_CNN = CnnConfig("cnn-wide-17M", 3, 32, 128, 256, 1024)
 
 
-def synthetic_batch(cfg: CnnConfig, batch: int, step: int, rank: int, backend) -> Tuple[Tensor, Tensor]:
-    """Images U[0,1) and uniform labels, seeded by (step, rank)."""
+def batch_seeds(step: int, rank: int) -> Tuple[int, int]:
+    """Counter-RNG seeds of the images and the labels of one synthetic batch."""
     seed = 10_000 + 1_000_003 * rank + step
-    x = Tensor.random_seeded([batch, cfg.in_ch, cfg.hw, cfg.hw], Distribution.uniform(0.0, 1.0), DType.F32, backend, seed)
-    y = Tensor.random_seeded([batch], Distribution.uniform(0.0, float(cfg.classes)), DType.I64, backend, seed + 500_000_000)
-    return x, y
+    return seed, seed + 500_000_000
 
 
-def build_cnn(cfg: CnnConfig, backend, seed: int = 42) -> nn.Sequential:
-    manual_seed(seed)
-    return nn.cnn(backend, cfg.in_ch, cfg.hw, cfg.c1, cfg.c2, cfg.hidden, cfg.classes, cfg.dropout)
-
-
-def primitive_train_step(model: nn.Sequential, opt, x: Tensor, y: Tensor, grad_hook=None) -> float:
-    """One step exactly as crates/weta/examples/mnist_cnn.rs:63-73 runs it: forward, cross-entropy,
-    zero_grad, backward, step, loss.item().  `grad_hook(params)` runs between backward and the
-    optimizer (the data-parallel gradient average)."""
-    loss = nn.cross_entropy(model(Var(x)), y)
-    opt.zero_grad()
-    loss.backward()
-    if grad_hook is not None:
-        grad_hook(model.parameters())
-    opt.step()
-    return loss.item()
-
-
-def mlp_batch(batch: int, step: int, backend) -> Tuple[Tensor, Tensor]:
-    """Config-1 inputs: pixels k/255 with k uniform in 0..255, labels uniform in 0..9."""
-    px = Tensor.random_seeded([batch, 784], Distribution.uniform(0.0, 256.0), DType.I64, backend, 10_000 + step)
-    x = px.to_dtype(DType.F32).mul_scalar(1.0 / 255.0)
-    y = Tensor.random_seeded([batch], Distribution.uniform(0.0, 10.0), DType.I64, backend, 20_000 + step)
+def synthetic_batch_device(cfg: CnnConfig, batch: int, step: int, rank: int, backend):
+    """Images U[0,1) f32 [batch, in_ch, hw, hw] and uniform i64 labels [batch] as device storages, seeded by
+    (step, rank).  Integer tensors are drawn as f64 and cast (crates/weta-tensor/src/random.rs:104-110)."""
+    sx, sy = batch_seeds(step, rank)
+    x = backend.random(batch * cfg.in_ch * cfg.hw * cfg.hw, DType.F32, Distribution.uniform(0.0, 1.0), sx)
+    yf = backend.random(batch, DType.F64, Distribution.uniform(0.0, float(cfg.classes)), sy)
+    y = backend.cast(yf, Layout.contiguous([batch]), DType.F64, DType.I64)
     return x, y
