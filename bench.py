@@ -12,8 +12,11 @@ split evenly over the ranks, f32 storage with TF32 tensor-core contractions, Ada
 seed shared by all ranks.  A step is forward + cross-entropy + backward + gradient all-reduce + Adam.
 
 One JSON line is printed by rank 0.  `value` times the step with inputs already resident in HBM;
-`e2e` times the same step through the host-facing call with pinned host buffers (upload of the batch and
-read-back of the loss inside the timed region).
+`e2e` times the same step through the host-facing C-ABI calls (wb_dp_submit / wb_dp_step_submitted) with pinned host
+buffers: upload of the batch and read-back of the loss inside the timed region.  Each timed pass of K steps is repeated
+(--repeats, default 5); `value` and `e2e` are the medians, the spread and the SM clock of each leg are on the line.
+Multi-GPU plumbing (rendezvous, barrier, max over ranks) is torch.distributed over gloo; the gradient exchange itself
+is the library's (NCCL or its peer-memory kernel, include/weta_b200.h wb_dp_*).
 """
 from __future__ import annotations
 
@@ -95,6 +98,7 @@ def cpu_reference_run(steps: int, warmup: int, sample_batch: int):
     from weta_b200.workloads import WIDE_CNN
 
     be = OracleBackend()
+    be.set_num_threads(os.cpu_count() or 1)  # a launcher may have exported OMP_NUM_THREADS=1 for its ranks
     model = build_cnn(WIDE_CNN, be, 42)
     opt = nn.Adam(model.parameters(), 1e-3)
     batches = [synthetic_batch(WIDE_CNN, sample_batch, s, 0, be) for s in range(2)]
@@ -126,26 +130,49 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def load_traffic():
+    """DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) of the trainer's ops at batch 512: lines
+    "label bytes" in the capture summary kept beside the other profiler summaries."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic_trainer_batch512.txt")
+    out = {}
+    if os.path.exists(path):
+        for line in open(path):
+            parts = line.split()
+            if len(parts) == 2 and not line.startswith("#"):
+                out[parts[0]] = float(parts[1])
+    return out
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2] if len(xs) % 2 else 0.5 * (xs[len(xs) // 2 - 1] + xs[len(xs) // 2])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5, help="timed passes of --steps steps each; the line reports their median")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--cpu-batch", type=int, default=32, help="sample batch of the CPU baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH)
+    ap.add_argument("--dp-mode", default="auto", choices=["auto", "allreduce", "sharded", "peer"], help="gradient exchange of the data-parallel step")
+    ap.add_argument("--bucket-elems", type=int, default=1 << 20)
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+
+    import ctypes
 
     import torch
     import torch.distributed as dist
 
     from weta_b200.backend import B200Backend
-    from weta_b200.core import manual_seed
-    from weta_b200.trainer import PrefetchingStepper, DataParallelTrainer, FusedTrainer, cnn_specs
-    from weta_b200.workloads import WIDE_CNN, synthetic_batch
+    from weta_b200.core import DType, Layout, manual_seed
+    from weta_b200.trainer import DP_MODE_NAMES, DataParallelTrainer, FusedTrainer, cnn_specs, make_dp_id
+    from weta_b200.workloads import WIDE_CNN, synthetic_batch_device
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -154,44 +181,54 @@ def main():
     assert args.warmup >= 3, "at least 3 warm-up steps"
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("gloo")  # host-side plumbing only: rendezvous id, barriers, max over ranks
     cfg = WIDE_CNN
     gb = args.global_batch
     assert gb % world == 0
     batch = gb // world
 
-    stream = torch.cuda.Stream()
+    # The compute stream outranks the library's side streams (exchange, optimizer, upload), which are created at the
+    # lowest priority: when both have blocks ready the step's own kernels are scheduled first.
+    stream = torch.cuda.Stream(priority=-1)
     be = B200Backend(local, stream=stream.cuda_stream)
     manual_seed(42)  # one model seed shared by all ranks
     tr = FusedTrainer(be, cnn_specs(cfg), batch, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=1)
     tr.init_from_global_rng()
-    dp = DataParallelTrainer(tr, stream, world)
+    dp_id = None
+    if world > 1:
+        box = [make_dp_id(be.lib) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        dp_id = box[0]
+    mode = {"auto": 0, "allreduce": 1, "sharded": 2, "peer": 3}[args.dp_mode]
+    dp = DataParallelTrainer(tr, rank, world, dp_id, mode=mode, bucket_elems=args.bucket_elems)
 
     # Synthetic batches: drawn on the device from the counter RNG, then copied to pinned host memory for
     # the end-to-end leg.  Two distinct batches alternate.
     n_in = batch * cfg.in_ch * cfg.hw * cfg.hw
     dev_batches, host_batches = [], []
     for s in range(2):
-        x, y = synthetic_batch(cfg, batch, s, rank, be)
+        x, y = synthetic_batch_device(cfg, batch, s, rank, be)
         dev_batches.append((x, y))
         hx = torch.empty(n_in, dtype=torch.float32, pin_memory=True)
         hy = torch.empty(batch, dtype=torch.int64, pin_memory=True)
-        hx.copy_(torch.from_numpy(x.numpy().reshape(-1)))
-        hy.copy_(torch.from_numpy(y.numpy().reshape(-1)))
+        hx.copy_(torch.from_numpy(be.to_host(x, Layout.contiguous([n_in]), DType.F32)))
+        hy.copy_(torch.from_numpy(be.to_host(y, Layout.contiguous([batch]), DType.I64)))
         host_batches.append((hx, hy))
-    import ctypes
+    lx, ly = Layout.contiguous([n_in]), Layout.contiguous([batch])
 
     def stage_from_device(i):
         x, y = dev_batches[i % 2]
-        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(x.layout.view(x.storage.ptr, 0)), 0, ctypes.c_void_p(tr.input_ptr())))
-        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(y.layout.view(y.storage.ptr, 2)), 2, ctypes.c_void_p(tr.labels_ptr())))
+        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(lx.view(x.ptr, DType.F32)), DType.F32, ctypes.c_void_p(tr.input_ptr())))
+        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(ly.view(y.ptr, DType.I64)), DType.I64, ctypes.c_void_p(tr.labels_ptr())))
 
     def barrier():
+        torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
     def timed(fn, steps):
+        """K steps bracketed by barrier + synchronize, timed with CUDA events on the compute stream; max over ranks."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
@@ -199,59 +236,82 @@ def main():
             fn(i)
         e1.record(stream)
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
     def resident_step(i):
         stage_from_device(i)       # device-to-device: the batch is already in HBM
-        dp.forward_backward_step()
+        dp.step()
 
     losses = []
+    pending = [0]
 
     # End to end: every step's batch is copied from pinned host memory inside the timed region; the copy of batch
     # i + 1 is in flight while step i computes (two device slots), and every step ends with the loss read-back.
-    stepper = PrefetchingStepper(dp)
-
     def e2e_step(i):
-        if stepper.submitted == stepper.stepped:
-            stepper.submit(*host_batches[i % 2])
-        stepper.submit(*host_batches[(i + 1) % 2])
-        losses.append(stepper.step())
+        if pending[0] == 0:
+            dp.submit(host_batches[i % 2][0].data_ptr(), host_batches[i % 2][1].data_ptr())
+            pending[0] += 1
+        dp.submit(host_batches[(i + 1) % 2][0].data_ptr(), host_batches[(i + 1) % 2][1].data_ptr())
+        losses.append(dp.step_submitted())
+
+    def drain_e2e():
+        while pending[0] > 0:  # a pass leaves one batch submitted ahead; step on it so the slots start empty again
+            dp.step_submitted()
+            pending[0] -= 1
 
     # ---- warm-up ------------------------------------------------------------------------------
     for i in range(args.warmup):
         resident_step(i)
+    dp.wait()
     be.gemm_check()
 
-    # ---- value: inputs resident in HBM, per-op timing on for the roofline ------------------------
+    # ---- value: inputs resident in HBM ----------------------------------------------------------
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     launches0 = be.launch_count()
-    total_ms = timed(resident_step, args.steps)
-    launches = be.launch_count() - launches0
-    # A second timed pass of the same K steps with an event pair around every trainer op, for the roofline
-    # (the ~90 extra event records per step open small gaps between kernels, so `value` comes from the pass above).
+    value_passes = [timed(resident_step, args.steps) for _ in range(args.repeats)]
+    launches = (be.launch_count() - launches0) // args.repeats
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = median(value_passes)
+    value = gb * args.steps / (total_ms / 1e3)
+
+    # ---- roofline pass: the same K steps with an event pair around every trainer op ---------------
+    # (the ~90 extra event records per step open small gaps between kernels, so `value` comes from the passes above)
     tr.set_timing(True)
+    dp.set_timing(True)
     tr.timing_report()
     timed_ops_ms = timed(resident_step, args.steps)
     op_times = tr.timing_report()
+    bucket_calls, bucket_ms = dp.timing_report()
     tr.set_timing(False)
-    clocks = sampler.stop() if rank == 0 else None
-    value = gb * args.steps / (total_ms / 1e3)
+    dp.set_timing(False)
 
-    # ---- e2e: through the host-facing call ------------------------------------------------------
-    for i in range(2):
-        e2e_step(i)
-    e2e_ms = timed(e2e_step, args.steps)
+    # ---- e2e: through the host-facing calls -------------------------------------------------------
+    e2e_step(0)
+    pending[0] = 1
+    e2e_step(1)
+    sampler2 = ClockSampler(local)
+    if rank == 0:
+        sampler2.start()
+    e2e_passes = []
+    for _ in range(args.repeats):
+        e2e_passes.append(timed(e2e_step, args.steps))
+    e2e_clocks = sampler2.stop() if rank == 0 else None
+    drain_e2e()
+    e2e_ms = median(e2e_passes)
     e2e_value = gb * args.steps / (e2e_ms / 1e3)
-    stepper.close()
+    dp.wait()
     be.gemm_check()
+    dp_mode_used = DP_MODE_NAMES.get(dp.mode, str(dp.mode)) if world > 1 else "none (one rank)"
 
     if rank != 0:
+        dp.close()
         if world > 1:
+            dist.barrier()
             dist.destroy_process_group()
         return
 
@@ -281,14 +341,9 @@ def main():
         "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
         "L6.adam": ("hbm", 28.0 * tr.arena_len),
     }
-    # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu captures summarised under
-    # profiles/, taken at batch 512 because a full-size step is too large to capture; every one of these ops
-    # streams its tensors once per image, so the traffic is scaled by batch / 512.
-    ncu_traffic_batch512 = {
-        "L0.bn_relu_pool_bwd": 908.4e6, "L1.bn_relu_pool_bwd": 699.0e6, "L0.bn_relu_pool_fwd": 425.2e6, "L1.bn_relu_pool_fwd": 150.3e6,
-        "L1.conv_fwd_gemm": 298.7e6, "L1.conv_wgrad_gemm": 363.2e6, "L1.conv_dgrad_gemm": 454.8e6,
-        "L0.conv_fwd_gemm": 269.6e6, "L0.conv_wgrad_gemm": 330.1e6,
-    }
+    # DRAM bytes per launch from the ncu capture at batch 512 (a full-size step is too large to capture); every one of
+    # these ops streams its tensors once per image, so the traffic is scaled by batch / 512.
+    ncu_traffic_batch512 = load_traffic()
     shares = {k: round(v[1] / timed_ops_ms, 4) for k, v in sorted(op_times.items(), key=lambda kv: -kv[1][1])}
     top_name, (top_calls, top_ms) = max(op_times.items(), key=lambda kv: kv[1][1])
     tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
@@ -315,11 +370,17 @@ def main():
     gemm_flops = sum(work[k][1] * v[0] for k, v in op_times.items() if k in work and work[k][0] == "tensor")
     roofline["all_contractions_tflops"] = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
     roofline["per_op"] = {k: {"bound": v["bound"], "achieved": round(v["achieved"], 1), "frac": round(v["frac"], 3)} for k, v in per_op.items()}
+    roofline["side_stream_ms_per_step"] = round(bucket_ms / max(args.steps, 1), 4)  # exchange + optimizer of all buckets (overlaps backward)
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         r = cpu_reference_run(2, 1, args.cpu_batch)
         cpu = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    def with_product(c, ms_per_step):
+        c = dict(c or {})
+        c["ms_per_step_x_sm_mhz"] = round(ms_per_step * c["sm_mhz"], 1) if c.get("sm_mhz") else None
+        return c
 
     line = {
         "metric": METRIC, "value": value, "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -327,18 +388,27 @@ def main():
         "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "global_batch": gb, "per_gpu_batch": batch, "image": "3x32x32", "params": cfg.num_params(), "optimizer": "Adam lr 1e-3",
-                   "parallelism": f"dp{world}", "l2": "per-step working set is several GB, far larger than the 126 MB L2; two batches alternate",
-                   "step": "upload/stage + forward + cross-entropy + backward + all-reduce + Adam",
-                   "timing": "value: K steps timed once without per-op events; roofline / op_time_shares: the same K steps timed again with an event pair around every op; e2e: batch i+1 uploaded from pinned memory while step i runs, loss read back every step"},
+                   "parallelism": f"dp{world}", "gradient_exchange": dp_mode_used, "buckets": len(dp.buckets),
+                   "l2": "per-step working set is several GB, far larger than the 126 MB L2; two batches alternate",
+                   "step": "upload/stage + forward + cross-entropy + backward + gradient exchange + Adam",
+                   "timing": f"value / e2e: median of {args.repeats} passes of K steps each, every pass bracketed by barrier + synchronize and timed "
+                             "with CUDA events on the compute stream, max over ranks; roofline / op_time_shares: the same K steps timed once more with "
+                             "an event pair around every op; e2e: batch i+1 uploaded from pinned memory while step i runs, loss read back every step"},
+        "repeats": {"passes": args.repeats, "value_ms_per_step": [round(p / args.steps, 4) for p in value_passes],
+                    "value_min_max": [gb * args.steps / (max(value_passes) / 1e3), gb * args.steps / (min(value_passes) / 1e3)],
+                    "e2e_ms_per_step": [round(p / args.steps, 4) for p in e2e_passes],
+                    "e2e_min_max": [gb * args.steps / (max(e2e_passes) / 1e3), gb * args.steps / (min(e2e_passes) / 1e3)]},
         "e2e": {"value": e2e_value, "unit": "samples/s", "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": n_in * 4 + batch * 8,
-                "d2h_bytes_per_step": 4, "last_loss": losses[-1]},
-        "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "op_time_shares": shares,
+                "d2h_bytes_per_step": 4, "last_loss": losses[-1], "clocks": with_product(e2e_clocks, e2e_ms / args.steps)},
+        "gpu_launches": int(launches), "clocks": with_product(clocks, total_ms / args.steps), "roofline": roofline, "op_time_shares": shares,
         "train_tflops": cfg.train_flops_per_sample() * value / 1e12,
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
+    dp.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -42,6 +42,7 @@ def _load():
     lib.wo_splitmix64.argtypes = [u64, u64]
     lib.wo_splitmix64.restype = u64
     lib.wo_set_num_threads.argtypes = [i32]
+    lib.wo_set_matmul_test_mode.argtypes = [i32, i32]
     return lib
 
 
@@ -55,6 +56,14 @@ class OracleBackend:
 
     def num_threads(self) -> int:
         return int(self.lib.wo_num_threads())
+
+    def set_num_threads(self, n: int) -> None:
+        self.lib.wo_set_num_threads(int(n))
+
+    def set_matmul_test_mode(self, tf32_operands: bool = False, f64_accumulate: bool = False) -> None:
+        """f32 matmul with operands truncated to TF32 (how a tensor-core instruction reads them) and / or the sum over k
+        kept in double; both off restores the plain restatement of weta-cpu."""
+        self.lib.wo_set_matmul_test_mode(int(tf32_operands), int(f64_accumulate))
 
     # helpers
     @staticmethod

@@ -378,29 +378,80 @@ int reduce_any(int op, const WoView& x, int axis, void* out) {
 // crates/weta-cpu/src/lib.rs:319-365.  out[b][i][j] = sum_k a[b][i][k] * b[b][k][j], k ascending,
 // accumulated in T.  The i-k-j loop keeps that order per output while letting the inner loop
 // vectorise; B is packed to unit column stride first when it is not already.
+// Test-only switches for f32 products (default off = the restatement above):
+//   g_tf32_operands   both operands lose their low 13 mantissa bits first, which is how a TF32 tensor-core
+//                     instruction reads an f32 operand; a GPU run in TF32 mode then differs from this oracle by
+//                     accumulation error only, not by operand rounding;
+//   g_f64_accumulate  the sum over k is kept in double and rounded to f32 once.
+bool g_tf32_operands = false;
+bool g_f64_accumulate = false;
+
+inline float tf32_trunc(float v) {
+    uint32_t u;
+    std::memcpy(&u, &v, 4);
+    u &= 0xFFFFE000u;
+    std::memcpy(&v, &u, 4);
+    return v;
+}
+
 template <class T>
 void matmul_float(const WoView& a, const WoView& b, T* out) {
     int64_t bs = a.shape[0], m = a.shape[1], k = a.shape[2], n = b.shape[2];
     if (bs * m * n == 0) return;
     const T* ap = static_cast<const T*>(a.data) + a.offset;
     const T* bp = static_cast<const T*>(b.data) + b.offset;
+    const bool special = sizeof(T) == 4 && (g_tf32_operands || g_f64_accumulate);
     std::vector<T> packed;
     for (int64_t batch = 0; batch < bs; ++batch) {
         const T* A = ap + batch * a.stride[0];
         const T* B = bp + batch * b.stride[0];
         int64_t brs = b.stride[1];
-        if (b.stride[2] != 1 && n > 1) {
+        if ((b.stride[2] != 1 && n > 1) || (special && g_tf32_operands)) {
             if (batch == 0 || b.stride[0] != 0) {
                 packed.resize(static_cast<size_t>(k * n));
 #pragma omp parallel for schedule(static)
                 for (int64_t kk = 0; kk < k; ++kk)
-                    for (int64_t j = 0; j < n; ++j) packed[kk * n + j] = B[kk * b.stride[1] + j * b.stride[2]];
+                    for (int64_t j = 0; j < n; ++j) {
+                        T v = B[kk * b.stride[1] + j * b.stride[2]];
+                        if constexpr (sizeof(T) == 4) { if (g_tf32_operands) v = tf32_trunc(v); }
+                        packed[kk * n + j] = v;
+                    }
             }
             B = packed.data();
             brs = n;
         }
         T* O = out + batch * m * n;
         int64_t as1 = a.stride[1], as2 = a.stride[2];
+        if (special) {
+#pragma omp parallel
+            {
+                std::vector<double> acc(static_cast<size_t>(n));
+#pragma omp for schedule(static)
+                for (int64_t i = 0; i < m; ++i) {
+                    T* orow = O + i * n;
+                    if (g_f64_accumulate) {
+                        std::fill(acc.begin(), acc.end(), 0.0);
+                        for (int64_t kk = 0; kk < k; ++kk) {
+                            T av = A[i * as1 + kk * as2];
+                            if constexpr (sizeof(T) == 4) { if (g_tf32_operands) av = tf32_trunc(av); }
+                            const double avd = static_cast<double>(av);
+                            const T* brow = B + kk * brs;
+                            for (int64_t j = 0; j < n; ++j) acc[j] += avd * static_cast<double>(brow[j]);
+                        }
+                        for (int64_t j = 0; j < n; ++j) orow[j] = static_cast<T>(acc[j]);
+                    } else {
+                        for (int64_t j = 0; j < n; ++j) orow[j] = 0;
+                        for (int64_t kk = 0; kk < k; ++kk) {
+                            T av = A[i * as1 + kk * as2];
+                            if constexpr (sizeof(T) == 4) av = tf32_trunc(av);
+                            const T* brow = B + kk * brs;
+                            for (int64_t j = 0; j < n; ++j) orow[j] = orow[j] + av * brow[j];
+                        }
+                    }
+                }
+            }
+            continue;
+        }
 #pragma omp parallel for schedule(static)
         for (int64_t i = 0; i < m; ++i) {
             T* orow = O + i * n;
@@ -531,6 +582,11 @@ extern "C" {
 
 int wo_num_threads() { return omp_get_max_threads(); }
 void wo_set_num_threads(int n) { omp_set_num_threads(n); }
+// Test-only: TF32-truncated operands and / or double accumulation for f32 matmul (see matmul_float).
+void wo_set_matmul_test_mode(int tf32_operands, int f64_accumulate) {
+    g_tf32_operands = tf32_operands != 0;
+    g_f64_accumulate = f64_accumulate != 0;
+}
 
 // crates/weta-cpu/src/lib.rs:510-512
 int wo_unary(int op, double p1, double p2, const WoView* x, void* out) {

@@ -29,3 +29,30 @@ def gpu():
     """The CUDA backend.  Fails loudly (never falls back) when the extension or device is missing."""
     from weta_b200.backend import B200Backend
     return B200Backend(0)
+
+
+@pytest.fixture(scope="session")
+def report():
+    """report(name, **numbers): appends one JSON line of measured figures (actual error against the tolerance asserted,
+    timings) to the file named by WETA_B200_TEST_REPORT, when that variable is set; otherwise does nothing."""
+    import json
+
+    path = os.environ.get("WETA_B200_TEST_REPORT")
+
+    def write(name, **numbers):
+        if path:
+            with open(path, "a") as f:
+                f.write(json.dumps({"test": name, **numbers}) + "\n")
+
+    return write
+
+
+@pytest.fixture()
+def tf32_oracle(oracle):
+    """The oracle with f32 matmul operands truncated to TF32 and the sum over k kept in double: what a TF32 tensor-core
+    contraction computes, up to the GPU's own accumulation error.  Restored to the plain restatement afterwards."""
+    oracle.set_matmul_test_mode(True, True)
+    try:
+        yield oracle
+    finally:
+        oracle.set_matmul_test_mode(False, False)

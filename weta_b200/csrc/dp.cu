@@ -143,6 +143,7 @@ __global__ void peer_announce_wait(PeerPtrs pp, int world, int rank, int bucket,
         store_release_sys(use_done ? &f->done[bucket][rank] : &f->ready[bucket][rank], seq);
     }
     if (wait) {
+        if (*reinterpret_cast<volatile uint32_t*>(status) != 0) return;  // an earlier wait of this step already gave up
         const PeerFlags* f = pp.flags[rank];
         const uint32_t* word = use_done ? &f->done[bucket][p] : &f->ready[bucket][p];
         const unsigned long long t0 = global_ns();

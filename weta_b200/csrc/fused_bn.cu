@@ -96,22 +96,79 @@ __global__ void bn_finalize_kernel(const double* __restrict__ part, int splits, 
     }
 }
 
-// The same from plain sums (sum x, sum x^2 per channel, in double) that a producer of x accumulated while it wrote x.
-__global__ void bn_finalize_sums_kernel(const double* __restrict__ sums, int c_total, int64_t count, float eps, float momentum,
-                                        float one_minus_momentum, float* __restrict__ mean, float* __restrict__ rstd,
-                                        float* __restrict__ running_mean, float* __restrict__ running_var) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= c_total) return;
-    const double dm = sums[2 * c] / static_cast<double>(count);
-    double var = sums[2 * c + 1] / static_cast<double>(count) - dm * dm;
-    if (var < 0.0) var = 0.0;
-    float m = static_cast<float>(dm), v = static_cast<float>(var);
+// Batch statistics from the sums a producer of x accumulated while it wrote x: per channel, in double, the sum and
+// the sum of squares of (x - pivot[c]) (pivot null = 0; for a convolution the pivot is its bias, so the sums are those
+// of the raw accumulator).  variance = E[d^2] - E[d]^2 loses digits when |E[d]| >> the standard deviation: the
+// producer's per-tile partial sums are f32, so E[d^2] carries about 1e-7 of relative error and a channel whose
+// variance is below 1e-3 of E[d^2] would keep fewer than four digits of it.  Such channels are left to
+// bn_stats_redo_kernel, which re-reads x; both kernels evaluate the same predicate on the same sums.
+__device__ __forceinline__ bool sums_cancel(double e1, double e2) { return !(e2 - e1 * e1 > 1e-3 * e2) && e2 > 0.0; }
+
+__device__ __forceinline__ void bn_store_stats(int c, double mean_d, double var_d, int64_t count, float eps, float momentum, float one_minus_momentum,
+                                               float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ running_mean,
+                                               float* __restrict__ running_var) {
+    if (var_d < 0.0) var_d = 0.0;
+    float m = static_cast<float>(mean_d), v = static_cast<float>(var_d);
     mean[c] = m;
     rstd[c] = 1.f / sqrtf(v + eps);
     if (running_mean) {
+        // running = running*(1-m) + batch*m with every product and sum rounded separately (functional.rs:165-167)
         float unbiased = __fadd_rn(__fmul_rn(v, static_cast<float>(static_cast<double>(count) / static_cast<double>((count > 2 ? count : 2) - 1))), 0.f);
         running_mean[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_mean[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(m, momentum), 0.f));
         running_var[c] = __fadd_rn(__fadd_rn(__fmul_rn(running_var[c], one_minus_momentum), 0.f), __fadd_rn(__fmul_rn(unbiased, momentum), 0.f));
+    }
+}
+
+__global__ void bn_finalize_sums_kernel(const double* __restrict__ sums, const float* __restrict__ pivot, int c_total, int64_t count, float eps,
+                                        float momentum, float one_minus_momentum, float* __restrict__ mean, float* __restrict__ rstd,
+                                        float* __restrict__ running_mean, float* __restrict__ running_var) {
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= c_total) return;
+    const double e1 = sums[2 * c] / static_cast<double>(count), e2 = sums[2 * c + 1] / static_cast<double>(count);
+    if (sums_cancel(e1, e2)) return;  // bn_stats_redo_kernel writes this channel
+    bn_store_stats(c, (pivot ? static_cast<double>(pivot[c]) : 0.0) + e1, e2 - e1 * e1, count, eps, momentum, one_minus_momentum, mean, rstd,
+                   running_mean, running_var);
+}
+
+// One block per channel; returns at once unless the channel's sums cancel (see above).  Then the block reads the
+// channel's n_img planes again and sums (x - m0), (x - m0)^2 about m0 = pivot + E[d], which is already within
+// rounding of the mean, so nothing cancels.
+__global__ void __launch_bounds__(THREADS) bn_stats_redo_kernel(const float* __restrict__ x, const double* __restrict__ sums,
+                                                                 const float* __restrict__ pivot, int64_t n_img, int c_total, int64_t hw, float eps,
+                                                                 float momentum, float one_minus_momentum, float* __restrict__ mean,
+                                                                 float* __restrict__ rstd, float* __restrict__ running_mean,
+                                                                 float* __restrict__ running_var) {
+    const int c = blockIdx.x;
+    const int64_t count = n_img * hw;
+    const double e1 = sums[2 * c] / static_cast<double>(count), e2 = sums[2 * c + 1] / static_cast<double>(count);
+    if (!sums_cancel(e1, e2)) return;
+    const float m0 = static_cast<float>((pivot ? static_cast<double>(pivot[c]) : 0.0) + e1);
+    double s1 = 0.0, s2 = 0.0;
+    float a1 = 0.f, a2 = 0.f;
+    int run = 0;
+    for (int64_t n = 0; n < n_img; ++n) {
+        const float* plane = x + (n * c_total + c) * hw;
+        for (int64_t p = threadIdx.x; p < hw; p += THREADS) {
+            const float d = plane[p] - m0;
+            a1 += d;
+            a2 += d * d;
+            if (++run == 64) { s1 += a1; s2 += a2; a1 = a2 = 0.f; run = 0; }
+        }
+    }
+    s1 += a1;
+    s2 += a2;
+    __shared__ double r1[THREADS], r2[THREADS];
+    r1[threadIdx.x] = s1;
+    r2[threadIdx.x] = s2;
+    __syncthreads();
+    for (int s = THREADS / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) { r1[threadIdx.x] += r1[threadIdx.x + s]; r2[threadIdx.x] += r2[threadIdx.x + s]; }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const double dm = r1[0] / static_cast<double>(count);
+        bn_store_stats(c, static_cast<double>(m0) + dm, r2[0] / static_cast<double>(count) - dm * dm, count, eps, momentum, one_minus_momentum, mean,
+                       rstd, running_mean, running_var);
     }
 }
 
@@ -732,10 +789,11 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
 
 // BatchNorm2d (training statistics) -> ReLU -> MaxPool2d(2); y_left / y_right (both or neither) also receive the
 // pooled tensor shifted one column right / left, zeros shifted in (needs w / 8 in {1, 2, 4, ..., 32}, aligned buffers).
-// channel_sums (optional): per channel (sum x, sum x^2) in double, when the producer of x already has them.
+// channel_sums (optional): per channel (sum d, sum d^2) in double with d = x - sums_pivot[channel] (pivot null = 0), when
+// the producer of x already has them.
 int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
                                 float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
-                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums) {
+                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums, const float* sums_pivot) {
     WB_REQUIRE(b && x && gamma && beta && y_pooled, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_fwd: height and width must be even");
     WB_REQUIRE((y_left == nullptr) == (y_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_fwd: give both shifted outputs or neither");
@@ -743,8 +801,14 @@ int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t
         // (sum, sum of squares) per channel already accumulated by the kernel that wrote x
         WB_REQUIRE(n * h * w > 0, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: empty input");
         bn_finalize_sums_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(
-            channel_sums, static_cast<int>(c), n * h * w, static_cast<float>(eps), static_cast<float>(momentum), static_cast<float>(1.0 - momentum),
-            save_mean, save_rstd, running_mean, running_var);
+            channel_sums, sums_pivot, static_cast<int>(c), n * h * w, static_cast<float>(eps), static_cast<float>(momentum),
+            static_cast<float>(1.0 - momentum), save_mean, save_rstd, running_mean, running_var);
+        WB_LAUNCH_OK(b);
+        // Channels whose sums cancel are recomputed from x (every other block of this launch returns at once).
+        bn_stats_redo_kernel<<<static_cast<unsigned>(c), THREADS, 0, b->stream>>>(x, channel_sums, sums_pivot, n, static_cast<int>(c), h * w,
+                                                                                  static_cast<float>(eps), static_cast<float>(momentum),
+                                                                                  static_cast<float>(1.0 - momentum), save_mean, save_rstd, running_mean,
+                                                                                  running_var);
         WB_LAUNCH_OK(b);
     } else {
         WB_TRY(wb_bn2d_stats(b, x, n, c, h * w, eps, momentum, save_mean, save_rstd, running_mean, running_var));
@@ -781,7 +845,7 @@ extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int6
                                    const float* beta, float* running_mean, float* running_var, double momentum, double eps, float* y_pooled,
                                    float* save_mean, float* save_rstd) {
     return wb_bn_relu_pool_fwd_shifted(b, x, n, c, h, w, gamma, beta, running_mean, running_var, momentum, eps, y_pooled, save_mean, save_rstd,
-                                       nullptr, nullptr, nullptr);
+                                       nullptr, nullptr, nullptr, nullptr);
 }
 
 // Backward of BatchNorm2d -> ReLU -> MaxPool2d(2); dx_left / dx_right (both or neither) also receive dx shifted one

@@ -44,10 +44,11 @@ struct Epilogue {
     const float* bias_m;   // per output row, may be null
     int relu;
     int accumulate;        // out += result instead of out = result
-    // Optional per-row statistics of the stored values, added (atomically, in double) over the whole launch:
-    // row_stats[2*row] += sum, row_stats[2*row + 1] += sum of squares.  The caller zeroes the array.  For a
-    // convolution whose rows are output channels these are the sums batch normalisation needs, so the
-    // activation is not read again to get them.  Not available with split-K.
+    // Optional per-row statistics, added (atomically, in double) over the whole launch: row_stats[2*row] += sum,
+    // row_stats[2*row + 1] += sum of squares, both of the accumulator BEFORE bias_m is added, i.e. of the stored
+    // value minus its row's bias (a large bias then costs the sum of squares no digits).  The caller zeroes the
+    // array.  For a convolution whose rows are output channels these are the sums batch normalisation needs, so
+    // the activation is not read again to get them.  Not available with split-K, bias_n or relu.
     double* row_stats = nullptr;
 };
 
@@ -512,8 +513,10 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         // Packed f32x2 arithmetic: one instruction per two values.
-                        float2 lo = __fadd2_rn(make_float2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1])), bm2);
-                        float2 hi = __fadd2_rn(make_float2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3])), bm2);
+                        const float2 rlo = make_float2(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]));
+                        const float2 rhi = make_float2(__uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3]));
+                        float2 lo = __fadd2_rn(rlo, bm2);
+                        float2 hi = __fadd2_rn(rhi, bm2);
                         if (bias_n) {
                             const int col = col0 + 4 * i;
                             if (col + 0 < args.n) lo.x += bias_n[col + 0];
@@ -526,11 +529,11 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                             const int col = col0 + 4 * i;
                             if (fast || col + 3 < args.n) {
                                 // four independent chains each: the adds of one chunk do not wait on one another
-                                q1[i & 3] = __fadd2_rn(q1[i & 3], __fadd2_rn(lo, hi));
-                                q2[i & 3] = __ffma2_rn(lo, lo, q2[i & 3]);
-                                q2[(i + 2) & 3] = __ffma2_rn(hi, hi, q2[(i + 2) & 3]);
+                                q1[i & 3] = __fadd2_rn(q1[i & 3], __fadd2_rn(rlo, rhi));
+                                q2[i & 3] = __ffma2_rn(rlo, rlo, q2[i & 3]);
+                                q2[(i + 2) & 3] = __ffma2_rn(rhi, rhi, q2[(i + 2) & 3]);
                             } else {
-                                const float e[4] = {lo.x, lo.y, hi.x, hi.y};
+                                const float e[4] = {rlo.x, rlo.y, rhi.x, rhi.y};
                                 for (int j = 0; j < 4; ++j)
                                     if (col + j < args.n) { q1[0].x += e[j]; q2[0].x += e[j] * e[j]; }
                             }

@@ -23,7 +23,7 @@
 
 int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
                                 float* running_mean, float* running_var, double momentum, double eps, float* y_pooled, float* save_mean,
-                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums);
+                                float* save_rstd, float* y_left, float* y_right, const double* channel_sums, const float* sums_pivot);
 int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                 const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                                 float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right);
@@ -573,7 +573,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 WB_TRY(wb_bn_relu_pool_fwd_shifted(b, L.conv_out, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
                                                    L.running_mean, L.running_var, 0.1, 1e-5, L.out_act, L.save_mean, L.save_rstd,
                                                    next ? next->x_shift[0] : nullptr, next ? next->x_shift[1] : nullptr,
-                                                   have_sums ? L.stat_sums : nullptr));
+                                                   have_sums ? L.stat_sums : nullptr, have_sums ? t->theta + L.off_b : nullptr));
             }
             act = L.out_act;
         } else if (L.kind == L_LINEAR) {
