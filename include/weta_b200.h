@@ -164,7 +164,8 @@ int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvParams* p, int6
 int wb_cast(WbBackend* b, const WbView* x, int dtype, WbStorage** out);
 int wb_cast_into(WbBackend* b, const WbView* x, int dtype, void* out);
 /* Backend::random (backend.rs:97-105; lib.rs:582-601; crates/weta-core/src/ops.rs:164-189):
- * element i = Distribution::sample(seed, i), bit-identical to the CPU backend for uniform fills. */
+ * element i = Distribution::sample(seed, i).  Uniform fills are bit-identical to the CPU backend; Normal fills
+ * evaluate ln and cos correctly rounded, which matches the CPU backend wherever its libm rounds correctly. */
 int wb_random(WbBackend* b, int64_t len, int dtype, int dist, double pa, double pb, uint64_t seed, WbStorage** out);
 int wb_random_into(WbBackend* b, int64_t len, int dtype, int dist, double pa, double pb, uint64_t seed, void* out);
 
@@ -174,6 +175,12 @@ void wb_pcg_seed(WbPcg* g, uint64_t seed); /* Rng::new */
 uint32_t wb_pcg_next_u32(WbPcg* g);
 uint64_t wb_pcg_next_u64(WbPcg* g);        /* the per-tensor seed */
 uint64_t wb_splitmix64(uint64_t seed, uint64_t i); /* crates/weta-core/src/ops.rs:164-169 */
+/* Host-side evaluation of what the Normal fill computes on the device (same source compiled for the CPU; needs no
+ * GPU): correctly rounded ln(x) for x in (0, 1], cos(t) for t in [0, 8), and element i of a Normal{mean, std} fill as
+ * f64 (Distribution::sample, crates/weta-core/src/ops.rs:182-186). */
+double wb_host_log_rn(double x);
+double wb_host_cos_rn(double t);
+double wb_host_normal_sample(uint64_t seed, uint64_t i, double mean, double std);
 
 /* ==== extension: entry points with no trait method today ===================================== */
 

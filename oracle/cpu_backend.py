@@ -60,9 +60,10 @@ class OracleBackend:
     def set_num_threads(self, n: int) -> None:
         self.lib.wo_set_num_threads(int(n))
 
-    def set_matmul_test_mode(self, tf32_operands: bool = False, f64_accumulate: bool = False) -> None:
-        """f32 matmul with operands truncated to TF32 (how a tensor-core instruction reads them) and / or the sum over k
-        kept in double; both off restores the plain restatement of weta-cpu."""
+    def set_matmul_test_mode(self, tf32_operands: int = 0, f64_accumulate: bool = False) -> None:
+        """f32 matmul with operands reduced to TF32 (0 off, 1 low 13 mantissa bits dropped, 2 rounded to nearest with ties
+        away from zero, 3 rounded to nearest even) and / or the sum over k kept in double; both off restores the plain
+        restatement of weta-cpu."""
         self.lib.wo_set_matmul_test_mode(int(tf32_operands), int(f64_accumulate))
 
     # helpers

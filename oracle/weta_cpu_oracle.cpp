@@ -379,16 +379,20 @@ int reduce_any(int op, const WoView& x, int axis, void* out) {
 // accumulated in T.  The i-k-j loop keeps that order per output while letting the inner loop
 // vectorise; B is packed to unit column stride first when it is not already.
 // Test-only switches for f32 products (default off = the restatement above):
-//   g_tf32_operands   both operands lose their low 13 mantissa bits first, which is how a TF32 tensor-core
-//                     instruction reads an f32 operand; a GPU run in TF32 mode then differs from this oracle by
-//                     accumulation error only, not by operand rounding;
+//   g_tf32_operands   both operands are reduced to TF32 (10 mantissa bits) first, the way a TF32 tensor-core
+//                     instruction reads an f32 operand (1 = low 13 bits dropped, 2 / 3 = rounded to nearest); a GPU
+//                     run in TF32 mode then differs from this oracle by accumulation error only;
 //   g_f64_accumulate  the sum over k is kept in double and rounded to f32 once.
-bool g_tf32_operands = false;
+int g_tf32_operands = 0;  // 0 off, 1 truncate, 2 round to nearest (ties away from zero), 3 round to nearest even
 bool g_f64_accumulate = false;
 
-inline float tf32_trunc(float v) {
+inline float tf32_trunc(float v) {  // f32 -> the 19-bit TF32 value a tensor core would use, by the selected rule
     uint32_t u;
     std::memcpy(&u, &v, 4);
+    if ((u & 0x7F800000u) != 0x7F800000u) {  // finite
+        if (g_tf32_operands == 2) u += 0x00001000u;
+        else if (g_tf32_operands == 3) u += 0x00000FFFu + ((u >> 13) & 1u);
+    }
     u &= 0xFFFFE000u;
     std::memcpy(&v, &u, 4);
     return v;
@@ -584,7 +588,7 @@ int wo_num_threads() { return omp_get_max_threads(); }
 void wo_set_num_threads(int n) { omp_set_num_threads(n); }
 // Test-only: TF32-truncated operands and / or double accumulation for f32 matmul (see matmul_float).
 void wo_set_matmul_test_mode(int tf32_operands, int f64_accumulate) {
-    g_tf32_operands = tf32_operands != 0;
+    g_tf32_operands = tf32_operands;
     g_f64_accumulate = f64_accumulate != 0;
 }
 

@@ -47,12 +47,17 @@ def report():
     return write
 
 
+# How tcgen05.mma kind::tf32 reads an f32 operand (1 = low 13 mantissa bits dropped, 2 / 3 = rounded to nearest); pinned
+# on the GPU by tests/test_gpu_gemm.py::test_how_the_tensor_core_reads_an_f32_operand_as_tf32.
+TF32_OPERAND_RULE = 1
+
+
 @pytest.fixture()
 def tf32_oracle(oracle):
-    """The oracle with f32 matmul operands truncated to TF32 and the sum over k kept in double: what a TF32 tensor-core
-    contraction computes, up to the GPU's own accumulation error.  Restored to the plain restatement afterwards."""
-    oracle.set_matmul_test_mode(True, True)
+    """The oracle with f32 matmul operands reduced to TF32 by that rule and the sum over k kept in double: what a TF32
+    tensor-core contraction computes, up to the GPU's own accumulation error.  Restored to the plain restatement afterwards."""
+    oracle.set_matmul_test_mode(TF32_OPERAND_RULE, True)
     try:
         yield oracle
     finally:
-        oracle.set_matmul_test_mode(False, False)
+        oracle.set_matmul_test_mode(0, False)

@@ -102,3 +102,37 @@ def test_fallback_layouts(gpu):
 def test_large_square(gpu):
     check(gpu, rnd(2048, 2048), rnd(2048, 2048), ident, ident, TF32, "2048^3 tf32")
     check(gpu, rnd(2048, 2048), rnd(2048, 2048), ident, tr, TF32X3, "2048^3 3xtf32 NT")
+
+
+def test_how_the_tensor_core_reads_an_f32_operand_as_tf32(gpu, oracle, report):
+    """TF32 keeps 10 mantissa bits.  Operands whose dropped 13 bits are 0.75, exactly 0.5 and just below 0.5 of a TF32
+    step tell truncation from rounding to nearest: the rule found here is the one the oracle's TF32 test mode
+    (conftest fixture `tf32_oracle`) must apply, or the tight fused-step tolerances would compare different operands."""
+    cases = {"0.75": 1.0 + 2.0 ** -11 + 2.0 ** -12, "0.5": 1.0 + 2.0 ** -11, "0.49": 1.0 + 2.0 ** -11 - 2.0 ** -23,
+             "-0.75": -(1.0 + 2.0 ** -11 + 2.0 ** -12), "odd+0.5": 1.0 + 2.0 ** -10 + 2.0 ** -11}
+    b = np.zeros((32, 128), np.float32)
+    b[0, :] = 1.0
+    seen = {}
+    gpu.set_matmul_mode(TF32)
+    for name, a in cases.items():
+        got = Tensor.from_numpy(np.full((128, 32), a, np.float32), gpu).matmul(Tensor.from_numpy(b, gpu)).numpy()
+        assert np.all(got == got[0, 0])
+        seen[name] = float(got[0, 0])
+    gpu.gemm_check()
+    gpu.set_matmul_mode(TF32X3)
+    step = 2.0 ** -10
+    rule = {(1.0, 1.0, 1.0, -1.0, 1.0 + step): 1,                           # low bits dropped
+            (1.0 + step, 1.0 + step, 1.0, -(1.0 + step), 1.0 + 2 * step): 2,  # nearest, ties away from zero
+            (1.0 + step, 1.0, 1.0, -(1.0 + step), 1.0 + 2 * step): 3}.get(   # nearest, ties to even
+        (seen["0.75"], seen["0.5"], seen["0.49"], seen["-0.75"], seen["odd+0.5"]))
+    report("tf32 operand read", seen=seen, rule=rule)
+    from conftest import TF32_OPERAND_RULE
+    assert rule == TF32_OPERAND_RULE, (seen, rule)
+    # the oracle's test mode applies the same rule
+    oracle.set_matmul_test_mode(TF32_OPERAND_RULE, True)
+    try:
+        for name, a in cases.items():
+            want = Tensor.from_numpy(np.full((4, 32), a, np.float32), oracle).matmul(Tensor.from_numpy(b, oracle)).numpy()
+            assert float(want[0, 0]) == seen[name], name
+    finally:
+        oracle.set_matmul_test_mode(0, False)

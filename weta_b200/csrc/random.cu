@@ -6,9 +6,13 @@
 // hi = 1 the f32 value is that number rounded once, which `__ull2float_rn(k) * 2^-53` also
 // produces (one rounding of a 53-bit integer, then an exact power-of-two scale) without touching
 // the FP64 pipe.  General bounds take `lo + (hi - lo) * unit` in f64 with two roundings (this file
-// is built with -fmad=false).  Normal fills use the device's f64 log / cos, which can differ from
-// glibc's in the last place; after the cast to f32 that shows up in at most a few elements per 2^28.
+// is built with -fmad=false).  Normal fills need ln and cos in f64: the device's versions are good to 1 and
+// 2 ulp, the CPU backend's libm rounds (almost always) correctly, so normal_dd.h evaluates both in
+// double-double and rounds once.  f64 tensors always take that evaluation.  f32 tensors take the device's fast
+// log / cos first and fall back to it only when the fast value, with its error bound, straddles an f32 rounding
+// boundary (about one element in 2^22), which gives the same f32 bits at the fast path's speed.
 #include "common.h"
+#include "normal_dd.h"
 
 namespace {
 
@@ -23,11 +27,27 @@ __device__ __forceinline__ double unit(uint64_t seed, uint64_t i) {
     return __ull2double_rn(splitmix64(seed, i) >> 11) * (1.0 / 9007199254740992.0);
 }
 
+// Distribution::sample in f64 (crates/weta-core/src/ops.rs:176-189), every step rounded as the CPU rounds it.
 __device__ __forceinline__ double sample(int dist, double a, double b, uint64_t seed, uint64_t i) {
     if (dist == WB_UNIFORM) return a + (b - a) * unit(seed, i);
-    double u1 = 1.0 - unit(seed, 2 * i);
-    double u2 = unit(seed, 2 * i + 1);
-    return a + b * sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
+    const double u1 = 1.0 - unit(seed, 2 * i);
+    const double u2 = unit(seed, 2 * i + 1);
+    return wbdd::normal_exact(a, b, u1, u2);
+}
+
+// The same sample rounded to f32.  Fast evaluation first: the device's log and cos are within 1 and 2 ulp, the other
+// steps within half an ulp each, so the product std * sqrt(..) * cos(..) is within 2^-49 of the exact chain's
+// relatively (a generous bound) and the sum within that plus an ulp.  When both ends of that interval round to the
+// same f32 the result is settled; otherwise the exact chain decides.
+__device__ __forceinline__ float sample_normal_f32(double mean, double std, uint64_t seed, uint64_t i) {
+    const double u1 = 1.0 - unit(seed, 2 * i);
+    const double u2 = unit(seed, 2 * i + 1);
+    const double prod = (std * sqrt(-2.0 * log(u1))) * cos(6.283185307179586 * u2);
+    const double v = mean + prod;
+    const double err = fabs(prod) * 3.5527136788005009e-15 /* 2^-48 */ + fabs(v) * 4.4408920985006262e-16 /* 2^-51 */;
+    const float lo = __double2float_rn(v - err), hi = __double2float_rn(v + err);
+    if (lo == hi) return lo;
+    return __double2float_rn(wbdd::normal_exact(mean, std, u1, u2));
 }
 
 constexpr int THREADS = 256;
@@ -50,9 +70,11 @@ template <class T>
 __global__ void __launch_bounds__(THREADS) random_general(T* __restrict__ out, int64_t n, int dist, double a, double b, uint64_t seed) {
     int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
     if (i >= n) return;
-    double v = sample(dist, a, b, seed, static_cast<uint64_t>(i));
-    if constexpr (sizeof(T) == 4) out[i] = __double2float_rn(v);
-    else out[i] = v;
+    if constexpr (sizeof(T) == 4) {
+        out[i] = dist == WB_NORMAL ? sample_normal_f32(a, b, seed, static_cast<uint64_t>(i)) : __double2float_rn(sample(dist, a, b, seed, static_cast<uint64_t>(i)));
+    } else {
+        out[i] = sample(dist, a, b, seed, static_cast<uint64_t>(i));
+    }
 }
 
 }  // namespace
@@ -73,6 +95,16 @@ extern "C" int wb_random_into(WbBackend* b, int64_t len, int dtype, int dist, do
     }
     WB_LAUNCH_OK(b);
     return WB_OK;
+}
+
+// Host evaluation of the functions the Normal fill runs on the device (same source, compiled for the CPU): lets a
+// test without a GPU compare them with arbitrary-precision values.
+extern "C" double wb_host_log_rn(double x) { return wbdd::log_rn(x); }
+extern "C" double wb_host_cos_rn(double t) { return wbdd::cos_rn(t); }
+extern "C" double wb_host_normal_sample(uint64_t seed, uint64_t i, double mean, double std) {
+    const double u1 = 1.0 - static_cast<double>(wb_splitmix64(seed, 2 * i) >> 11) * (1.0 / 9007199254740992.0);
+    const double u2 = static_cast<double>(wb_splitmix64(seed, 2 * i + 1) >> 11) * (1.0 / 9007199254740992.0);
+    return wbdd::normal_exact(mean, std, u1, u2);
 }
 
 extern "C" int wb_random(WbBackend* b, int64_t len, int dtype, int dist, double pa, double pb, uint64_t seed, WbStorage** out) {
