@@ -188,6 +188,9 @@ double wb_host_normal_sample(uint64_t seed, uint64_t i, double mean, double std)
  * runs out (WB_ERR_TIMEOUT), then clears it.  Synchronises the stream.  The reference has no
  * counterpart: cuBLAS reports its own failures through the call's status (lib.rs:387). */
 int wb_gemm_check(WbBackend* b);
+/* Test hook: one thread waits with the GEMM kernels' bounded barrier wait on a barrier nothing arrives at, gives up
+ * after `polls` polls (1..2^20) and raises the same flag; the next wb_gemm_check then returns WB_ERR_TIMEOUT. */
+int wb_gemm_selftest_timeout(WbBackend* b, int polls);
 
 /* ---- fused layer ops ------------------------------------------------------------------------
  * Each stands for the chain of trait calls the reference issues for one layer; pointers are f32

@@ -136,3 +136,24 @@ def test_how_the_tensor_core_reads_an_f32_operand_as_tf32(gpu, oracle, report):
             assert float(want[0, 0]) == seen[name], name
     finally:
         oracle.set_matmul_test_mode(0, False)
+
+
+def test_a_pipeline_wait_that_runs_out_is_reported_and_the_context_survives(gpu):
+    """The tensor-core kernels bound every mbarrier wait; when one runs out they raise a flag that wb_gemm_check turns
+    into WB_ERR_TIMEOUT.  A one-thread kernel makes the same wait run out on a barrier nothing arrives at."""
+    import ctypes
+
+    from weta_b200.backend import BackendError
+
+    lib = gpu.lib
+    lib.wb_gemm_selftest_timeout.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.wb_gemm_selftest_timeout.restype = ctypes.c_int
+    gpu.gemm_check()  # clean before
+    gpu.check(lib.wb_gemm_selftest_timeout(gpu.handle, 4096))
+    with pytest.raises(BackendError) as e:
+        gpu.gemm_check()
+    assert e.value.status == 6  # WB_ERR_TIMEOUT
+    gpu.gemm_check()  # the flag was cleared
+    a = Tensor.from_numpy(np.eye(64, dtype=np.float32), gpu)
+    assert np.array_equal(a.matmul(a).numpy(), np.eye(64, dtype=np.float32))
+    gpu.gemm_check()

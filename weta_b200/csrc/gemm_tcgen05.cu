@@ -408,6 +408,29 @@ int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const 
     return run_tiles(be, st, args, blocks * tc::BM, m, 1, BN, pair, false, false, ep, 0, /*two_blocks=*/pair_mode(blocks * tc::BM, BN));
 }
 
+// One thread waits, with the GEMM kernels' own bounded mbar_wait, on a shared-memory barrier that nothing ever
+// arrives at (no copy or MMA is in flight), gives up after `polls` polls and raises the error flag the way the
+// GEMM kernels do.
+__global__ void mbar_timeout_selftest_kernel(int* error_flag, uint32_t polls) {
+    __shared__ alignas(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!tc::mbar_wait(&bar, 0, polls)) atomicExch(error_flag, 1);
+    }
+}
+
+// Test hook of the bounded pipeline waits: after this call wb_gemm_check reports WB_ERR_TIMEOUT (and clears the flag),
+// exactly as it would after a tensor-core kernel had given up on a barrier; the context stays usable.
+extern "C" int wb_gemm_selftest_timeout(WbBackend* b, int polls) {
+    WB_REQUIRE(b && polls > 0 && polls <= (1 << 20), WB_ERR_INVALID, "wb_gemm_selftest_timeout: polls must be 1..2^20");
+    GemmState* st = nullptr;
+    WB_TRY(get_state(b, &st));
+    mbar_timeout_selftest_kernel<<<1, 32, 0, b->stream>>>(st->error_flag, static_cast<uint32_t>(polls));
+    WB_LAUNCH_OK(b);
+    return WB_OK;
+}
+
 // Reads the device-side error flag the GEMM kernels raise when a bounded wait runs out.
 // Synchronises the stream; meant for tests and for wb_synchronize-style checkpoints.
 extern "C" int wb_gemm_check(WbBackend* b) {
