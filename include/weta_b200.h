@@ -192,6 +192,20 @@ int wb_gemm_check(WbBackend* b);
  * after `polls` polls (1..2^20) and raises the same flag; the next wb_gemm_check then returns WB_ERR_TIMEOUT. */
 int wb_gemm_selftest_timeout(WbBackend* b, int polls);
 
+/* A chain of unary / binary trait calls over one index space as ONE launch (no counterpart in the reference, which
+ * launches each op by itself: crates/weta-cuda/src/lib.rs:482-521).  `inputs`: up to 8 f32 views of n elements each
+ * (strided or broadcast; they may differ in shape, the linear row-major index is what they share).  `prog`: up to
+ * 48 instructions, instruction k producing value k: kind 0 loads inputs[a]; kind 1 applies WbUnaryOp `op` with (p1, p2)
+ * to value a; kind 2 applies WbBinaryOp `op` to values a and b (a, b < k).  Values out_regs[0..n_outputs) are stored
+ * contiguously to outs[..] (up to 4).  An output may be the storage of an input read through a contiguous view.
+ * Results are bit-identical to issuing the same ops one launch at a time. */
+#define WB_EWF_MAX_INPUTS 8
+#define WB_EWF_MAX_INSTRS 48
+#define WB_EWF_MAX_OUTPUTS 4
+typedef struct WbEwInstr { int32_t kind, op, a, b; double p1, p2; } WbEwInstr;
+int wb_ew_fused(WbBackend* b, const WbView* inputs, int n_inputs, const WbEwInstr* prog, int n_instr, const int32_t* out_regs,
+                void* const* outs, int n_outputs, int64_t n);
+
 /* ---- fused layer ops ------------------------------------------------------------------------
  * Each stands for the chain of trait calls the reference issues for one layer; pointers are f32
  * device memory, tensors are contiguous NCHW / row-major. */

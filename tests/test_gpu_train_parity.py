@@ -107,3 +107,15 @@ def test_cnn_three_adam_steps(oracle, gpu):
         # so it inherits that bound scaled by the momentum; the variance does not depend on the bias.
         tol = (0.0, 3 * 1e-3) if n.endswith("running_mean") else (1e-4, 1e-5)
         assert allclose(bg.numpy(), bc.numpy(), *tol), n
+
+
+def test_gradcheck_on_the_gpu(gpu):  # cuda_parity.rs:214-228
+    """f64 central differences through conv2d -> relu -> max_pool2d -> softmax on the CUDA backend (every primitive in
+    f64: im2col, the CUDA-core matmul, reductions, element-wise ops), eps 1e-5, tolerance 1e-6 like the reference."""
+    from oracle.mirror.gradcheck import gradcheck
+
+    manual_seed(5)
+    leaf = lambda s: Var(Tensor.randn(s, DType.F64, gpu), requires_grad=True)
+    x, w, b = leaf([2, 2, 5, 5]), leaf([3, 2, 3, 3]), leaf([3])
+    f = lambda t: nn.max_pool2d(nn.conv2d(t[0], t[1], t[2], stride=(1, 1), padding=(1, 1)).relu(), 2, 2).softmax(1)
+    assert gradcheck(f, [x, w, b]) is None

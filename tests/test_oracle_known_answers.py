@@ -102,3 +102,18 @@ def test_integer_semantics(oracle):  # crates/weta-cpu/src/lib.rs:190-241, :552-
     assert np.isnan(nanmax).all()  # NaN anywhere wins a reduction (dtype.rs:136-149)
     ties = T(oracle, [[2.0, 5.0, 5.0, 1.0]]).argmax(1).numpy().tolist()
     assert ties == [1]
+
+
+def test_gradcheck_of_a_conv_relu_pool_softmax_chain(oracle):
+    """crates/weta-autograd/tests/gradcheck.rs style: f64 central differences, eps 1e-5, tolerance 1e-6, on the chain the
+    reference also checks on its GPU backend (crates/weta/tests/cuda_parity.rs:214-228); a wrong backward rule is caught."""
+    from oracle.mirror.gradcheck import gradcheck
+    from weta_b200.core import manual_seed
+
+    manual_seed(5)
+    leaf = lambda s: Var(Tensor.randn(s, DType.F64, oracle), requires_grad=True)
+    x, w, b = leaf([2, 2, 5, 5]), leaf([3, 2, 3, 3]), leaf([3])
+    f = lambda t: nn.max_pool2d(nn.conv2d(t[0], t[1], t[2], stride=(1, 1), padding=(1, 1)).relu(), 2, 2).softmax(1)
+    assert gradcheck(f, [x, w, b]) is None
+    wrong = lambda t: t[0].mul(t[0]).detach().mul(t[0])  # d/dx (x^2 x) reported as x^2: must be flagged
+    assert gradcheck(wrong, [leaf([3])]) is not None
