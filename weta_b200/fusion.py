@@ -187,11 +187,26 @@ class FusingBackend:
             n_instr = len(order) + len(inputs)
             if n_instr <= MAX_INSTRS and len(inputs) <= MAX_INPUTS and 1 + len(extra) <= MAX_OUTPUTS:
                 break
-            # Too large for one launch: store a sub-tree of its own first (it then enters as an input).  Prefer a node whose
-            # value is wanted anyway; else the child of the root with the largest sub-tree.
-            victim = extra[0] if extra else max((s for s, _ in root.inputs if isinstance(s, _Node) and s.concrete is None),
-                                                 key=lambda s: len(self._tree(s)), default=None)
-            if victim is None:  # a single op with too many operands cannot happen (at most two); guard anyway
+            # Too large for one launch: store a sub-tree of its own first (it then enters as an input).  Too many values
+            # wanted outside: store one of those.  Too many ops or operands: store the largest sub-tree that fits by
+            # itself (upper bounds: shared nodes are counted once per use), so a long chain splits into few launches.
+            if 1 + len(extra) > MAX_OUTPUTS:
+                victim = extra[0]
+            else:
+                size = {}
+                victim, best = None, -1
+                for nd in order:
+                    ops, leaves = 1, 0
+                    for src, _ in nd.inputs:
+                        if isinstance(src, _Node) and src.concrete is None:
+                            ops += size[id(src)][0]
+                            leaves += size[id(src)][1]
+                        else:
+                            leaves += 1
+                    size[id(nd)] = (ops, leaves)
+                    if nd is not root and ops + leaves <= MAX_INSTRS and leaves <= MAX_INPUTS and ops > best:
+                        victim, best = nd, ops
+            if victim is None:  # cannot happen: a single op has at most two operands
                 raise RuntimeError("element-wise program does not fit and cannot be split")
             self._materialise(victim)
         # emit: loads first, then the ops in dependency order
