@@ -72,6 +72,7 @@ extern "C" int wb_backend_destroy(WbBackend* b) {
     wb_gemm_state_destroy(b);
     for (auto& kv : b->free_blocks) cudaFree(kv.second);
     if (b->scratch) cudaFree(b->scratch);
+    if (b->narrow_counters) cudaFree(b->narrow_counters);
     if (b->own_stream) cudaStreamDestroy(b->stream);
     delete b;
     return WB_OK;

@@ -87,6 +87,8 @@ struct WbBackend {
     size_t scratch_bytes = 0;
     // lazily created resources of the tensor-core GEMM path
     void* gemm_state = nullptr;
+    // block counters of the narrow linear layer's weight gradient (narrow_linear.cu), zero between launches
+    void* narrow_counters = nullptr;
 };
 
 inline size_t wb_dtype_size(int dt) { return dt == WB_F32 ? 4 : 8; }

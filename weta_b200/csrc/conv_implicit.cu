@@ -29,17 +29,21 @@ __global__ void __launch_bounds__(256) shift_copies_kernel(const float* __restri
 // kind 0: dst[o][tap][c] = src[o][c][tap]        (forward operand)
 // kind 1: dst[c][tap][o] = src[o][c][8 - tap]    (input-gradient operand: transposed channels, flipped taps)
 // kind 2: dst[o][c][tap] = src[tap][c][o]        (weight gradient back to the parameter's element order)
-__global__ void __launch_bounds__(256) weight_reorder_kernel(const float* __restrict__ src, float* __restrict__ dst, int o_n, int c_n, int kind) {
+// kind 3: kinds 0 and 1 in one launch, into dst and dst2 (both operands of a step from the same parameters)
+__global__ void __launch_bounds__(256) weight_reorder_kernel(const float* __restrict__ src, float* __restrict__ dst, float* __restrict__ dst2,
+                                                             int o_n, int c_n, int kind) {
     const int64_t total = static_cast<int64_t>(o_n) * c_n * 9;
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
-    if (kind == 0) {
+    if (kind == 0 || kind == 3) {
         const int c = static_cast<int>(i % c_n), tap = static_cast<int>(i / c_n % 9), o = static_cast<int>(i / (9 * c_n));
         dst[i] = src[(static_cast<int64_t>(o) * c_n + c) * 9 + tap];
-    } else if (kind == 1) {
+    }
+    if (kind == 1 || kind == 3) {
         const int o = static_cast<int>(i % o_n), tap = static_cast<int>(i / o_n % 9), c = static_cast<int>(i / (9 * o_n));
-        dst[i] = src[(static_cast<int64_t>(o) * c_n + c) * 9 + (8 - tap)];
-    } else {
+        (kind == 3 ? dst2 : dst)[i] = src[(static_cast<int64_t>(o) * c_n + c) * 9 + (8 - tap)];
+    }
+    if (kind == 2) {
         const int tap = static_cast<int>(i % 9), c = static_cast<int>(i / 9 % c_n), o = static_cast<int>(i / (9 * c_n));
         dst[i] = src[(static_cast<int64_t>(tap) * c_n + c) * o_n + o];
     }
@@ -59,10 +63,10 @@ int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, fl
     return WB_OK;
 }
 
-int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n) {
+int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n, float* dst2) {
     const int64_t total = static_cast<int64_t>(o_n) * c_n * 9;
     if (total == 0) return WB_OK;
-    weight_reorder_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, b->stream>>>(src, dst, o_n, c_n, kind);
+    weight_reorder_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, b->stream>>>(src, dst, dst2, o_n, c_n, kind);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

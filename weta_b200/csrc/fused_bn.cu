@@ -7,6 +7,8 @@
 #include <algorithm>
 #include <cmath>
 
+#include <cstdlib>
+
 #include "common.h"
 
 namespace {
@@ -100,8 +102,8 @@ __global__ void bn_finalize_kernel(const double* __restrict__ part, int splits, 
 // the sum of squares of (x - pivot[c]) (pivot null = 0; for a convolution the pivot is its bias, so the sums are those
 // of the raw accumulator).  variance = E[d^2] - E[d]^2 loses digits when |E[d]| >> the standard deviation: the
 // producer's per-tile partial sums are f32, so E[d^2] carries about 1e-7 of relative error and a channel whose
-// variance is below 1e-3 of E[d^2] would keep fewer than four digits of it.  Such channels are left to
-// bn_stats_redo_kernel, which re-reads x; both kernels evaluate the same predicate on the same sums.
+// variance is below 1e-3 of E[d^2] would keep fewer than four digits of it.  Such channels are recomputed from x
+// by the same kernel that finalises the others (bn_stats_from_sums_kernel).
 __device__ __forceinline__ bool sums_cancel(double e1, double e2) { return !(e2 - e1 * e1 > 1e-3 * e2) && e2 > 0.0; }
 
 __device__ __forceinline__ void bn_store_stats(int c, double mean_d, double var_d, int64_t count, float eps, float momentum, float one_minus_momentum,
@@ -119,21 +121,10 @@ __device__ __forceinline__ void bn_store_stats(int c, double mean_d, double var_
     }
 }
 
-__global__ void bn_finalize_sums_kernel(const double* __restrict__ sums, const float* __restrict__ pivot, int c_total, int64_t count, float eps,
-                                        float momentum, float one_minus_momentum, float* __restrict__ mean, float* __restrict__ rstd,
-                                        float* __restrict__ running_mean, float* __restrict__ running_var) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= c_total) return;
-    const double e1 = sums[2 * c] / static_cast<double>(count), e2 = sums[2 * c + 1] / static_cast<double>(count);
-    if (sums_cancel(e1, e2)) return;  // bn_stats_redo_kernel writes this channel
-    bn_store_stats(c, (pivot ? static_cast<double>(pivot[c]) : 0.0) + e1, e2 - e1 * e1, count, eps, momentum, one_minus_momentum, mean, rstd,
-                   running_mean, running_var);
-}
-
-// One block per channel; returns at once unless the channel's sums cancel (see above).  Then the block reads the
-// channel's n_img planes again and sums (x - m0), (x - m0)^2 about m0 = pivot + E[d], which is already within
-// rounding of the mean, so nothing cancels.
-__global__ void __launch_bounds__(THREADS) bn_stats_redo_kernel(const float* __restrict__ x, const double* __restrict__ sums,
+// One block per channel.  Normally thread 0 turns the channel's sums into mean / rstd / running statistics and the
+// block is done; when the sums cancel (see above) the block reads the channel's n_img planes again and sums
+// (x - m0), (x - m0)^2 about m0 = pivot + E[d], which is already within rounding of the mean, so nothing cancels.
+__global__ void __launch_bounds__(THREADS) bn_stats_from_sums_kernel(const float* __restrict__ x, const double* __restrict__ sums,
                                                                  const float* __restrict__ pivot, int64_t n_img, int c_total, int64_t hw, float eps,
                                                                  float momentum, float one_minus_momentum, float* __restrict__ mean,
                                                                  float* __restrict__ rstd, float* __restrict__ running_mean,
@@ -141,7 +132,12 @@ __global__ void __launch_bounds__(THREADS) bn_stats_redo_kernel(const float* __r
     const int c = blockIdx.x;
     const int64_t count = n_img * hw;
     const double e1 = sums[2 * c] / static_cast<double>(count), e2 = sums[2 * c + 1] / static_cast<double>(count);
-    if (!sums_cancel(e1, e2)) return;
+    if (!sums_cancel(e1, e2)) {
+        if (threadIdx.x == 0)
+            bn_store_stats(c, (pivot ? static_cast<double>(pivot[c]) : 0.0) + e1, e2 - e1 * e1, count, eps, momentum, one_minus_momentum, mean, rstd,
+                           running_mean, running_var);
+        return;
+    }
     const float m0 = static_cast<float>((pivot ? static_cast<double>(pivot[c]) : 0.0) + e1);
     double s1 = 0.0, s2 = 0.0;
     float a1 = 0.f, a2 = 0.f;
@@ -494,6 +490,67 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
     if (threadIdx.x == 0 && bias_part) bias_part[static_cast<int64_t>(c) * gridDim.y + blockIdx.y] = rs[0];
 }
 
+// The backward sums of BatchNorm -> ReLU -> MaxPool(2) can be taken from the POOLED tensors alone: a window passes
+// gradient only to the positions equal to its maximum, all of which hold the same value, so per window
+//     sum(dy)        = g                     if y > 0 else 0        (g: the window's upstream gradient, y: its pooled output)
+//     sum(dy * xhat) = g * (y - beta)/gamma  if y > 0 else 0        (y = xhat_w * gamma + beta at the winner)
+// which reads a quarter of the activation instead of all of it.  Recovering xhat from y costs |y| * 2^-23 / |gamma| of
+// accuracy, so a channel takes this path only when |gamma| >= |beta| / 64 and |gamma| >= 1e-6 (always, for freshly
+// initialised and normally trained layers); the other channels are summed from x by the kernel below.
+__device__ __forceinline__ bool pooled_sums_ok(float g, float b) { return fabsf(g) * 64.f >= fabsf(b) && fabsf(g) >= 1e-6f; }
+
+// Same (channel, slab) items and the same layout of `part` as bn_relu_pool_bwd_pair_kernel<false, ...>.
+__global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(const float* __restrict__ yp, const float* __restrict__ dyp,
+                                                                                const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                                int64_t n_img, int c_total, int pooled, double* __restrict__ part,
+                                                                                int slabs) {
+    const int64_t per = (n_img + slabs - 1) / slabs;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t q = static_cast<uint32_t>(pooled >> 2);  // pooled % 4 == 0 (checked by the host)
+    __shared__ double red[2][THREADS / 32];
+    for (int item = blockIdx.x; item < c_total * slabs; item += gridDim.x) {
+        const int c = item / slabs, sl = item - c * slabs;
+        const float g = __ldg(gamma + c), b = __ldg(beta + c);
+        if (!pooled_sums_ok(g, b)) continue;  // block-uniform
+        const int64_t n0 = min(n_img, static_cast<int64_t>(sl) * per), n1 = min(n_img, n0 + per);
+        const uint32_t items = static_cast<uint32_t>(n1 - n0) * q;
+        const int64_t stride = static_cast<int64_t>(c_total) * pooled, base = (n0 * c_total + c) * pooled;
+        double s1 = 0.0, s2 = 0.0;
+        float a1 = 0.f, a2 = 0.f;
+        int flushed = 0;
+        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
+            const uint32_t n = j / q, i = j - n * q;
+            const int64_t o = base + n * stride + 4 * static_cast<int64_t>(i);
+            const float4 y = *reinterpret_cast<const float4*>(yp + o);
+            const float4 u = *reinterpret_cast<const float4*>(dyp + o);
+            const float ys[4] = {y.x, y.y, y.z, y.w}, us[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                if (ys[k] > 0.f) {
+                    a1 += us[k];
+                    a2 += us[k] * ((ys[k] - b) / g);
+                }
+            if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+        }
+        s1 += a1;
+        s2 += a2;
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) {
+            s1 += __shfl_down_sync(0xffffffffu, s1, sh);
+            s2 += __shfl_down_sync(0xffffffffu, s2, sh);
+        }
+        if (lane == 0) { red[0][warp] = s1; red[1][warp] = s2; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t1 = 0.0, t2 = 0.0;
+            for (int w = 0; w < THREADS / 32; ++w) { t1 += red[0][w]; t2 += red[1][w]; }
+            part[static_cast<int64_t>(item) * 2] = t1;
+            part[static_cast<int64_t>(item) * 2 + 1] = t2;
+        }
+        __syncthreads();
+    }
+}
+
 // Width-multiple-of-4 variants: one thread handles two neighbouring pooled elements, i.e. a 2x4 patch
 // of x, with 128-bit loads and stores; same arithmetic as the kernels above.
 // SHIFT (with WRITE_DX): also writes dx shifted one column right (dx_left[y][x] = dx[y][x-1]) and left
@@ -507,7 +564,7 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
                                                                             const float* __restrict__ beta, const float* __restrict__ dgamma,
                                                                             const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
                                                                             int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
-                                                                            FastDiv div_owp, int slabs) {
+                                                                            FastDiv div_owp, int slabs, int skip_pooled_ok) {
     // Work items are (channel, slab of images) pairs, many more than blocks, walked round-robin: every SM stays
     // equally loaded whatever the channel count.  The two windows a thread owns are computed side by side in
     // packed f32x2 arithmetic (.x = left window, .y = right window).
@@ -520,6 +577,8 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
     for (int item = blockIdx.x; item < c_total * slabs; item += gridDim.x) {
         const int c = item / slabs, sl = item - c * slabs;
         const float m = __ldg(mean + c), r = __ldg(rstd + c), g = __ldg(gamma + c), b = __ldg(beta + c);
+        // sums pass only: this channel's sums were already taken from the pooled tensors (block-uniform)
+        if (!WRITE_DX && skip_pooled_ok && pooled_sums_ok(g, b)) continue;
         float k1 = 0.f, k2 = 0.f, gr = 0.f;
         if (WRITE_DX) { k1 = __ldg(dbeta + c) * inv_count; k2 = __ldg(dgamma + c) * inv_count; gr = g * r; }
         const float2 negm2 = make_float2(-m, -m), r2 = make_float2(r, r), g2 = make_float2(g, g), b2 = make_float2(b, b);
@@ -800,12 +859,8 @@ int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t
     if (channel_sums) {
         // (sum, sum of squares) per channel already accumulated by the kernel that wrote x
         WB_REQUIRE(n * h * w > 0, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: empty input");
-        bn_finalize_sums_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(
-            channel_sums, sums_pivot, static_cast<int>(c), n * h * w, static_cast<float>(eps), static_cast<float>(momentum),
-            static_cast<float>(1.0 - momentum), save_mean, save_rstd, running_mean, running_var);
-        WB_LAUNCH_OK(b);
-        // Channels whose sums cancel are recomputed from x (every other block of this launch returns at once).
-        bn_stats_redo_kernel<<<static_cast<unsigned>(c), THREADS, 0, b->stream>>>(x, channel_sums, sums_pivot, n, static_cast<int>(c), h * w,
+        // One block per channel: statistics straight from the sums, or recomputed from x where the sums cancel.
+        bn_stats_from_sums_kernel<<<static_cast<unsigned>(c), THREADS, 0, b->stream>>>(x, channel_sums, sums_pivot, n, static_cast<int>(c), h * w,
                                                                                   static_cast<float>(eps), static_cast<float>(momentum),
                                                                                   static_cast<float>(1.0 - momentum), save_mean, save_rstd, running_mean,
                                                                                   running_var);
@@ -852,7 +907,7 @@ extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int6
 // column right / left, zeros shifted in (needs w / 4 in {1, 2, 4, ..., 32} and 16-byte aligned buffers).
 int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                 const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
-                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right) {
+                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right, const float* y_pooled) {
     WB_REQUIRE(b && x && dy_pooled && dx && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
     WB_REQUIRE((dx_left == nullptr) == (dx_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_bwd: give both shifted outputs or neither");
@@ -886,10 +941,21 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     dim3 grid(static_cast<unsigned>(c), splits);
     const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
     const FastDiv div_pairs(static_cast<uint32_t>(std::max<int64_t>(1, (h / 2) * (w / 4)))), div_owp(static_cast<uint32_t>(std::max<int64_t>(1, w / 4)));
+    // y_pooled (the forward's output, when the caller still has it): channels with a usable gamma take their sums from
+    // the pooled tensors, a quarter of the bytes; the pass over x then skips those channels (all of them, normally).
+    const int64_t pooled = (h / 2) * (w / 2);
+    static const bool sums_from_x = [] { const char* e = std::getenv("WETA_B200_BN_SUMS_FROM_X"); return e && e[0] == '1'; }();  // diagnostic switch
+    const bool from_pooled = !sums_from_x && pairs && y_pooled && pooled % 4 == 0 && pooled < (int64_t(1) << 30) &&
+                             ((reinterpret_cast<uintptr_t>(y_pooled) | reinterpret_cast<uintptr_t>(dy_pooled)) & 15) == 0;
+    if (from_pooled) {
+        bn_relu_pool_bwd_sums_pooled_kernel<<<flat_blocks, THREADS, 0, b->stream>>>(y_pooled, dy_pooled, gamma, beta, n, static_cast<int>(c),
+                                                                                   static_cast<int>(pooled), part, splits);
+        WB_LAUNCH_OK(b);
+    }
     if (pairs)
         bn_relu_pool_bwd_pair_kernel<false, false><<<flat_blocks, THREADS, 0, b->stream>>>(
             nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr, nullptr, n, static_cast<int>(c), static_cast<int>(h),
-            static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits);
+            static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits, from_pooled ? 1 : 0);
     else
         bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
                                                                       static_cast<int>(h), static_cast<int>(w), part);
@@ -899,11 +965,11 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     if (pairs && dx_left)
         bn_relu_pool_bwd_pair_kernel<true, true><<<flat_blocks, THREADS, 0, b->stream>>>(
             dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
-            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits);
+            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits, 0);
     else if (pairs)
         bn_relu_pool_bwd_pair_kernel<true, false><<<flat_blocks, THREADS, 0, b->stream>>>(
             dx, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
-            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits);
+            static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits, 0);
     else
         bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
                                                                    static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
@@ -920,6 +986,6 @@ extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy
                                    const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                                    float* dgamma, float* dbeta, float* dbias_conv) {
     return wb_bn_relu_pool_bwd_shifted(b, x, dy_pooled, n, c, h, w, gamma, beta, save_mean, save_rstd, dx, dgamma, dbeta, dbias_conv, nullptr,
-                                       nullptr);
+                                       nullptr, nullptr);
 }
 

@@ -26,7 +26,7 @@ int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const 
 struct WbConv3 { int64_t n, c, h, w, o; };
 bool wb_conv3_eligible(const WbConv3& g);
 int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, float* left, float* right);
-int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n);
+int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n, float* dst2 = nullptr);
 int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y,
                  double* channel_sums);
 int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float* const x3[3], float* dwr, float* dweight);
@@ -37,3 +37,9 @@ int wb_gemm_dispatch(WbBackend* be, int mode, WbGemmOperand A, WbGemmOperand B, 
                      int64_t span_batch, bool* used_tc);
 
 int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);
+
+// Linear layers with at most 16 outputs on CUDA cores, in the arithmetic of `mode` (narrow_linear.cu).
+bool wb_narrow_linear_ok(int64_t n, int64_t in, int64_t out, const float* x, const float* w);
+int wb_narrow_linear_fwd(WbBackend* b, int mode, const float* x, const float* w, const float* bias, int n, int in, int out, int relu, float* y);
+int wb_narrow_linear_wgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* x, int n, int in, int out, float* dw);
+int wb_narrow_linear_dgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* w, int n, int in, int out, float* dx);

@@ -26,7 +26,7 @@ int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t
                                 float* save_rstd, float* y_left, float* y_right, const double* channel_sums, const float* sums_pivot);
 int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                 const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
-                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right);
+                                float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right, const float* y_pooled);
 int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labels, int64_t rows, int64_t cols, float* probs, float* dlogits,
                           int64_t dz_pitch, float* row_loss, float* mean_loss, double upstream);
 
@@ -536,7 +536,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                     OpTimer tm(t, i, "conv_shift_x");
                     WB_TRY(wb_conv3_shift_copies(b, act, B * L.cin * L.h, L.w, L.x_shift[0], L.x_shift[1]));
                 }
-                WB_TRY(wb_conv3_weight_reorder(b, 0, t->theta + L.off_w, L.w_fwd, L.cout, L.cin));
+                // the forward operand and, when this block has an input gradient, its operand too: the parameters do not
+                // change between this block's forward and its backward
+                WB_TRY(wb_conv3_weight_reorder(b, L.w_dgrad ? 3 : 0, t->theta + L.off_w, L.w_fwd, L.cout, L.cin, L.w_dgrad));
                 const float* x3[3] = {L.x_shift[0], act, L.x_shift[1]};
                 WB_CHECK_CUDA(cudaMemsetAsync(L.stat_sums, 0, 2 * sizeof(double) * L.cout, b->stream));
                 { OpTimer tm(t, i, "conv_fwd_gemm"); WB_TRY(wb_conv3_fwd(b, geo, x3, L.w_fwd, t->theta + L.off_b, L.conv_out, L.stat_sums)); }
@@ -578,6 +580,13 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             act = L.out_act;
         } else if (L.kind == L_LINEAR) {
             // F::linear (functional.rs:54-60): x W^T + b, ReLU folded into the epilogue
+            if (wb_narrow_linear_ok(B, L.in, L.out, act, t->theta + L.off_w)) {  // e.g. the logits layer
+                OpTimer tm(t, i, "linear_fwd_gemm");
+                WB_TRY(wb_narrow_linear_fwd(b, t->matmul_mode, act, t->theta + L.off_w, t->theta + L.off_b, static_cast<int>(B), L.in, L.out, L.relu,
+                                            L.out_act));
+                act = L.out_act;
+                continue;
+            }
             WbGemmOperand Ax{act, B, L.in, L.in, 0, false};
             WbGemmOperand Bw{t->theta + L.off_w, L.out, L.in, L.in, 0, false};
             tc::Epilogue ep{L.out_act, L.out, 0, t->theta + L.off_b, nullptr, L.relu, 0};
@@ -603,6 +612,18 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             const int64_t gld = (i == nl - 1) ? t->dl_pitch : L.out;  // row pitch of dZ (the logits' gradient is padded)
             if (L.relu && !L.relu_bwd_done) WB_TRY(relu_bwd_inplace(t, gz, L.out_act, B * L.out));
             // MatmulBw (ops.rs:821-827): dW = dZ^T X, db = sum over the batch, dX = dZ W
+            if (wb_narrow_linear_ok(B, L.in, L.out, in_act, t->theta + L.off_w)) {
+                { OpTimer tm(t, i, "linear_wgrad_gemm"); WB_TRY(wb_narrow_linear_wgrad(b, t->matmul_mode, gz, gld, in_act, static_cast<int>(B), L.in, L.out, t->grad + L.off_w)); }
+                { OpTimer tm(t, i, "linear_bias_grad"); WB_TRY(column_sum(t, gz, B, L.out, gld, t->grad + L.off_b)); }
+                if (need_dx) {
+                    float* dx = t->gbuf[pp];
+                    pp ^= 1;
+                    { OpTimer tm(t, i, "linear_dgrad_gemm"); WB_TRY(wb_narrow_linear_dgrad(b, t->matmul_mode, gz, gld, t->theta + L.off_w, static_cast<int>(B), L.in, L.out, dx)); }
+                    g = dx;
+                }
+                if (t->cb && L.range_len > 0) t->cb(t->cb_user, t->grad + L.range_begin, L.range_len);
+                continue;
+            }
             WbGemmOperand Az{gz, L.out, B, gld, 0, true};
             WbGemmOperand Bx{in_act, L.in, B, L.in, 0, true};
             tc::Epilogue epw{t->grad + L.off_w, L.in, 0, nullptr, nullptr, 0, 0};
@@ -638,7 +659,7 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 const bool fuse = L.implicit && need_dx && L.dy_shift_fused;
                 WB_TRY(wb_bn_relu_pool_bwd_shifted(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
                                                    L.save_mean, L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta,
-                                                   t->grad + L.off_b, fuse ? t->dy_shift[0] : nullptr, fuse ? t->dy_shift[1] : nullptr));
+                                                   t->grad + L.off_b, fuse ? t->dy_shift[0] : nullptr, fuse ? t->dy_shift[1] : nullptr, L.out_act));
             }
             if (L.implicit) {
                 const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
@@ -649,7 +670,6 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                         OpTimer tm(t, i, "conv_shift_dy");
                         WB_TRY(wb_conv3_shift_copies(b, dconv, B * L.cout * L.h, L.w, t->dy_shift[0], t->dy_shift[1]));
                     }
-                    WB_TRY(wb_conv3_weight_reorder(b, 1, t->theta + L.off_w, L.w_dgrad, L.cout, L.cin));
                     float* dx = t->gbuf[pp];
                     pp ^= 1;
                     const float* d3[3] = {t->dy_shift[0], dconv, t->dy_shift[1]};
