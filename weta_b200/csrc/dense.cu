@@ -55,8 +55,6 @@ extern "C" int wb_linear_fwd(WbBackend* b, const float* x, const float* weight, 
     WB_REQUIRE(b && x && weight && y && n > 0 && in > 0 && out > 0, WB_ERR_INVALID, "wb_linear_fwd: bad arguments");
     WB_REQUIRE(n < (1 << 30) && in < (1 << 30) && out < (1 << 30), WB_ERR_INVALID, "wb_linear_fwd: dimension too large");
     WbProfileScope ps(b, "linear_fwd");
-    if (wb_narrow_linear_ok(n, in, out, x, weight))
-        return wb_narrow_linear_fwd(b, b->matmul_mode, x, weight, bias, static_cast<int>(n), static_cast<int>(in), static_cast<int>(out), relu, y);
     WbGemmOperand Ax{x, n, in, in, 0, false};
     WbGemmOperand Bw{weight, out, in, in, 0, false};
     tc::Epilogue ep{y, out, 0, bias, nullptr, relu ? 1 : 0, 0};
@@ -69,9 +67,15 @@ extern "C" int wb_linear_bwd(WbBackend* b, const float* x, const float* weight, 
     WB_REQUIRE(n < (1 << 30) && in < (1 << 30) && out < (1 << 30), WB_ERR_INVALID, "wb_linear_bwd: dimension too large");
     WbProfileScope ps(b, "linear_bwd");
     const bool narrow = wb_narrow_linear_ok(n, in, out, x, weight);
-    if (narrow && dweight) WB_TRY(wb_narrow_linear_wgrad(b, b->matmul_mode, dy, out, x, static_cast<int>(n), static_cast<int>(in), static_cast<int>(out), dweight));
-    if (narrow && dx) WB_TRY(wb_narrow_linear_dgrad(b, b->matmul_mode, dy, out, weight, static_cast<int>(n), static_cast<int>(in), static_cast<int>(out), dx));
-    if (narrow) { dweight = nullptr; dx = nullptr; }
+    // at most 16 outputs: CUDA-core kernels (narrow_linear.cu), the weight gradient only for small batches
+    if (narrow && dweight && n <= 1024) {
+        WB_TRY(wb_narrow_linear_wgrad(b, b->matmul_mode, dy, out, x, static_cast<int>(n), static_cast<int>(in), static_cast<int>(out), dweight));
+        dweight = nullptr;
+    }
+    if (narrow && dx) {
+        WB_TRY(wb_narrow_linear_dgrad(b, b->matmul_mode, dy, out, weight, static_cast<int>(n), static_cast<int>(in), static_cast<int>(out), dx));
+        dx = nullptr;
+    }
     if (dweight) {  // dW[out, in] = dY^T X
         WbGemmOperand Az{dy, out, n, out, 0, true};
         WbGemmOperand Bx{x, in, n, in, 0, true};

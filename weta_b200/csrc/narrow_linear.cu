@@ -3,7 +3,8 @@
 // F::linear and MatmulBw (crates/weta-nn/src/functional.rs:54-60, crates/weta-autograd/src/ops.rs:821-827) for
 // out <= 16.  The tensor-core kernel needs ~10-20 us for such a product whatever its size (a 128-wide tile, a
 // pipeline of K blocks walked by four CTAs, a split-K pass): at small batches the three products of a 1024 -> 10
-// layer cost more than its 20 MFLOP deserve.  Here each is one short launch:
+// layer cost more than its 20 MFLOP deserve.  Here each is one short launch (the callers use the two gradient kernels;
+// the forward kernel measured slower than the tensor-core path and is kept for layers TMA cannot read):
 //   forward   y[b][s]  = sum_k x[b][k] w[s][k] (+ bias[s])   one warp per sample, lanes stride over k
 //   dweight   dw[s][j] = sum_b dy[b][s] x[b][j]             slabs of samples in parallel, the last block adds the
 //                                                           slabs in ascending order (deterministic, one launch)
@@ -27,12 +28,22 @@ __global__ void __launch_bounds__(256) narrow_fwd_kernel(float* __restrict__ y, 
     float acc[S];
 #pragma unroll
     for (int s = 0; s < S; ++s) acc[s] = 0.f;
-    const float* xr = x + static_cast<int64_t>(row) * in;
-    for (int k = lane; k < in; k += 32) {
-        const float xv = operand(xr[k], tf32);
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<int64_t>(row) * in);  // in % 4 == 0, 16-byte aligned rows
+    const int q = in >> 2;
+    for (int k = lane; k < q; k += 32) {
+        const float4 xv = xr[k];
+        const float x0 = operand(xv.x, tf32), x1 = operand(xv.y, tf32), x2 = operand(xv.z, tf32), x3 = operand(xv.w, tf32);
+        float4 wv[S];
 #pragma unroll
         for (int s = 0; s < S; ++s)
-            if (s < out) acc[s] += xv * operand(w[static_cast<int64_t>(s) * in + k], tf32);
+            wv[s] = s < out ? __ldg(reinterpret_cast<const float4*>(w + static_cast<int64_t>(s) * in) + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+            acc[s] += x0 * operand(wv[s].x, tf32);
+            acc[s] += x1 * operand(wv[s].y, tf32);
+            acc[s] += x2 * operand(wv[s].z, tf32);
+            acc[s] += x3 * operand(wv[s].w, tf32);
+        }
     }
 #pragma unroll
     for (int s = 0; s < S; ++s)
@@ -86,12 +97,18 @@ __global__ void __launch_bounds__(256) narrow_wgrad_kernel(float* __restrict__ d
     __syncthreads();
     if (!last) return;
     __threadfence();
-    if (j < in)
-        for (int s = 0; s < out; ++s) {
-            float t = 0.f;
-            for (int sl = 0; sl < slabs; ++sl) t += __ldcg(&part[(static_cast<int64_t>(sl) * out + s) * in + j]);
-            dw[static_cast<int64_t>(s) * in + j] = t;
-        }
+    if (j < in) {
+        float t[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s) t[s] = 0.f;
+        for (int sl = 0; sl < slabs; ++sl)
+#pragma unroll
+            for (int s = 0; s < S; ++s)
+                if (s < out) t[s] += __ldcg(&part[(static_cast<int64_t>(sl) * out + s) * in + j]);
+#pragma unroll
+        for (int s = 0; s < S; ++s)
+            if (s < out) dw[static_cast<int64_t>(s) * in + j] = t[s];
+    }
     if (threadIdx.x == 0) counter[blockIdx.x] = 0;  // ready for the next launch
 }
 
@@ -136,7 +153,7 @@ int wb_narrow_linear_fwd(WbBackend* b, int mode, const float* x, const float* w,
 int wb_narrow_linear_wgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* x, int n, int in, int out, float* dw) {
     const int tf32 = mode == WB_MM_TF32;
     const int strips = (in + 255) / 256;
-    int slabs = std::max(1, std::min(std::min(n / 64, 64), (2 * b->sm_count + strips - 1) / strips));
+    int slabs = std::max(1, std::min(std::min(n / 64, 16), (2 * b->sm_count + strips - 1) / strips));
     const int per = ((n + slabs - 1) / slabs + 63) / 64 * 64;
     slabs = (n + per - 1) / per;
     const size_t part_bytes = static_cast<size_t>(slabs) * out * in * sizeof(float);
