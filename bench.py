@@ -214,12 +214,11 @@ def main():
         hx.copy_(torch.from_numpy(be.to_host(x, Layout.contiguous([n_in]), DType.F32)))
         hy.copy_(torch.from_numpy(be.to_host(y, Layout.contiguous([batch]), DType.I64)))
         host_batches.append((hx, hy))
-    lx, ly = Layout.contiguous([n_in]), Layout.contiguous([batch])
 
     def stage_from_device(i):
+        # the batch is already in HBM: the step reads it where it lies (two batches alternate)
         x, y = dev_batches[i % 2]
-        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(lx.view(x.ptr, DType.F32)), DType.F32, ctypes.c_void_p(tr.input_ptr())))
-        be.check(be.lib.wb_cast_into(be.handle, ctypes.byref(ly.view(y.ptr, DType.I64)), DType.I64, ctypes.c_void_p(tr.labels_ptr())))
+        be.check(be.lib.wb_trainer_set_input(tr.handle, ctypes.c_void_p(x.ptr), ctypes.c_void_p(y.ptr)))
 
     def barrier():
         torch.cuda.synchronize()
@@ -242,7 +241,7 @@ def main():
         return float(ms.item())
 
     def resident_step(i):
-        stage_from_device(i)       # device-to-device: the batch is already in HBM
+        stage_from_device(i)
         dp.step()
 
     losses = []
@@ -291,6 +290,7 @@ def main():
     dp.set_timing(False)
 
     # ---- e2e: through the host-facing calls -------------------------------------------------------
+    be.check(be.lib.wb_trainer_set_input(tr.handle, None, None))
     e2e_step(0)
     pending[0] = 1
     e2e_step(1)

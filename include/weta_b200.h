@@ -304,7 +304,10 @@ typedef struct WbLayerSpec { int32_t kind, a, b, c; double p; } WbLayerSpec;
 /* Adam / AdamW hyper-parameters (crates/weta-optim/src/lib.rs:178-207, 276-283). */
 typedef struct WbAdamConfig { double lr, beta1, beta2, eps, weight_decay; int32_t decoupled; } WbAdamConfig;
 typedef struct WbTrainer WbTrainer;
-/* Called during backward each time one layer's gradients are final: a contiguous arena range. */
+/* Called during backward each time one layer's gradients are final: a contiguous arena range.  Also called with
+ * (NULL, 0) at each "quiet point" of backward: right after a conv block's memory-bound BatchNorm pass has been queued
+ * and before its tensor-core contractions, the moment at which side-stream work (a gradient exchange) disturbs the
+ * step least. */
 typedef void (*wb_bucket_callback)(void* user, float* grad_range, int64_t len);
 
 /* Input is [batch, in_c, in_h, in_w] (NCHW; use in_h = in_w = 1 for flat features). */

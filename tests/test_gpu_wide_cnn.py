@@ -210,3 +210,46 @@ def test_dropout_with_p_zero_draws_no_seed(oracle, gpu):
         assert abs(tr.loss() - losses[step]) < 2e-4
     assert core.global_rng().state == state, "the fused trainer drew a seed for a p = 0 dropout"
     tr.close()
+
+
+def test_batch_norm_backward_sums_with_unusable_gamma(oracle, gpu, report):
+    """The backward sums of BatchNorm -> ReLU -> pool normally come from the pooled tensors (xhat at a window's winner is
+    (y - beta) / gamma); channels whose gamma is zero, tiny, or far below |beta| must be summed from the activation
+    instead.  Both kinds of channel in one layer, FP32 contractions, against the oracle's autograd chain."""
+    cfg = CnnConfig("cnn-implicit", 3, 16, 128, 32, 64)
+    batch = 16
+    ref = build_cnn(cfg, oracle, 42)
+    manual_seed(42)
+    tr = FusedTrainer(gpu, cnn_specs(cfg), batch, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=2)
+    tr.init_from_global_rng()
+    names = [n for n, _ in ref.named_parameters()]
+    rng = np.random.default_rng(8)
+    for bn in ("1", "5"):
+        gi, bi = names.index(f"{bn}.weight"), names.index(f"{bn}.bias")
+        c = ref.parameters()[gi].numpy().size
+        gamma = (1.0 + 0.2 * rng.standard_normal(c)).astype(np.float32)
+        beta = (0.3 * rng.standard_normal(c)).astype(np.float32)
+        gamma[0::4] = 0.0          # no slope at all
+        gamma[1::4] = 1e-8         # tiny
+        beta[2::4] = 100.0         # |beta| far above 64 |gamma|
+        for i, v in ((gi, gamma), (bi, beta)):
+            ref.parameters()[i].data.assign(Tensor.from_numpy(v, oracle))
+            tr.set_param(i, v)
+    opt = nn.Adam(ref.parameters(), 1e-3)
+    state = core.global_rng().state
+    x, y = synthetic_batch(cfg, batch, 0, 0, oracle)
+    want_loss = primitive_train_step(ref, opt, x, y)
+    core.global_rng().state = state
+    tr.stage(x.numpy(), y.numpy())
+    tr.forward_backward()
+    errs = {}
+    for k, (n, p) in enumerate(ref.named_parameters()):
+        if n in ("0.bias", "4.bias"):
+            continue
+        g = p.grad.numpy().reshape(-1)
+        errs[n] = float(np.abs(tr.get_grad(k) - g).max() / max(np.abs(g).max(), 1e-20))
+    report("BN backward sums with unusable gamma", loss=(tr.loss(), want_loss), grad_max_err=errs)
+    assert abs(tr.loss() - want_loss) < 2e-4
+    for n, e in errs.items():
+        assert e < 2e-3, (n, e)
+    tr.close()

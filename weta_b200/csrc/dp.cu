@@ -30,7 +30,8 @@
 #include "adam.cuh"
 #include "common.h"
 
-int wb_trainer_internal_info(WbTrainer* t, WbBackend** be, int64_t* batch, int64_t* in_elems, std::vector<std::pair<int64_t, int64_t>>* ranges);
+int wb_trainer_internal_info(WbTrainer* t, WbBackend** be, int64_t* batch, int64_t* in_elems, std::vector<std::pair<int64_t, int64_t>>* ranges,
+                             std::vector<int>* conv_follows);
 const WbAdamConfig* wb_trainer_adam_config(const WbTrainer* t);
 
 namespace {
@@ -251,6 +252,9 @@ struct WbDp {
     ncclComm_t comm = nullptr;
     cudaStream_t comm_stream = nullptr, adam_stream = nullptr, copy_stream = nullptr;
     std::vector<Bucket> buckets;
+    std::vector<int> defer;        // per bucket: a quiet point of backward follows its completion, start its work there
+    std::vector<int> deferred;     // buckets complete but not yet issued
+    bool defer_enabled = false;    // measured at 4 ranks: no gain (the BatchNorm pass recovers what the contractions then lose)
     std::vector<cudaEvent_t> bucket_ready;  // recorded on the compute stream when a bucket's gradients are final
     cudaEvent_t ev_side = nullptr, ev_adam = nullptr, ev_step = nullptr;
     int64_t n_params = 0, batch = 0, in_elems = 0;
@@ -291,6 +295,18 @@ int issue_bucket(WbDp* dp, int bi);
 void on_range(void* user, float* ptr, int64_t len) {
     WbDp* dp = static_cast<WbDp*>(user);
     if (dp->issue_error != WB_OK) return;
+    if (len == 0) {  // a quiet point of backward: start the work of the buckets that were waiting for one
+        for (int bi : dp->deferred) {
+            int s = issue_bucket(dp, bi);
+            if (s != WB_OK) {
+                dp->issue_error = s;
+                dp->issue_message = wb_last_error();
+                break;
+            }
+        }
+        dp->deferred.clear();
+        return;
+    }
     const int64_t off = ptr - dp->grad;
     if (off != dp->covered) {
         dp->issue_error = WB_ERR_INVALID;
@@ -301,11 +317,18 @@ void on_range(void* user, float* ptr, int64_t len) {
     while (dp->next_bucket < static_cast<int>(dp->buckets.size())) {
         const Bucket& b = dp->buckets[dp->next_bucket];
         if (dp->covered < b.off + b.len) break;
-        int s = issue_bucket(dp, dp->next_bucket);
-        if (s != WB_OK) {
-            dp->issue_error = s;
-            dp->issue_message = wb_last_error();
-            return;
+        if (dp->defer_enabled && dp->defer[dp->next_bucket]) {
+            // The next ops of backward are a conv block's BatchNorm pass, which streams HBM with every block slot of
+            // every SM taken: an exchange started now would share its bandwidth and push part of its single wave of
+            // blocks into a second one.  Hold the bucket until that pass is queued (the quiet point that follows).
+            dp->deferred.push_back(dp->next_bucket);
+        } else {
+            int s = issue_bucket(dp, dp->next_bucket);
+            if (s != WB_OK) {
+                dp->issue_error = s;
+                dp->issue_message = wb_last_error();
+                return;
+            }
         }
         dp->next_bucket++;
     }
@@ -488,7 +511,8 @@ extern "C" int wb_dp_create(WbTrainer* t, const WbDpId* id, int rank, int world,
     dp->rank = rank;
     dp->world = world;
     std::vector<std::pair<int64_t, int64_t>> ranges;
-    wb_trainer_internal_info(t, &dp->be, &dp->batch, &dp->in_elems, &ranges);
+    std::vector<int> conv_follows;
+    wb_trainer_internal_info(t, &dp->be, &dp->batch, &dp->in_elems, &ranges, &conv_follows);
     dp->n_params = wb_trainer_arena_len(t);
     dp->theta = wb_trainer_params(t);
     dp->grad = wb_trainer_grads(t);
@@ -496,6 +520,13 @@ extern "C" int wb_dp_create(WbTrainer* t, const WbDpId* id, int rank, int world,
     dp->v = wb_trainer_exp_avg_sq(t);
     if (bucket_elems <= 0) bucket_elems = 1 << 20;
     dp->buckets = plan_buckets(ranges, bucket_elems);
+    for (const Bucket& bk : dp->buckets) {  // a bucket ends with some layer range: is a conv block still ahead of it in backward?
+        int flag = 0;
+        for (size_t r = 0; r < ranges.size(); ++r)
+            if (ranges[r].first + ranges[r].second == bk.off + bk.len) flag = conv_follows[r];
+        dp->defer.push_back(flag);
+    }
+    if (const char* env = std::getenv("WETA_B200_DP_DEFER")) dp->defer_enabled = env[0] == '1';
     int s = WB_OK;
     auto fail = [&](int st) { wb_dp_destroy(dp); return st; };
     if (static_cast<int>(dp->buckets.size()) > MAX_BUCKETS) { wb_set_error("wb_dp_create: %zu buckets, at most %d", dp->buckets.size(), MAX_BUCKETS); return fail(WB_ERR_INVALID); }
@@ -646,7 +677,9 @@ extern "C" int wb_dp_step(WbDp* dp, const uint64_t* dropout_seeds, int n_seeds) 
     dp->next_bucket = 0;
     dp->covered = 0;
     dp->issue_error = WB_OK;
+    dp->deferred.clear();
     WB_TRY(wb_trainer_forward_backward(dp->tr, dropout_seeds, n_seeds));
+    if (dp->issue_error == WB_OK && !dp->deferred.empty()) on_range(dp, nullptr, 0);  // no quiet point came: start them now
     if (dp->issue_error != WB_OK) {
         wb_set_error("%s", dp->issue_message.c_str());
         return dp->issue_error;

@@ -499,38 +499,72 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
 // initialised and normally trained layers); the other channels are summed from x by the kernel below.
 __device__ __forceinline__ bool pooled_sums_ok(float g, float b) { return fabsf(g) * 64.f >= fabsf(b) && fabsf(g) >= 1e-6f; }
 
-// Same (channel, slab) items and the same layout of `part` as bn_relu_pool_bwd_pair_kernel<false, ...>.
+// Same (channel, slab) items and the same layout of `part` as bn_relu_pool_bwd_pair_kernel<false, ...>, one WARP per
+// item (no block-wide barrier: an item is a few hundred to a few thousand float4s).  Channels that fail the test above
+// are summed from x by the same warp, window by window, with the arithmetic of pool_window_grads.
 __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(const float* __restrict__ yp, const float* __restrict__ dyp,
-                                                                                const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                                                int64_t n_img, int c_total, int pooled, double* __restrict__ part,
-                                                                                int slabs) {
+                                                                                const float* __restrict__ x, const float* __restrict__ mean,
+                                                                                const float* __restrict__ rstd, const float* __restrict__ gamma,
+                                                                                const float* __restrict__ beta, int64_t n_img, int c_total, int h,
+                                                                                int w, double* __restrict__ part, int slabs) {
+    const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
     const int64_t per = (n_img + slabs - 1) / slabs;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * THREADS) >> 5, first = (blockIdx.x * THREADS + threadIdx.x) >> 5;
     const uint32_t q = static_cast<uint32_t>(pooled >> 2);  // pooled % 4 == 0 (checked by the host)
-    __shared__ double red[2][THREADS / 32];
-    for (int item = blockIdx.x; item < c_total * slabs; item += gridDim.x) {
+    for (int item = first; item < c_total * slabs; item += warps) {
         const int c = item / slabs, sl = item - c * slabs;
         const float g = __ldg(gamma + c), b = __ldg(beta + c);
-        if (!pooled_sums_ok(g, b)) continue;  // block-uniform
         const int64_t n0 = min(n_img, static_cast<int64_t>(sl) * per), n1 = min(n_img, n0 + per);
-        const uint32_t items = static_cast<uint32_t>(n1 - n0) * q;
         const int64_t stride = static_cast<int64_t>(c_total) * pooled, base = (n0 * c_total + c) * pooled;
         double s1 = 0.0, s2 = 0.0;
         float a1 = 0.f, a2 = 0.f;
         int flushed = 0;
-        for (uint32_t j = threadIdx.x; j < items; j += THREADS) {
-            const uint32_t n = j / q, i = j - n * q;
-            const int64_t o = base + n * stride + 4 * static_cast<int64_t>(i);
-            const float4 y = *reinterpret_cast<const float4*>(yp + o);
-            const float4 u = *reinterpret_cast<const float4*>(dyp + o);
-            const float ys[4] = {y.x, y.y, y.z, y.w}, us[4] = {u.x, u.y, u.z, u.w};
+        if (pooled_sums_ok(g, b)) {
+            const uint32_t items = static_cast<uint32_t>(n1 - n0) * q;
+            // four float4 pairs per lane in flight: all eight loads are issued before any of them is used
+            for (uint32_t j0 = lane; j0 < items; j0 += 128) {
+                float4 y[4], u[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-                if (ys[k] > 0.f) {
-                    a1 += us[k];
-                    a2 += us[k] * ((ys[k] - b) / g);
+                for (int t = 0; t < 4; ++t) {
+                    const uint32_t j = j0 + 32 * t;
+                    if (j < items) {
+                        const uint32_t n = j / q, i = j - n * q;
+                        const int64_t o = base + n * stride + 4 * static_cast<int64_t>(i);
+                        y[t] = *reinterpret_cast<const float4*>(yp + o);
+                        u[t] = *reinterpret_cast<const float4*>(dyp + o);
+                    } else {
+                        y[t] = u[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
                 }
-            if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const float ys[4] = {y[t].x, y[t].y, y[t].z, y[t].w}, us[4] = {u[t].x, u[t].y, u[t].z, u[t].w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        if (ys[k] > 0.f) {
+                            a1 += us[k];
+                            a2 += us[k] * ((ys[k] - b) / g);
+                        }
+                }
+                if (++flushed == 8) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+            }
+        } else {
+            const float m = __ldg(mean + c), r = __ldg(rstd + c);
+            const uint32_t up = static_cast<uint32_t>(pooled), items = static_cast<uint32_t>(n1 - n0) * up;
+            const int64_t xstride = static_cast<int64_t>(c_total) * h * w;
+            const float* xslab = x + (n0 * c_total + c) * h * w;
+            for (uint32_t j = lane; j < items; j += 32) {
+                const uint32_t n = j / up, i = j - n * up;
+                const uint32_t oy = i / static_cast<uint32_t>(ow), ox = i - oy * ow;
+                const float* src = xslab + n * xstride + 2 * oy * w + 2 * ox;
+                const float2 r0 = *reinterpret_cast<const float2*>(src), r1 = *reinterpret_cast<const float2*>(src + w);
+                float v[4] = {r0.x, r0.y, r1.x, r1.y}, go[4], xh[4];
+                pool_window_grads(v, m, r, g, b, dyp[base + n * stride + i], go, xh);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a1 += go[k]; a2 += go[k] * xh[k]; }
+                if (++flushed == 32) { s1 += a1; s2 += a2; a1 = a2 = 0.f; flushed = 0; }
+            }
         }
         s1 += a1;
         s2 += a2;
@@ -539,15 +573,10 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(c
             s1 += __shfl_down_sync(0xffffffffu, s1, sh);
             s2 += __shfl_down_sync(0xffffffffu, s2, sh);
         }
-        if (lane == 0) { red[0][warp] = s1; red[1][warp] = s2; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            double t1 = 0.0, t2 = 0.0;
-            for (int w = 0; w < THREADS / 32; ++w) { t1 += red[0][w]; t2 += red[1][w]; }
-            part[static_cast<int64_t>(item) * 2] = t1;
-            part[static_cast<int64_t>(item) * 2 + 1] = t2;
+        if (lane == 0) {
+            part[static_cast<int64_t>(item) * 2] = s1;
+            part[static_cast<int64_t>(item) * 2 + 1] = s2;
         }
-        __syncthreads();
     }
 }
 
@@ -942,20 +971,20 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     const float inv_count = static_cast<float>(1.0 / static_cast<double>(n * h * w));
     const FastDiv div_pairs(static_cast<uint32_t>(std::max<int64_t>(1, (h / 2) * (w / 4)))), div_owp(static_cast<uint32_t>(std::max<int64_t>(1, w / 4)));
     // y_pooled (the forward's output, when the caller still has it): channels with a usable gamma take their sums from
-    // the pooled tensors, a quarter of the bytes; the pass over x then skips those channels (all of them, normally).
+    // the pooled tensors, a quarter of the bytes; the same kernel sums the other channels (normally none) from x.
     const int64_t pooled = (h / 2) * (w / 2);
     static const bool sums_from_x = [] { const char* e = std::getenv("WETA_B200_BN_SUMS_FROM_X"); return e && e[0] == '1'; }();  // diagnostic switch
     const bool from_pooled = !sums_from_x && pairs && y_pooled && pooled % 4 == 0 && pooled < (int64_t(1) << 30) &&
                              ((reinterpret_cast<uintptr_t>(y_pooled) | reinterpret_cast<uintptr_t>(dy_pooled)) & 15) == 0;
     if (from_pooled) {
-        bn_relu_pool_bwd_sums_pooled_kernel<<<flat_blocks, THREADS, 0, b->stream>>>(y_pooled, dy_pooled, gamma, beta, n, static_cast<int>(c),
-                                                                                   static_cast<int>(pooled), part, splits);
-        WB_LAUNCH_OK(b);
-    }
-    if (pairs)
+        const int64_t warps_needed = static_cast<int64_t>(c) * splits;
+        const unsigned grid = static_cast<unsigned>(std::min<int64_t>((warps_needed + THREADS / 32 - 1) / (THREADS / 32), 8LL * b->sm_count));
+        bn_relu_pool_bwd_sums_pooled_kernel<<<grid, THREADS, 0, b->stream>>>(y_pooled, dy_pooled, x, save_mean, save_rstd, gamma, beta, n,
+                                                                            static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), part, splits);
+    } else if (pairs)
         bn_relu_pool_bwd_pair_kernel<false, false><<<flat_blocks, THREADS, 0, b->stream>>>(
             nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr, nullptr, n, static_cast<int>(c), static_cast<int>(h),
-            static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits, from_pooled ? 1 : 0);
+            static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits, 0);
     else
         bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
                                                                       static_cast<int>(h), static_cast<int>(w), part);

@@ -116,6 +116,28 @@ __global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ p
     *dst = ep.accumulate ? *dst + acc : acc;
 }
 
+// The same for many splits over a small output: one warp per output element, lanes over the splits (each lane adds its
+// splits in ascending order, the lanes' sums are combined by a fixed shuffle tree: one order, every run).
+__global__ void __launch_bounds__(256) splitk_reduce_warp(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
+                                                          int m, int n, tc::Epilogue ep) {
+    const int64_t i = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (i >= total) return;
+    float acc = 0.f;
+    for (int s = lane; s < splits; s += 32) acc += part[s * split_stride + i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if (lane != 0) return;
+    const int64_t per = static_cast<int64_t>(m) * n;
+    const int64_t batch = i / per, r = i % per;
+    const int row = static_cast<int>(r / n), col = static_cast<int>(r % n);
+    if (ep.bias_m) acc += ep.bias_m[row];
+    if (ep.bias_n) acc += ep.bias_n[col];
+    if (ep.relu) acc = fmaxf(acc, 0.f);
+    float* dst = ep.out + batch * ep.batch_stride_d + static_cast<int64_t>(row) * ep.ldd + col;
+    *dst = ep.accumulate ? *dst + acc : acc;
+}
+
 // hi = x with the 13 low mantissa bits cleared (exactly a tf32 value), lo = x - hi (exact in f32).
 __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
                                                    int64_t nb, int64_t outer, int64_t inner, int64_t bs, int64_t ld, int64_t inner_p) {
@@ -258,8 +280,12 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     }
     if (status == WB_OK && splits > 1) {
         const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
-        splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
-                                                                                        total, m, n, ep);
+        if (splits >= 32 && total <= (1 << 16))
+            splitk_reduce_warp<<<static_cast<unsigned>((total * 32 + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits,
+                                                                                                      total, total, m, n, ep);
+        else
+            splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
+                                                                                            total, m, n, ep);
         cudaError_t e = cudaPeekAtLastError();
         if (e != cudaSuccess) { wb_set_error("split-K reduce launch failed: %s", cudaGetErrorString(e)); status = WB_ERR_CUDA; }
         else be->launches++;

@@ -486,14 +486,23 @@ extern "C" int wb_trainer_bn_buffers(WbTrainer* t, int conv_index, float** runni
 }
 
 // Internal (dp.cu): the trainer's backend, batch geometry and per-layer arena ranges in arena order (last layer first).
-int wb_trainer_internal_info(WbTrainer* t, WbBackend** be, int64_t* batch, int64_t* in_elems, std::vector<std::pair<int64_t, int64_t>>* ranges) {
+// conv_follows[k]: after range k has been reported, backward still has a conv block to go (so a "quiet point"
+// notification, see wb_bucket_callback, will follow).
+int wb_trainer_internal_info(WbTrainer* t, WbBackend** be, int64_t* batch, int64_t* in_elems, std::vector<std::pair<int64_t, int64_t>>* ranges,
+                             std::vector<int>* conv_follows) {
     if (be) *be = t->be;
     if (batch) *batch = t->batch;
     if (in_elems) *in_elems = t->in_elems;
     if (ranges) {
         ranges->clear();
-        for (int i = static_cast<int>(t->layers.size()) - 1; i >= 0; --i)
-            if (t->layers[i].range_len > 0) ranges->push_back({t->layers[i].range_begin, t->layers[i].range_len});
+        if (conv_follows) conv_follows->clear();
+        for (int i = static_cast<int>(t->layers.size()) - 1; i >= 0; --i) {
+            if (t->layers[i].range_len <= 0) continue;
+            ranges->push_back({t->layers[i].range_begin, t->layers[i].range_len});
+            bool follows = false;
+            for (int j = 0; j < i; ++j) follows = follows || t->layers[j].kind == L_CONV;
+            if (conv_follows) conv_follows->push_back(follows ? 1 : 0);
+        }
     }
     return WB_OK;
 }
@@ -667,6 +676,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                                                    L.save_mean, L.save_rstd, dconv, t->grad + L.off_gamma, t->grad + L.off_beta,
                                                    t->grad + L.off_b, fuse ? t->dy_shift[0] : nullptr, fuse ? t->dy_shift[1] : nullptr, L.out_act));
             }
+            // Quiet point: the memory-bound pass of this block is queued and tensor-core contractions follow, which neither
+            // fill every block slot of the SMs nor live on HBM bandwidth; side-stream work started now disturbs the least.
+            if (t->cb) t->cb(t->cb_user, nullptr, 0);
             if (L.implicit) {
                 const WbConv3 geo{B, L.cin, L.h, L.w, L.cout};
                 const float* x3[3] = {L.x_shift[0], in_act, L.x_shift[1]};

@@ -220,11 +220,12 @@ class FusedTrainer:
         return out
 
     def set_bucket_callback(self, fn: Optional[Callable[[int, int], None]]):
-        """fn(device_pointer, n_floats) fires during backward whenever one layer's gradients are final."""
+        """fn(device_pointer, n_floats) fires during backward whenever one layer's gradients are final (the library's
+        "quiet point" notifications, which carry no range, are not forwarded)."""
         if fn is None:
             self._cb = BUCKET_CB(0)
         else:
-            self._cb = BUCKET_CB(lambda user, ptr, n: fn(ptr, n))
+            self._cb = BUCKET_CB(lambda user, ptr, n: fn(ptr, n) if n > 0 else None)
         self.be.check(self.lib.wb_trainer_set_bucket_callback(self.handle, self._cb, None))
 
 
