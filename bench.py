@@ -334,9 +334,10 @@ def main():
         "L0.im2col": ("hbm", in1 * 10), "L1.im2col": ("hbm", in2 * 10), "L1.col2im": ("hbm", in2 * 10),
         # BN+ReLU+pool forward: the statistics come from the convolution's epilogue, so x is read once and x/4 written;
         # block 0 also writes the two column-shifted copies of its output that block 1's implicit GEMM reads.
-        # Backward reads x and dy/4 twice (sums, then dx) and writes dx; block 1 also writes dx's two shifted copies.
+        # Backward: the sums pass reads the pooled output and the pooled gradient (x/4 each), the dx pass reads x and
+        # dy/4 and writes dx; block 1 also writes dx's two shifted copies.
         "L0.bn_relu_pool_fwd": ("hbm", act1 * 1.75), "L1.bn_relu_pool_fwd": ("hbm", act2 * 1.25),
-        "L0.bn_relu_pool_bwd": ("hbm", act1 * 3.5), "L1.bn_relu_pool_bwd": ("hbm", act2 * 5.5),
+        "L0.bn_relu_pool_bwd": ("hbm", act1 * 2.75), "L1.bn_relu_pool_bwd": ("hbm", act2 * 4.75),
         "L2.dropout_fwd": ("hbm", 8.0 * batch * fc_in), "L2.dropout_bwd": ("hbm", 8.0 * batch * fc_in),
         "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
         "L6.adam": ("hbm", 28.0 * tr.arena_len),

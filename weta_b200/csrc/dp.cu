@@ -158,6 +158,22 @@ __global__ void peer_announce_wait(PeerPtrs pp, int world, int rank, int bucket,
     }
 }
 
+// The end-of-step wait in one launch: thread (b, p) polls done[b][p] of this rank's block for every bucket b and peer p.
+__global__ void peer_wait_all_done(PeerPtrs pp, int world, int rank, int n_buckets, uint32_t seq, unsigned long long timeout_ns, uint32_t* status) {
+    const int b = threadIdx.x / MAX_WORLD, p = threadIdx.x % MAX_WORLD;
+    if (b >= n_buckets || p >= world) return;
+    if (*reinterpret_cast<volatile uint32_t*>(status) != 0) return;
+    const uint32_t* word = &pp.flags[rank]->done[b][p];
+    const unsigned long long t0 = global_ns();
+    while (static_cast<int32_t>(load_acquire_sys(word) - seq) < 0) {
+        if (global_ns() - t0 > timeout_ns) {
+            atomicCAS(status, 0u, 0x80000000u | (1u << 16) | (static_cast<uint32_t>(b) << 8) | static_cast<uint32_t>(p));
+            return;
+        }
+        __nanosleep(256);
+    }
+}
+
 struct FusedArgs {
     const float* grad[MAX_WORLD];  // the replicas' gradient arenas (peer or local pointers)
     float* theta[MAX_WORLD];       // the replicas' parameter arenas
@@ -689,11 +705,9 @@ extern "C" int wb_dp_step(WbDp* dp, const uint64_t* dropout_seeds, int n_seeds) 
     if (dp->world > 1 && dp->mode == WB_DP_PEER) {
         // The next step may start once every peer has stored its shards of every bucket here (which also means every
         // peer has finished reading this rank's gradients): wait for the `done` words of all buckets.
-        for (size_t bi = 0; bi < dp->buckets.size(); ++bi) {
-            peer_announce_wait<<<1, 32, 0, dp->comm_stream>>>(dp->peers, dp->world, dp->rank, static_cast<int>(bi), 1, 0, 1, dp->seq, dp->timeout_ns,
-                                                              dp->status_dev);
-            WB_LAUNCH_OK(dp->side_be);
-        }
+        peer_wait_all_done<<<1, MAX_BUCKETS * MAX_WORLD, 0, dp->comm_stream>>>(dp->peers, dp->world, dp->rank, static_cast<int>(dp->buckets.size()), dp->seq,
+                                                                              dp->timeout_ns, dp->status_dev);
+        WB_LAUNCH_OK(dp->side_be);
     }
     WB_CHECK_CUDA(cudaEventRecord(dp->ev_step, dp->comm_stream));
     WB_CHECK_CUDA(cudaStreamWaitEvent(dp->be->stream, dp->ev_step, 0));
