@@ -370,7 +370,8 @@ def main():
     gemm_ms = sum(v[1] for k, v in op_times.items() if k in work and work[k][0] == "tensor")
     gemm_flops = sum(work[k][1] * v[0] for k, v in op_times.items() if k in work and work[k][0] == "tensor")
     roofline["all_contractions_tflops"] = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
-    roofline["per_op"] = {k: {"bound": v["bound"], "achieved": round(v["achieved"], 1), "frac": round(v["frac"], 3)} for k, v in per_op.items()}
+    roofline["per_op"] = {k: {"bound": v["bound"], "achieved": round(v["achieved"], 1), "frac": round(v["frac"], 3), "ms": round(v["avg_ms"], 4)}
+                          for k, v in per_op.items()}
     roofline["side_stream_ms_per_step"] = round(bucket_ms / max(args.steps, 1), 4)  # exchange + optimizer of all buckets (overlaps backward)
 
     cpu = None

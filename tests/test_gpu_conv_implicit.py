@@ -12,7 +12,8 @@ pytestmark = pytest.mark.gpu
 P3 = Im2ColParams((3, 3), (1, 1), (1, 1), (1, 1))
 # (n, c, h, w, o): square and non-square images, pixel counts that are not multiples of the 32-pixel K block
 # or the 128/256-pixel tile, output channels below / above / not a multiple of the 128-row tile.
-SHAPES = [(3, 128, 8, 8, 32), (2, 128, 6, 12, 160), (2, 256, 16, 16, 64), (1, 128, 20, 20, 96), (5, 128, 4, 4, 128)]
+SHAPES = [(3, 128, 8, 8, 32), (2, 128, 6, 12, 160), (2, 256, 16, 16, 64), (1, 128, 20, 20, 96), (5, 128, 4, 4, 128),
+          (3, 128, 16, 16, 256), (2, 128, 32, 16, 32)]  # the last three 16-wide ones take the kernels whose taps share pixel copies
 
 
 def oracle_chain(oracle, x, w, bias, dy):

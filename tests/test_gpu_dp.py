@@ -64,16 +64,19 @@ def test_per_bucket_adam_equals_adam_after_backward_bit_for_bit(gpu):
     assert np.array_equal(bucketed[1], plain[1])
 
 
-def test_reduce_adam_broadcast_equals_sum_then_adam(gpu):
-    """The peer-mode kernel with four local buffers standing for four replicas: shard r of the range is owned by
-    "rank" r.  Afterwards every parameter buffer holds what wb_adam_step gives on the gradient sum scaled by 1/4."""
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_reduce_adam_broadcast_equals_sum_then_adam(gpu, world):
+    """The peer-mode kernel with `world` local buffers standing for as many replicas (each world size takes a different
+    unrolling of the kernel): shard r of the range is owned by "rank" r.  Afterwards every parameter buffer holds what
+    wb_adam_step gives on the gradient sum scaled by 1/world.  The shard length is not a multiple of the threads per
+    round, so the last round of every variant is a partial one."""
     lib = gpu.lib
     _declare(lib)
     _declare_dp(lib)
-    world, n = 4, 4 * 1024 * 3 + 64
+    n = world * (1024 * 300 + 64)
     rng = np.random.default_rng(9)
     theta0 = rng.standard_normal(n).astype(np.float32)
-    grads = [rng.standard_normal(n).astype(np.float32) * s for s in (1.0, 0.5, 2.0, 1e-3)]
+    grads = [rng.standard_normal(n).astype(np.float32) * s for s in (1.0, 0.5, 2.0, 1e-3, 3.0, 0.25, 1e2, 1.5)[:world]]
     gsum = grads[0].copy()
     for g in grads[1:]:
         gsum = gsum + g  # index order, f32

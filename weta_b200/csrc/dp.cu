@@ -190,32 +190,47 @@ struct FusedArgs {
 
 // Gradient sum over the replicas in index order, Adam on the sum, new parameters stored into every replica: the
 // reduce-scatter, the optimizer and the all-gather of one shard in one pass.  Loads from the replicas bypass L1
-// (another GPU wrote them); one thread handles four consecutive elements with 128-bit accesses.
+// (another GPU wrote them); one thread handles U groups of four consecutive elements at a time with 128-bit accesses,
+// and issues the U x world replica loads of a round before it uses any of them: a peer load takes a few microseconds,
+// so the bytes in flight per thread, not the link, set the rate (U = 8 / world keeps eight loads in flight).
+template <int U>
 __global__ void __launch_bounds__(512) reduce_adam_broadcast(FusedArgs a) {
     if (a.status && *a.status != 0) return;
     const int64_t groups = a.len / 4;
-    for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t i = a.off + g * 4;
-        float4 part[MAX_WORLD];
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t g0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g0 < groups; g0 += stride * U) {
+        float4 part[U][MAX_WORLD];
 #pragma unroll
-        for (int p = 0; p < MAX_WORLD; ++p)
-            if (p < a.world) part[p] = __ldcv(reinterpret_cast<const float4*>(a.grad[p] + i));
-        float4 s = part[0];
+        for (int u = 0; u < U; ++u) {
+            const int64_t g = g0 + u * stride;
+            if (g < groups) {
 #pragma unroll
-        for (int p = 1; p < MAX_WORLD; ++p)
-            if (p < a.world) { s.x += part[p].x; s.y += part[p].y; s.z += part[p].z; s.w += part[p].w; }
-        float4 th = *reinterpret_cast<const float4*>(a.theta[a.self] + i);
-        float4 mi = a.k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(a.m + i);
-        float4 vi = a.k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(a.v + i);
-        adam_one(th.x, s.x, mi.x, vi.x, a.k);
-        adam_one(th.y, s.y, mi.y, vi.y, a.k);
-        adam_one(th.z, s.z, mi.z, vi.z, a.k);
-        adam_one(th.w, s.w, mi.w, vi.w, a.k);
-        *reinterpret_cast<float4*>(a.m + i) = mi;
-        *reinterpret_cast<float4*>(a.v + i) = vi;
+                for (int p = 0; p < MAX_WORLD; ++p)
+                    if (p < a.world) part[u][p] = __ldcv(reinterpret_cast<const float4*>(a.grad[p] + a.off + g * 4));
+            }
+        }
 #pragma unroll
-        for (int p = 0; p < MAX_WORLD; ++p)
-            if (p < a.world) *reinterpret_cast<float4*>(a.theta[p] + i) = th;
+        for (int u = 0; u < U; ++u) {
+            const int64_t g = g0 + u * stride;
+            if (g >= groups) break;
+            const int64_t i = a.off + g * 4;
+            float4 s = part[u][0];
+#pragma unroll
+            for (int p = 1; p < MAX_WORLD; ++p)
+                if (p < a.world) { s.x += part[u][p].x; s.y += part[u][p].y; s.z += part[u][p].z; s.w += part[u][p].w; }
+            float4 th = *reinterpret_cast<const float4*>(a.theta[a.self] + i);
+            float4 mi = a.k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(a.m + i);
+            float4 vi = a.k.first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(a.v + i);
+            adam_one(th.x, s.x, mi.x, vi.x, a.k);
+            adam_one(th.y, s.y, mi.y, vi.y, a.k);
+            adam_one(th.z, s.z, mi.z, vi.z, a.k);
+            adam_one(th.w, s.w, mi.w, vi.w, a.k);
+            *reinterpret_cast<float4*>(a.m + i) = mi;
+            *reinterpret_cast<float4*>(a.v + i) = vi;
+#pragma unroll
+            for (int p = 0; p < MAX_WORLD; ++p)
+                if (p < a.world) *reinterpret_cast<float4*>(a.theta[p] + i) = th;
+        }
     }
     if (a.block_counter) {
         __threadfence_system();  // this block's stores to the replicas are ordered before the signal below
@@ -229,6 +244,12 @@ __global__ void __launch_bounds__(512) reduce_adam_broadcast(FusedArgs a) {
             }
         }
     }
+}
+
+void launch_reduce_adam_broadcast(const FusedArgs& a, int blocks, cudaStream_t stream) {
+    if (a.world <= 2) reduce_adam_broadcast<4><<<blocks, 512, 0, stream>>>(a);
+    else if (a.world <= 4) reduce_adam_broadcast<2><<<blocks, 512, 0, stream>>>(a);
+    else reduce_adam_broadcast<1><<<blocks, 512, 0, stream>>>(a);
 }
 
 struct Bucket {
@@ -271,6 +292,8 @@ struct WbDp {
     std::vector<int> defer;        // per bucket: a quiet point of backward follows its completion, start its work there
     std::vector<int> deferred;     // buckets complete but not yet issued
     bool defer_enabled = false;    // measured at 4 ranks: no gain (the BatchNorm pass recovers what the contractions then lose)
+    bool defer_all = false;        // diagnostic (WETA_B200_DP_DEFER=2): no exchange starts before backward is over
+    bool flushing = false;
     std::vector<cudaEvent_t> bucket_ready;  // recorded on the compute stream when a bucket's gradients are final
     cudaEvent_t ev_side = nullptr, ev_adam = nullptr, ev_step = nullptr;
     int64_t n_params = 0, batch = 0, in_elems = 0;
@@ -312,6 +335,7 @@ void on_range(void* user, float* ptr, int64_t len) {
     WbDp* dp = static_cast<WbDp*>(user);
     if (dp->issue_error != WB_OK) return;
     if (len == 0) {  // a quiet point of backward: start the work of the buckets that were waiting for one
+        if (dp->defer_all && !dp->flushing) return;
         for (int bi : dp->deferred) {
             int s = issue_bucket(dp, bi);
             if (s != WB_OK) {
@@ -333,7 +357,7 @@ void on_range(void* user, float* ptr, int64_t len) {
     while (dp->next_bucket < static_cast<int>(dp->buckets.size())) {
         const Bucket& b = dp->buckets[dp->next_bucket];
         if (dp->covered < b.off + b.len) break;
-        if (dp->defer_enabled && dp->defer[dp->next_bucket]) {
+        if (dp->defer_all || (dp->defer_enabled && dp->defer[dp->next_bucket])) {
             // The next ops of backward are a conv block's BatchNorm pass, which streams HBM with every block slot of
             // every SM taken: an exchange started now would share its bandwidth and push part of its single wave of
             // blocks into a second one.  Hold the bucket until that pass is queued (the quiet point that follows).
@@ -403,7 +427,7 @@ int issue_bucket(WbDp* dp, int bi) {
         a.status = dp->status_dev;
         const int64_t groups = shard / 4;
         const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(dp->fused_blocks, (groups + 511) / 512)));
-        reduce_adam_broadcast<<<blocks, 512, 0, dp->comm_stream>>>(a);
+        launch_reduce_adam_broadcast(a, blocks, dp->comm_stream);
         WB_LAUNCH_OK(dp->side_be);
     }
     if (dp->timing) {
@@ -542,7 +566,7 @@ extern "C" int wb_dp_create(WbTrainer* t, const WbDpId* id, int rank, int world,
             if (ranges[r].first + ranges[r].second == bk.off + bk.len) flag = conv_follows[r];
         dp->defer.push_back(flag);
     }
-    if (const char* env = std::getenv("WETA_B200_DP_DEFER")) dp->defer_enabled = env[0] == '1';
+    if (const char* env = std::getenv("WETA_B200_DP_DEFER")) { dp->defer_enabled = env[0] == '1'; dp->defer_all = env[0] == '2'; }
     int s = WB_OK;
     auto fail = [&](int st) { wb_dp_destroy(dp); return st; };
     if (static_cast<int>(dp->buckets.size()) > MAX_BUCKETS) { wb_set_error("wb_dp_create: %zu buckets, at most %d", dp->buckets.size(), MAX_BUCKETS); return fail(WB_ERR_INVALID); }
@@ -695,7 +719,11 @@ extern "C" int wb_dp_step(WbDp* dp, const uint64_t* dropout_seeds, int n_seeds) 
     dp->issue_error = WB_OK;
     dp->deferred.clear();
     WB_TRY(wb_trainer_forward_backward(dp->tr, dropout_seeds, n_seeds));
-    if (dp->issue_error == WB_OK && !dp->deferred.empty()) on_range(dp, nullptr, 0);  // no quiet point came: start them now
+    if (dp->issue_error == WB_OK && !dp->deferred.empty()) {  // no quiet point came: start them now
+        dp->flushing = true;
+        on_range(dp, nullptr, 0);
+        dp->flushing = false;
+    }
     if (dp->issue_error != WB_OK) {
         wb_set_error("%s", dp->issue_message.c_str());
         return dp->issue_error;
@@ -870,7 +898,7 @@ extern "C" int wb_reduce_adam_broadcast(WbBackend* b, const float* const* grads,
     a.k = wb_adam_constants(t, lr, beta1, beta2, eps, weight_decay, decoupled, grad_scale);
     const int64_t groups = len / 4;
     const int blocks = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(4 * b->sm_count, (groups + 511) / 512)));
-    reduce_adam_broadcast<<<blocks, 512, 0, b->stream>>>(a);
+    launch_reduce_adam_broadcast(a, blocks, b->stream);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

@@ -152,12 +152,12 @@ __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, 
     lo[i] = v - h;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8, int MT = 1>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8, int MT = 1, int HALO = 0>
 int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
-    using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW, MT>;
+    using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW, MT, HALO>;
     constexpr size_t smem = sizeof(SS) + 1024;
     static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
-    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW, MT>;
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW, MT, HALO>;
     // The attribute belongs to the device's context: one flag per device ordinal and instantiation.
     static std::atomic<uint64_t> attr_done{0};
     const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
@@ -202,7 +202,7 @@ bool pair_mode(int m, int BN) {
 // Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
 // the persistent kernel, split-K finish.  `args` arrives with its tensor maps, k_blocks and mode fields set.
 int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool pair, bool amn, bool bmn,
-              const tc::Epilogue& ep, int force_splits, bool two_blocks = false) {
+              const tc::Epilogue& ep, int force_splits, bool two_blocks = false, bool shared_taps = false) {
     args.m = m;
     args.n = n;
     args.error_flag = st->error_flag;
@@ -251,6 +251,12 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
         // Shared memory: a 192 KB ring (6 x 32 KB per CTA of a pair, 4 x 48 KB for BN = 256, 5 x 32 KB for BN = 128)
         // + 32 KB epilogue staging; one persistent CTA per SM.
         if (status != WB_OK) {
+        } else if (shared_taps && !pair && splits == 1 && BN == 256 && !amn && bmn) {
+            // Implicit convolution on 16-pixel-wide images, 128-row tiles: the taps of a kernel column share their pixel
+            // copies (a fifth fewer operand bytes through L2; the input gradient of the 128 -> 256 channel layer went
+            // from 511 to 618 TFLOP/s).  The ring slots grow by one 4 KB chunk and the staging shrinks to four warps'.
+            // CTA pairs gain nothing from it (607 against 610 TFLOP/s on that layer's forward, with 5 slots for 6).
+            status = launch_tc<256, 4, false, true, 1, 4, 1, 1>(be, st, args, grid);
         } else if (pair) {
             if (!amn && !bmn) status = launch_tc<256, 6, false, false, 2>(be, st, args, grid);
             else if (!amn && bmn) status = launch_tc<256, 6, false, true, 2>(be, st, args, grid);
@@ -409,7 +415,8 @@ int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const 
         args.conv_cb = static_cast<int>(ch / 32);
         args.batched_a = 0;
         args.batched_b = 1;
-        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, BN, pair_mode(m, BN), false, true, ep, 1);
+        static const bool no_shared_taps = [] { const char* e = std::getenv("WETA_B200_NO_SHARED_TAPS"); return e && e[0] == '1'; }();
+        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, BN, pair_mode(m, BN), false, true, ep, 1, false, w == 16 && !no_shared_taps);
     }
     const int BN = m > 128 ? 256 : 128;
     for (int kx = 0; kx < 3; ++kx) {

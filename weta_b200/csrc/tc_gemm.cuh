@@ -206,11 +206,11 @@ __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 
-template <int BN, int STAGES, int CTAS, int EPW, int MT>
+template <int BN, int STAGES, int CTAS, int EPW, int MT, int HALO = 0>
 struct SharedStorage {
     // Stage buffers first: each must start on a 1024-byte boundary for the 128B swizzle.
     alignas(1024) float a[STAGES][MT * BM * BK];   // MT row blocks of BM rows, one after the other
-    alignas(1024) float b[STAGES][BN / CTAS * BK];  // a CTA of a pair holds half of the tile's B rows
+    alignas(1024) float b[STAGES][(BN / CTAS + 32 * HALO) * BK];  // a CTA of a pair holds half of the tile's B rows
     // Epilogue staging, one 32 x 32 slab per epilogue warp; 16-byte chunk j of row r sits at chunk j ^ (r & 7),
     // so the row-per-lane writes and the row-segment reads are both free of bank conflicts without padding.
     alignas(128) float stage[EPW][32 * 32];
@@ -240,11 +240,19 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // MT = 2 (single CTAs only): one CTA owns a (2*BM) x BN tile as two BM-row blocks that share every B box - the
 // same third fewer operand bytes per flop as a CTA pair, inside one SM.  Both TMEM accumulators belong to the one
 // tile, so its epilogue does not overlap the next tile's MMAs: used for contractions whose tiles run long.
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT>
+// HALO = 1 (conv_mode 1 on images 16 pixels wide, one split): the three taps of one kernel column share their
+// pixels.  Rows come two to a 32-pixel chunk, so the windows of the upper and the lower tap (one image row up, one
+// down) are the same chunks, one chunk apart, of a single copy that starts one image row early and is one chunk
+// longer; only the middle tap needs a copy of its own.  The K blocks of a (channel block, kernel column) then run in
+// the order middle, upper, lower; the lower tap's ring slot carries weights only and its MMAs read the pixels from
+// the upper tap's slot, which is handed back together with its own.  Two pixel copies instead of three per kernel
+// column: a fifth fewer operand bytes through L2 on 128 x 256 tiles.  (Works for CTA pairs too; measured no gain there.)
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT, int HALO = 0>
 __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using SS = SharedStorage<BN, STAGES, CTAS, EPW, MT>;
+    using SS = SharedStorage<BN, STAGES, CTAS, EPW, MT, HALO>;
     static_assert(MT == 1 || (CTAS == 1 && BN == 256), "two row blocks per CTA: single CTAs with 256-wide tiles");
+    static_assert(HALO == 0 || (MT == 1 && B_MN && !A_MN && STAGES >= 3), "shared tap windows: implicit convolution tiles only");
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
     constexpr int TILE_M = BM * CTAS * MT;   // output rows per tile
@@ -340,7 +348,20 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 const int kz = args.kpb > 0 ? kb / args.kpb : 0;
                 const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
                 const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
-                if (args.conv_mode == 1) {
+                if constexpr (HALO == 1) {
+                    // kb = (channel block * 3 + kx) * 3 + r; r = 0: middle tap (ky = 1) with its own pixels, r = 1: upper
+                    // tap (ky = 0) with the long copy that starts one image row early, r = 2: lower tap (ky = 2), weights only.
+                    const int cb = kb / 9, j = kb - cb * 9;
+                    const int kx = j / 3, r = j - kx * 3;
+                    const int tap = (r == 0 ? 1 : (r == 1 ? 0 : 2)) * 3 + kx;
+                    copy(&ss.a[s][0], ma, (tap * args.conv_cb + cb) * BK, m0, 0);
+                    if (r < 2) {
+                        const CUtensorMap* mx = &args.seg[kx].b;
+                        const int x0 = n0 - (r == 1 ? args.conv_w : 0);
+                        const int chunks = B_ROWS / 32 + (r == 1 ? 1 : 0);
+                        for (int ch = 0; ch < chunks; ++ch) copy(&ss.b[s][ch * 32 * BK], mx, x0 + ch * 32, cb * 32, batch);
+                    }
+                } else if (args.conv_mode == 1) {
                     // kb = channel block * 9 + tap, tap = ky*3 + kx: the nine taps of a channel block follow one
                     // another, so the rows a tap shares with the previous ones (same pixels, moved by a row) are
                     // still in L2.  The window of tap (ky, kx) over a run of pixels is the same run, moved (ky-1)
@@ -385,8 +406,14 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 if (!mbar_wait(&ss.empty[s], ph ^ 1)) { ok = false; break; }
-                if (rank == 0)  // the leader's barrier counts both CTAs' bytes
-                    mbar_expect_tx(&ss.full[s], static_cast<uint32_t>((blocks_of(cur) * BM * BK + B_ROWS * BK) * sizeof(float)) * CTAS);
+                if (rank == 0) {  // the leader's barrier counts both CTAs' bytes
+                    int b_rows = B_ROWS;
+                    if constexpr (HALO == 1) {
+                        const int r = cur.kb % 3;
+                        b_rows = r == 0 ? B_ROWS : (r == 1 ? B_ROWS + 32 : 0);
+                    }
+                    mbar_expect_tx(&ss.full[s], static_cast<uint32_t>((blocks_of(cur) * BM * BK + b_rows * BK) * sizeof(float)) * CTAS);
+                }
                 issue(s, cur);
                 next(cur);
             }
@@ -423,7 +450,13 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&ss.full[s], ph)) { ok = false; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t b_base = smem_u32(&ss.b[s][0]);
+                    uint32_t b_base = smem_u32(&ss.b[s][0]);
+                    int halo_r = 0;
+                    if constexpr (HALO == 1) {
+                        halo_r = (kb_begin + i) % 3;
+                        // the lower tap reads the upper tap's copy, one chunk (two image rows) further on
+                        if (halo_r == 2) b_base = smem_u32(&ss.b[(it + STAGES - 1) % STAGES][0]) + 32 * BK * 4;
+                    }
                     for (int sub = 0; sub < nsub; ++sub) {
                         const uint32_t a_base = smem_u32(&ss.a[s][sub * BM * BK]);
                         const uint32_t d = tmem_d + static_cast<uint32_t>(sub * BN);
@@ -440,7 +473,9 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                             else umma_tf32(d, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
                         }
                     }
-                    commit(&ss.empty[s]);  // frees this stage once the MMAs above have read it
+                    // frees this stage once the MMAs above have read it (the upper tap's stage stays until the lower tap is done)
+                    if (HALO == 1 && halo_r == 2) commit(&ss.empty[(it + STAGES - 1) % STAGES]);
+                    if (HALO == 0 || halo_r != 1) commit(&ss.empty[s]);
                 }
                 if (!ok) break;
                 commit(&ss.tmem_full[acc]);  // accumulator complete once every MMA above has retired
