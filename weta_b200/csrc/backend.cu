@@ -169,6 +169,15 @@ void wb_arena_free(WbBackend* b, void* p, size_t klass) {
     b->free_blocks.emplace(klass, p);
 }
 
+int wb_block_counters(WbBackend* b, unsigned int** out) {
+    if (!b->narrow_counters) {
+        WB_CHECK_CUDA(cudaMalloc(&b->narrow_counters, 4096 * sizeof(unsigned int)));
+        WB_CHECK_CUDA(cudaMemsetAsync(b->narrow_counters, 0, 4096 * sizeof(unsigned int), b->stream));
+    }
+    *out = static_cast<unsigned int*>(b->narrow_counters);
+    return WB_OK;
+}
+
 int wb_scratch(WbBackend* b, size_t bytes, void** out) {
     if (bytes > b->scratch_bytes) {
         // Queued kernels may still read the old scratch: wait before releasing it.

@@ -87,7 +87,8 @@ struct WbBackend {
     size_t scratch_bytes = 0;
     // lazily created resources of the tensor-core GEMM path
     void* gemm_state = nullptr;
-    // block counters of the narrow linear layer's weight gradient (narrow_linear.cu), zero between launches
+    // 4096 block counters for kernels whose last block finishes a reduction (narrow_linear.cu, trainer.cu); every such
+    // kernel finds them zero and leaves them zero
     void* narrow_counters = nullptr;
 };
 
@@ -111,6 +112,8 @@ inline bool wb_is_contiguous(const WbView& v) {
 int wb_arena_alloc(WbBackend* b, size_t bytes, void** out, size_t* klass);
 void wb_arena_free(WbBackend* b, void* p, size_t klass);
 int wb_scratch(WbBackend* b, size_t bytes, void** out);
+// The backend's 4096 zeroed block counters (created on first use).
+int wb_block_counters(WbBackend* b, unsigned int** out);
 int wb_new_storage(WbBackend* b, int64_t len, int dtype, WbStorage** out);
 
 // RAII profiling scope: when profiling is on, brackets the op with events and a sync (like the

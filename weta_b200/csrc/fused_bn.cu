@@ -251,17 +251,26 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __re
 }
 
 // dbeta = sum dy, dgamma = sum dy*xhat (gradients of the affine parameters).
-__global__ void bn_bwd_finalize_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ dgamma,
-                                       float* __restrict__ dbeta) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel: lane l adds the slabs l, l + 32, ... in ascending order and the lanes' sums are combined by a
+// fixed shuffle tree (one order, every run).
+__global__ void __launch_bounds__(128) bn_bwd_finalize_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ dgamma,
+                                                              float* __restrict__ dbeta) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= c_total) return;
     double s1 = 0.0, s2 = 0.0;
-    for (int s = 0; s < splits; ++s) {
+    for (int s = lane; s < splits; s += 32) {
         s1 += part[(static_cast<int64_t>(c) * splits + s) * 2];
         s2 += part[(static_cast<int64_t>(c) * splits + s) * 2 + 1];
     }
-    dbeta[c] = static_cast<float>(s1);
-    dgamma[c] = static_cast<float>(s2);
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) {
+        s1 += __shfl_down_sync(0xffffffffu, s1, sh);
+        s2 += __shfl_down_sync(0xffffffffu, s2, sh);
+    }
+    if (lane == 0) {
+        dbeta[c] = static_cast<float>(s1);
+        dgamma[c] = static_cast<float>(s2);
+    }
 }
 
 // dx = gamma * rstd * (dy - dbeta/count - xhat * dgamma/count)
@@ -714,12 +723,15 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
     }
 }
 
-__global__ void sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel, as bn_bwd_finalize_kernel.
+__global__ void __launch_bounds__(128) sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= c_total) return;
     double s = 0.0;
-    for (int k = 0; k < splits; ++k) s += part[static_cast<int64_t>(c) * splits + k];
-    out[c] = static_cast<float>(s);
+    for (int k = lane; k < splits; k += 32) s += part[static_cast<int64_t>(c) * splits + k];
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) s += __shfl_down_sync(0xffffffffu, s, sh);
+    if (lane == 0) out[c] = static_cast<float>(s);
 }
 
 // Number of image slabs per channel for the per-channel reductions (grid = channels x slabs).  The grid
@@ -862,7 +874,7 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
     bn_bwd_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, dy, save_mean, save_rstd, n, static_cast<int>(c), hw,
                                                                                           static_cast<double*>(s));
     WB_LAUNCH_OK(b);
-    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
+    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
     unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw / 4 + THREADS - 1) / THREADS, 64)));
     for (int64_t p0 = 0; p0 < n * c; p0 += 65535 / c * c) {
@@ -989,7 +1001,7 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
         bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
                                                                       static_cast<int>(h), static_cast<int>(w), part);
     WB_LAUNCH_OK(b);
-    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
+    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
     if (pairs && dx_left)
         bn_relu_pool_bwd_pair_kernel<true, true><<<flat_blocks, THREADS, 0, b->stream>>>(
@@ -1005,7 +1017,7 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
                                                                    dbias_conv ? bias_part : nullptr);
     WB_LAUNCH_OK(b);
     if (dbias_conv) {
-        sum_parts_kernel<<<static_cast<unsigned>((c + 127) / 128), 128, 0, b->stream>>>(bias_part, splits, static_cast<int>(c), dbias_conv);
+        sum_parts_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(bias_part, splits, static_cast<int>(c), dbias_conv);
         WB_LAUNCH_OK(b);
     }
     return WB_OK;

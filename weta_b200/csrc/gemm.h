@@ -40,6 +40,5 @@ int wb_matmul_simt(WbBackend* be, const WbView* a, const WbView* b, void* out);
 
 // Linear layers with at most 16 outputs on CUDA cores, in the arithmetic of `mode` (narrow_linear.cu).
 bool wb_narrow_linear_ok(int64_t n, int64_t in, int64_t out, const float* x, const float* w);
-int wb_narrow_linear_fwd(WbBackend* b, int mode, const float* x, const float* w, const float* bias, int n, int in, int out, int relu, float* y);
 int wb_narrow_linear_wgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* x, int n, int in, int out, float* dw);
 int wb_narrow_linear_dgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* w, int n, int in, int out, float* dx);

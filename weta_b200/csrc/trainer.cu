@@ -167,10 +167,11 @@ int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, i
     return wb_gemm_dispatch(t->be, t->matmul_mode, A, B, batch, m, n, k, ep, span_batch, used_tc);
 }
 
-// Column sums in two fixed-order stages: part[slab][j] over a slab of rows (a warp reads 32 adjacent columns of
-// one row, eight rows in flight per block), then the slabs in ascending order.
-__global__ void __launch_bounds__(256) column_sum_slabs(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int64_t per,
-                                                        float* __restrict__ part) {
+// Column sums in two fixed-order stages inside one launch: part[slab][j] over a slab of rows (a warp reads 32 adjacent
+// columns of one row, eight rows in flight per block); the last block of a column strip to finish then adds the
+// strip's slabs in ascending order.
+__global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int64_t per,
+                                                         float* __restrict__ part, unsigned int* __restrict__ counter, float* __restrict__ dst) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + lane;
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * per, r1 = min(rows, r0 + per);
@@ -186,21 +187,26 @@ __global__ void __launch_bounds__(256) column_sum_slabs(const float* __restrict_
         for (int w = 0; w < 8; ++w) t += red[w][lane];
         part[static_cast<int64_t>(blockIdx.y) * cols + col] = t;
     }
-}
-
-__global__ void __launch_bounds__(256) column_sum_finish(const float* __restrict__ part, int slabs, int64_t cols, float* __restrict__ dst) {
-    const int64_t col = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-    if (col >= cols) return;
-    float t = 0.f;
-    for (int s = 0; s < slabs; ++s) t += part[static_cast<int64_t>(s) * cols + col];
-    dst[col] = t;
+    __threadfence();
+    __syncthreads();
+    __shared__ unsigned int last;
+    if (threadIdx.x == 0) last = atomicAdd(&counter[blockIdx.x], 1u) == gridDim.y - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    if (warp == 0 && col < cols) {
+        float t = 0.f;
+        for (unsigned int s = 0; s < gridDim.y; ++s) t += __ldcg(&part[static_cast<int64_t>(s) * cols + col]);
+        dst[col] = t;
+    }
+    if (threadIdx.x == 0) counter[blockIdx.x] = 0;  // ready for the next launch
 }
 
 // dst[j] = sum_i src[i][j] over a dense [rows, cols] matrix (a bias gradient, crates/weta-autograd/src/ops.rs:46-58).
 // Small matrices go through Backend::reduce (the reference's summation order); tall ones are split over row slabs so
 // the whole GPU takes part (same result every run, order differs from the sequential sum by rounding only).
 int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, int64_t pitch, float* dst) {
-    if (rows < 256 || cols <= 0) {
+    if (rows < 256 || cols <= 0 || cols > 32 * 4096) {
         WbView v{};
         v.data = const_cast<float*>(src); v.dtype = WB_F32; v.ndim = 2;
         v.shape[0] = rows; v.shape[1] = cols; v.stride[0] = pitch; v.stride[1] = 1;
@@ -214,11 +220,10 @@ int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, int64
     slabs = (rows + per - 1) / per;
     void* scratch = nullptr;
     WB_TRY(wb_scratch(b, static_cast<size_t>(slabs) * cols * sizeof(float), &scratch));
-    column_sum_slabs<<<dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs)), 256, 0, b->stream>>>(src, rows, cols, pitch, per,
-                                                                                                                     static_cast<float*>(scratch));
-    WB_LAUNCH_OK(b);
-    column_sum_finish<<<static_cast<unsigned>((cols + 255) / 256), 256, 0, b->stream>>>(static_cast<const float*>(scratch), static_cast<int>(slabs),
-                                                                                      cols, dst);
+    unsigned int* counters = nullptr;
+    WB_TRY(wb_block_counters(b, &counters));
+    column_sum_kernel<<<dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs)), 256, 0, b->stream>>>(src, rows, cols, pitch, per,
+                                                                                                                      static_cast<float*>(scratch), counters, dst);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -615,9 +620,9 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             if (L.relu && !L.relu_bwd_done) WB_TRY(relu_bwd_inplace(t, gz, L.out_act, B * L.out));
             // MatmulBw (ops.rs:821-827): dW = dZ^T X, db = sum over the batch, dX = dZ W
             // The logits layer (at most 16 outputs): its gradients on the CUDA cores.  Measured on 1024 -> 10: dX 8 us against
-            // 16 us on the tensor-core path at batch 512 (equal at 4096); dW 16 us against 24 us at batch 512 but 44 us
-            // against 24 us at 4096, so dW only up to 1024 samples; the forward product stays on the tensor cores (15 us
-            // against 27 us).
+            // 16 us on the tensor-core path at batch 512 (equal at 4096); dW only up to 1024 samples (one block per 32
+            // inputs walks the whole batch); the forward product stays on the tensor cores (a warp per row on CUDA cores
+            // took 27-30 us against 15 us, at batch 512 and at 4096).
             if (wb_narrow_linear_ok(B, L.in, L.out, in_act, t->theta + L.off_w)) {
                 if (B <= 1024) {
                     OpTimer tm(t, i, "linear_wgrad_gemm");
