@@ -335,9 +335,9 @@ def main():
         # BN+ReLU+pool forward: the statistics come from the convolution's epilogue, so x is read once and x/4 written;
         # block 0 also writes the two column-shifted copies of its output that block 1's implicit GEMM reads.
         # Backward: the sums pass reads the pooled output and the pooled gradient (x/4 each), the dx pass reads x and
-        # dy/4 and writes dx; block 1 also writes dx's two shifted copies.
+        # dy/4 and writes dx (no shifted copies of dx: block 1's input gradient applies the horizontal moves to its result).
         "L0.bn_relu_pool_fwd": ("hbm", act1 * 1.75), "L1.bn_relu_pool_fwd": ("hbm", act2 * 1.25),
-        "L0.bn_relu_pool_bwd": ("hbm", act1 * 2.75), "L1.bn_relu_pool_bwd": ("hbm", act2 * 4.75),
+        "L0.bn_relu_pool_bwd": ("hbm", act1 * 2.75), "L1.bn_relu_pool_bwd": ("hbm", act2 * 2.75),
         "L2.dropout_fwd": ("hbm", 8.0 * batch * fc_in), "L2.dropout_bwd": ("hbm", 8.0 * batch * fc_in),
         "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
         "L6.adam": ("hbm", 28.0 * tr.arena_len),

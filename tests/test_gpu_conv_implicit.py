@@ -13,7 +13,9 @@ P3 = Im2ColParams((3, 3), (1, 1), (1, 1), (1, 1))
 # (n, c, h, w, o): square and non-square images, pixel counts that are not multiples of the 32-pixel K block
 # or the 128/256-pixel tile, output channels below / above / not a multiple of the 128-row tile.
 SHAPES = [(3, 128, 8, 8, 32), (2, 128, 6, 12, 160), (2, 256, 16, 16, 64), (1, 128, 20, 20, 96), (5, 128, 4, 4, 128),
-          (3, 128, 16, 16, 256), (2, 128, 32, 16, 32)]  # the last three 16-wide ones take the kernels whose taps share pixel copies
+          (3, 128, 16, 16, 256), (2, 128, 32, 16, 32),  # 16-wide: the kernels whose taps share pixel copies
+          # widths 4 / 8 / 16 / 32 with a multiple of 128 pixels: the input gradient that reads dY without shifted copies
+          (2, 128, 32, 4, 32), (2, 128, 16, 8, 64), (1, 128, 8, 32, 32), (2, 128, 24, 16, 96)]
 
 
 def oracle_chain(oracle, x, w, bias, dy):

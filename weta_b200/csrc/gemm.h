@@ -22,6 +22,10 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch, i
 int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const img[3], int64_t batch, int64_t ch, int64_t h, int64_t w, int m,
                     tc::Epilogue ep);
 
+// Whether mode 3 of wb_tc_conv_gemm (input gradient from the unshifted gradient tensor) takes this layer: ch = the
+// contraction's channels (the layer's outputs), m = the result's rows (its inputs).
+bool wb_tc_conv_mode3_ok(int64_t ch, int64_t h, int64_t w, int64_t m);
+
 // Implicit 3x3 convolution built on wb_tc_conv_gemm (conv_implicit.cu).
 struct WbConv3 { int64_t n, c, h, w, o; };
 bool wb_conv3_eligible(const WbConv3& g);
@@ -30,6 +34,8 @@ int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst
 int wb_conv3_fwd(WbBackend* b, const WbConv3& g, const float* const x3[3], const float* wr, const float* bias, float* y,
                  double* channel_sums);
 int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float* const x3[3], float* dwr, float* dweight);
+// dy3[0] == dy3[2] == nullptr: the layer must pass wb_conv3_dgrad_needs_no_copies; the gradient is then read from dy3[1] alone.
+bool wb_conv3_dgrad_needs_no_copies(const WbConv3& g);
 int wb_conv3_dgrad(WbBackend* b, const WbConv3& g, const float* const dy3[3], const float* wt, float* dx);
 
 // Tensor cores first, CUDA-core tiles otherwise (dense.cu).

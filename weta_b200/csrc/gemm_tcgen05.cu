@@ -202,7 +202,7 @@ bool pair_mode(int m, int BN) {
 // Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
 // the persistent kernel, split-K finish.  `args` arrives with its tensor maps, k_blocks and mode fields set.
 int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_t grid_batch, int BN, bool pair, bool amn, bool bmn,
-              const tc::Epilogue& ep, int force_splits, bool two_blocks = false, bool shared_taps = false) {
+              const tc::Epilogue& ep, int force_splits, bool two_blocks = false, bool shared_taps = false, bool three_blocks = false) {
     args.m = m;
     args.n = n;
     args.error_flag = st->error_flag;
@@ -251,6 +251,9 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
         // Shared memory: a 192 KB ring (6 x 32 KB per CTA of a pair, 4 x 48 KB for BN = 256, 5 x 32 KB for BN = 128)
         // + 32 KB epilogue staging; one persistent CTA per SM.
         if (status != WB_OK) {
+        } else if (three_blocks) {
+            // conv_mode 3: three row blocks (kernel columns) per 128 x 128 tile, 3 x 64 KB ring
+            status = launch_tc<128, 3, false, true, 1, 8, 3>(be, st, args, grid);
         } else if (shared_taps && !pair && splits == 1 && BN == 256 && !amn && bmn) {
             // Implicit convolution on 16-pixel-wide images, 128-row tiles: the taps of a kernel column share their pixel
             // copies (a fifth fewer operand bytes through L2; the input gradient of the 128 -> 256 channel layer went
@@ -386,22 +389,42 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
 //   mode 1: D[batch][m][h*w] = Wr[m][tap][ch] (x) windows(img) (+ epilogue).  Forward with Wr = weights as [O][tap][C];
 //           input gradient with img = dY and Wr = weights as [C][flipped tap][O].
 //   mode 2: D[tap][ch][m] = sum over images and pixels of window_tap(img)[ch][px] * a[img][m][px]  (the weight gradient, a = dY).
+//   mode 3: mode 1's result from img[1] alone (img[0], img[2] unused): the input gradient without shifted copies of dY.
 // Requirements (else WB_ERR_UNSUPPORTED, no message): w and h*w multiples of 4, ch a multiple of 32 (mode 1)
 // or of 128 (mode 2), 16-byte aligned pointers.
+// conv_mode 3 needs image rows that tile the accumulator's 32-column chunks and 128-pixel tiles that end on row ends.
+bool wb_tc_conv_mode3_ok(int64_t ch, int64_t h, int64_t w, int64_t m) {
+    static const bool off = [] { const char* e = std::getenv("WETA_B200_SHIFTED_DGRAD"); return e && e[0] == '1'; }();
+    return !off && (w == 4 || w == 8 || w == 16 || w == 32) && (h * w) % 128 == 0 && ch % 32 == 0 && m > 0;
+}
+
 int wb_tc_conv_gemm(WbBackend* be, int mode, const float* a, const float* const img[3], int64_t batch, int64_t ch, int64_t h, int64_t w, int m,
                     tc::Epilogue ep) {
     const int64_t hw = h * w;
     if (w % 4 != 0 || hw % 4 != 0 || hw >= (int64_t(1) << 30)) return WB_ERR_UNSUPPORTED;
-    if (mode == 1 ? ch % 32 != 0 : ch % 128 != 0) return WB_ERR_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(img[0]) & 15) || (reinterpret_cast<uintptr_t>(img[1]) & 15) ||
-        (reinterpret_cast<uintptr_t>(img[2]) & 15))
-        return WB_ERR_UNSUPPORTED;
+    if (mode == 2 ? ch % 128 != 0 : ch % 32 != 0) return WB_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(img[1]) & 15)) return WB_ERR_UNSUPPORTED;
+    if (mode != 3 && ((reinterpret_cast<uintptr_t>(img[0]) & 15) || (reinterpret_cast<uintptr_t>(img[2]) & 15))) return WB_ERR_UNSUPPORTED;
     GemmState* st = nullptr;
     WB_TRY(get_state(be, &st));
     tc::Args args{};
     args.num_segments = 1;
     args.conv_mode = mode;
     args.conv_w = static_cast<int>(w);
+    if (mode == 3) {
+        // Input gradient from the unshifted gradient tensor alone (img[1]); see tc::Args::conv_mode.
+        if (!wb_tc_conv_mode3_ok(ch, h, w, m) || ep.bias_m || ep.bias_n || ep.row_stats || ep.relu || ep.accumulate) return WB_ERR_UNSUPPORTED;
+        const int64_t k = 9 * ch;
+        WbGemmOperand A{a, m, k, k, 0, false};
+        WB_TRY(make_map(st, A, 1, tc::BM, &args.seg[0].a));
+        WbGemmOperand B{img[1], hw, ch, hw, ch * hw, true};
+        WB_TRY(make_map(st, B, batch, 128, &args.seg[0].b));
+        args.k_blocks = static_cast<int>(3 * (ch / 32));
+        args.conv_cb = static_cast<int>(ch / 32);
+        args.batched_a = 0;
+        args.batched_b = 1;
+        return run_tiles(be, st, args, m, static_cast<int>(hw), batch, 128, false, false, true, ep, 1, false, false, true);
+    }
     if (mode == 1) {
         const int BN = hw > 128 ? 256 : 128;
         const int64_t k = 9 * ch;

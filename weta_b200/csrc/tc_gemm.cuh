@@ -69,7 +69,13 @@ struct Args {
     //     B chunks are 32 pixels x 32 channels, N-major.
     //   conv_mode 2 (weight gradient): M index = (tap, c): A is one box of BM channels x 32 pixels of the tap's
     //     window (seg[kx].a maps the shifted copies), K-major; B = dY [o][pixels] per image; K index = (image, pixel block).
-    int conv_mode, conv_w, conv_cb;  // conv_cb: 32-channel blocks per tap (mode 1) / BM-channel blocks per tap (mode 2)
+    //   conv_mode 3 (input gradient without shifted copies, MT = 3 kernels): the horizontal move is applied to the
+    //     RESULT instead of the operand.  Row block kx of a tile accumulates P_kx[m][q] = sum over (ky, c) of
+    //     A[m][(ky, kx)][c] * img[c][q + (ky-1)*w] from the unshifted tensor (seg[0].b); the epilogue stores
+    //     P_1[m][q] + P_0[m][q-1] + P_2[m][q+1], dropping the terms that would cross an image row's ends.  The
+    //     neighbours are registers of the same thread: tiles are 128 pixels wide and w divides 32, so a 32-column
+    //     chunk of the accumulator never ends inside an image row.
+    int conv_mode, conv_w, conv_cb;  // conv_cb: 32-channel blocks per tap (modes 1, 3) / BM-channel blocks per tap (mode 2)
     Epilogue ep;
     int64_t split_stride_d;    // distance between split-K partial outputs
     int* error_flag;
@@ -251,11 +257,12 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT, i
 __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using SS = SharedStorage<BN, STAGES, CTAS, EPW, MT, HALO>;
-    static_assert(MT == 1 || (CTAS == 1 && BN == 256), "two row blocks per CTA: single CTAs with 256-wide tiles");
+    static_assert(MT == 1 || (MT == 2 && CTAS == 1 && BN == 256) || (MT == 3 && CTAS == 1 && BN == 128 && B_MN && !A_MN && HALO == 0),
+                  "two row blocks per CTA: single CTAs with 256-wide tiles; three (conv_mode 3): 128-wide tiles");
     static_assert(HALO == 0 || (MT == 1 && B_MN && !A_MN && STAGES >= 3), "shared tap windows: implicit convolution tiles only");
     SS& ss = *reinterpret_cast<SS*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr int B_ROWS = BN / CTAS;   // B rows this CTA loads
-    constexpr int TILE_M = BM * CTAS * MT;   // output rows per tile
+    constexpr int TILE_M = MT == 3 ? BM : BM * CTAS * MT;   // output rows per tile (the three blocks of conv_mode 3 are the same rows)
     constexpr int NACC = 512 / BN;      // accumulators in TMEM (all 512 columns), used round-robin: 2 or 4 tiles in flight
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -328,7 +335,7 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 }
             };
             // Row blocks of the tile that hold rows of the matrix (the last tile of an odd block count has one).
-            auto blocks_of = [&](const Cursor& c) { return (MT == 2 && c.m0 + BM < args.m) ? 2 : 1; };
+            auto blocks_of = [&](const Cursor& c) { return MT == 3 ? 3 : ((MT == 2 && c.m0 + BM < args.m) ? 2 : 1); };
             // One K block of operands into ring slot s.
             auto issue = [&](const int s, const Cursor& c) {
                 const CUtensorMap* ma = &args.seg[c.sg].a;
@@ -348,7 +355,15 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 const int kz = args.kpb > 0 ? kb / args.kpb : 0;
                 const int za = args.kpb > 0 ? kz : (args.batched_a ? batch : 0);
                 const int zb = args.kpb > 0 ? kz : (args.batched_b ? batch : 0);
-                if constexpr (HALO == 1) {
+                if constexpr (MT == 3) {
+                    // kb = channel block * 3 + ky; the three kernel columns are the three row blocks
+                    const int cb = kb / 3, ky = kb - cb * 3;
+#pragma unroll
+                    for (int kx = 0; kx < 3; ++kx) copy(&ss.a[s][kx * BM * BK], ma, ((ky * 3 + kx) * args.conv_cb + cb) * BK, m0, 0);
+                    const int x0 = n0 + (ky - 1) * args.conv_w;
+#pragma unroll
+                    for (int ch = 0; ch < B_ROWS / 32; ++ch) copy(&ss.b[s][ch * 32 * BK], mb, x0 + ch * 32, cb * 32, batch);
+                } else if constexpr (HALO == 1) {
                     // kb = (channel block * 3 + kx) * 3 + r; r = 0: middle tap (ky = 1) with its own pixels, r = 1: upper
                     // tap (ky = 0) with the long copy that starts one image row early, r = 2: lower tap (ky = 2), weights only.
                     const int cb = kb / 9, j = kb - cb * 9;
@@ -436,9 +451,9 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
                 int m0, n0, batch, split, kb_begin, kb_end;
                 decode(t, m0, n0, batch, split, kb_begin, kb_end);
                 // MT == 1: the tiles take the accumulators in turn.  MT == 2: row block `sub` of every tile uses accumulator `sub`.
-                const int acc = MT == 2 ? 0 : tile_iter % NACC;
-                const uint32_t use = static_cast<uint32_t>(MT == 2 ? tile_iter : tile_iter / NACC);
-                const int nsub = (MT == 2 && m0 + BM < args.m) ? 2 : 1;  // row blocks that hold rows of the matrix
+                const int acc = MT >= 2 ? 0 : tile_iter % NACC;
+                const uint32_t use = static_cast<uint32_t>(MT >= 2 ? tile_iter : tile_iter / NACC);
+                const int nsub = MT == 3 ? 3 : ((MT == 2 && m0 + BM < args.m) ? 2 : 1);  // row blocks that hold rows of the matrix
                 // Wait until the epilogue has drained the accumulator(s) (passes at once on first use).
                 if (!mbar_wait(&ss.tmem_empty[acc], (use & 1) ^ 1)) { ok = false; break; }
                 if (MT == 2 && !mbar_wait(&ss.tmem_empty[1], (use & 1) ^ 1)) { ok = false; break; }
@@ -509,6 +524,71 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
             int tile_m0, n0, batch, split, kb_begin, kb_end;
             decode(t, tile_m0, n0, batch, split, kb_begin, kb_end);
+          if constexpr (MT == 3) {
+            // conv_mode 3: the tile's three accumulators (kernel columns 0, 1, 2 at TMEM columns 0, BN, 2 * BN) are read
+            // together and combined with a move of one pixel each way; plain stores only (no bias, no statistics).
+            if (!mbar_wait(&ss.tmem_full[0], static_cast<uint32_t>(tile_iter) & 1)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int cbase = half * HALF_N;
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(cbase) + (static_cast<uint32_t>(lg * 32) << 16);
+            float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d;
+            const int wmask = args.conv_w - 1;  // w is a power of two that divides 32
+            const bool fast = vec_ok && tile_m0 + lg * 32 + 32 <= args.m && n0 + cbase + HALF_N <= args.n;
+#pragma unroll 1
+            for (int c = 0; c < HALF_N; c += 32) {
+                const int col0 = n0 + cbase + c;
+                uint32_t r0[32], r1[32], r2[32];
+                tmem_ld32_issue(tmem_d + c, r0);
+                tmem_ld32_issue(tmem_d + BN + c, r1);
+                tmem_ld32_issue(tmem_d + 2 * BN + c, r2);
+                tmem_ld_wait();
+                if (c + 32 >= HALF_N) {
+                    // Last TMEM read of this warp for the tile: hand the accumulators back before the stores.
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ss.tmem_empty[0]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float v[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = 4 * i + e, x = j & wmask;  // column c + j starts a chunk-aligned run: its x is j mod w
+                        float acc = __uint_as_float(r1[j]);
+                        if (j > 0 && x != 0) acc += __uint_as_float(r0[j > 0 ? j - 1 : 0]);
+                        if (j < 31 && x != wmask) acc += __uint_as_float(r2[j < 31 ? j + 1 : 31]);
+                        v[e] = acc;
+                    }
+                    *reinterpret_cast<float4*>(stage + lane * 32 + ((i ^ sw) << 2)) = make_float4(v[0], v[1], v[2], v[3]);
+                }
+                __syncwarp();
+                if (col0 < args.n) {
+                    const int rsub = lane >> 3, cc = lane & 7;
+                    if (fast) {
+                        float* p = out_base + static_cast<int64_t>(tile_m0 + lg * 32 + rsub) * args.ep.ldd + col0 + cc * 4;
+                        const int64_t step = static_cast<int64_t>(args.ep.ldd) * 4;
+#pragma unroll
+                        for (int it8 = 0; it8 < 8; ++it8) {
+                            const int r = it8 * 4 + rsub;
+                            *reinterpret_cast<float4*>(p + it8 * step) = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int it8 = 0; it8 < 8; ++it8) {
+                            const int r = it8 * 4 + rsub;
+                            const int grow = tile_m0 + lg * 32 + r, gcol = col0 + cc * 4;
+                            if (grow < args.m && gcol < args.n) {
+                                const float4 val = *reinterpret_cast<const float4*>(stage + r * 32 + ((cc ^ (r & 7)) << 2));
+                                float* p = out_base + static_cast<int64_t>(grow) * args.ep.ldd + gcol;
+                                const float e4[4] = {val.x, val.y, val.z, val.w};
+                                for (int j = 0; j < 4 && gcol + j < args.n; ++j) p[j] = e4[j];
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+          } else
           for (int sub = 0; sub < MT && ok; ++sub) {
             const int m0 = tile_m0 + rank * BM + sub * BM;  // this CTA's (this row block's) rows of the tile
             const int acc = MT == 2 ? sub : tile_iter % NACC;

@@ -58,6 +58,7 @@ struct Layer {
     bool implicit = false;
     bool x_shift_fused = false;   // the previous block's BN/ReLU/pool pass writes x_shift
     bool dy_shift_fused = false;  // this block's BN/ReLU/pool backward writes the trainer's dy_shift
+    bool dgrad_plain = false;     // the input gradient reads dY alone (no shifted copies are made)
     float* x_shift[2] = {nullptr, nullptr};
     float *w_fwd = nullptr, *w_dgrad = nullptr, *dw_taps = nullptr;
     double* stat_sums = nullptr;  // [cout][2]: sum and sum of squares of conv_out, accumulated by the convolution's epilogue
@@ -345,7 +346,8 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
                 A(dev_alloc_t(t, batch * L.cin * hw, &L.x_shift[1]));
                 A(dev_alloc_t(t, wn, &L.w_fwd));
                 A(dev_alloc_t(t, wn, &L.dw_taps));
-                L.dy_shift_fused = !first_conv && L.w % 4 == 0 && 32 % (L.w / 4) == 0;
+                L.dgrad_plain = !first_conv && wb_conv3_dgrad_needs_no_copies(WbConv3{batch, L.cin, L.h, L.w, L.cout});
+                L.dy_shift_fused = !first_conv && !L.dgrad_plain && L.w % 4 == 0 && 32 % (L.w / 4) == 0;
                 {
                     // input = the pooled output of a conv block directly before this one, whose width is 2 * L.w
                     const size_t li = static_cast<size_t>(&L - t->layers.data());
@@ -353,7 +355,7 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
                 }
                 if (!first_conv) {
                     A(dev_alloc_t(t, wn, &L.w_dgrad));
-                    max_dy_shift = std::max(max_dy_shift, batch * L.cout * hw);
+                    if (!L.dgrad_plain) max_dy_shift = std::max(max_dy_shift, batch * L.cout * hw);
                 }
             } else {
                 A(dev_alloc_t(t, batch * L.cin * 9 * hw, &L.cols));
@@ -689,13 +691,13 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
                 const float* x3[3] = {L.x_shift[0], in_act, L.x_shift[1]};
                 { OpTimer tm(t, i, "conv_wgrad_gemm"); WB_TRY(wb_conv3_wgrad(b, geo, dconv, x3, L.dw_taps, t->grad + L.off_w)); }
                 if (need_dx) {
-                    if (!L.dy_shift_fused) {
+                    if (!L.dy_shift_fused && !L.dgrad_plain) {
                         OpTimer tm(t, i, "conv_shift_dy");
                         WB_TRY(wb_conv3_shift_copies(b, dconv, B * L.cout * L.h, L.w, t->dy_shift[0], t->dy_shift[1]));
                     }
                     float* dx = t->gbuf[pp];
                     pp ^= 1;
-                    const float* d3[3] = {t->dy_shift[0], dconv, t->dy_shift[1]};
+                    const float* d3[3] = {L.dgrad_plain ? nullptr : t->dy_shift[0], dconv, L.dgrad_plain ? nullptr : t->dy_shift[1]};
                     { OpTimer tm(t, i, "conv_dgrad_gemm"); WB_TRY(wb_conv3_dgrad(b, geo, d3, L.w_dgrad, dx)); }
                     g = dx;
                 }
