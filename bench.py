@@ -324,7 +324,9 @@ def main():
     work = {  # per launch, per rank: ("tensor", algorithmic 2*M*N*K flops) or ("hbm", algorithmic bytes moved)
         # conv1 contracts over 27 values per output: its two GEMMs are bound by writing / reading the 128-channel
         # activation (act1) plus the 27-row im2col matrix (9 x the input), not by the tensor cores
-        "L0.conv_fwd_gemm": ("hbm", act1 + 9.0 * in1), "L0.conv_wgrad_gemm": ("hbm", act1 + 9.0 * in1),
+        # conv1's weight gradient is fused with the block's BatchNorm+ReLU+pool backward: it reads the activation, the
+        # pooled gradient and the im2col matrix and writes nothing of that size
+        "L0.conv_fwd_gemm": ("hbm", act1 + 9.0 * in1), "L0.conv_wgrad_gemm": ("hbm", act1 * 1.25 + 9.0 * in1),
         "L1.conv_fwd_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2), "L1.conv_wgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
         "L1.conv_dgrad_gemm": ("tensor", 2.0 * batch * cfg.c2 * cfg.c1 * 9 * hw2),
         "L3.linear_fwd_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in), "L3.linear_wgrad_gemm": ("tensor", 2.0 * batch * cfg.hidden * fc_in),
@@ -337,7 +339,8 @@ def main():
         # Backward: the sums pass reads the pooled output and the pooled gradient (x/4 each), the dx pass reads x and
         # dy/4 and writes dx (no shifted copies of dx: block 1's input gradient applies the horizontal moves to its result).
         "L0.bn_relu_pool_fwd": ("hbm", act1 * 1.75), "L1.bn_relu_pool_fwd": ("hbm", act2 * 1.25),
-        "L0.bn_relu_pool_bwd": ("hbm", act1 * 2.75), "L1.bn_relu_pool_bwd": ("hbm", act2 * 2.75),
+        # (block 0: only the sums pass is left under this label; its dx pass lives in L0.conv_wgrad_gemm)
+        "L0.bn_relu_pool_bwd": ("hbm", act1 * 0.5), "L1.bn_relu_pool_bwd": ("hbm", act2 * 2.75),
         "L2.dropout_fwd": ("hbm", 8.0 * batch * fc_in), "L2.dropout_bwd": ("hbm", 8.0 * batch * fc_in),
         "L4.dropout_fwd": ("hbm", 8.0 * batch * cfg.hidden), "L4.dropout_bwd": ("hbm", 12.0 * batch * cfg.hidden),
         "L6.adam": ("hbm", 28.0 * tr.arena_len),

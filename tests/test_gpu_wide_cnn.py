@@ -253,3 +253,49 @@ def test_batch_norm_backward_sums_with_unusable_gamma(oracle, gpu, report):
     for n, e in errs.items():
         assert e < 2e-3, (n, e)
     tr.close()
+
+
+def test_first_block_backward_fused_with_its_weight_gradient(gpu, report):
+    """The first block's BatchNorm+ReLU+pool backward and the convolution's weight gradient as one kernel (the output
+    gradient never reaches memory) against the same trainer with the two stand-alone ops: the dconv values are computed
+    with the same arithmetic and reach the tensor core as the same TF32 operands, so only the order of the f32
+    accumulation differs.  Every other gradient is bit-identical."""
+    import os
+
+    cfg, batch = WIDE_CNN, 48  # 48 images x 16 row pairs = 768 steps over 148 CTAs: unequal ranges, some of five steps, some of six
+    rng = np.random.default_rng(3)
+    x = rng.random((batch, cfg.in_ch, cfg.hw, cfg.hw), dtype=np.float32)
+    y = rng.integers(0, cfg.classes, batch).astype(np.int64)
+    gamma = (1.0 + 0.3 * rng.standard_normal(cfg.c1)).astype(np.float32)
+    beta = (0.2 * rng.standard_normal(cfg.c1)).astype(np.float32)
+    grads = {}
+    for fused in (False, True):
+        os.environ["WETA_B200_NO_FUSED_CONV1_BWD"] = "0" if fused else "1"
+        try:
+            manual_seed(11)
+            tr = FusedTrainer(gpu, cnn_specs(cfg), batch, (cfg.in_ch, cfg.hw, cfg.hw), lr=1e-3, matmul_mode=TF32)
+            tr.init_from_global_rng()
+            # BatchNorm parameters away from their initial 1 / 0, so every term of dx is exercised
+            tr.set_param(2, gamma)
+            tr.set_param(3, beta)
+            tr.stage(x, y)
+            manual_seed(5)
+            tr.forward_backward()
+            gpu.gemm_check()
+            grads[fused] = [tr.get_grad(i) for i in range(len(tr.ranges))]
+            loss = tr.loss()
+            grads[("loss", fused)] = loss
+            tr.close()
+        finally:
+            os.environ.pop("WETA_B200_NO_FUSED_CONV1_BWD", None)
+    assert grads[("loss", True)] == grads[("loss", False)]
+    a, b = grads[False], grads[True]
+    dw_err = float(np.linalg.norm(a[0] - b[0]) / np.linalg.norm(a[0]))
+    # the bias gradient of a convolution followed by BatchNorm is rounding noise around zero: compare on the scale of
+    # the sum of |dconv| it is the residue of, which the weight gradient's magnitude stands for
+    db_err = float(np.abs(a[1] - b[1]).max() / max(float(np.abs(a[0]).max()), 1e-30))
+    report("first-block fused backward", dw_rel_l2=dw_err, dbias_abs_over_dw_max=db_err)
+    assert dw_err < 2e-6, dw_err
+    assert db_err < 1e-4, db_err
+    for i in range(2, len(a)):
+        assert np.array_equal(a[i], b[i]), i

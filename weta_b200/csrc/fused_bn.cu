@@ -946,11 +946,13 @@ extern "C" int wb_bn_relu_pool_fwd(WbBackend* b, const float* x, int64_t n, int6
 
 // Backward of BatchNorm2d -> ReLU -> MaxPool2d(2); dx_left / dx_right (both or neither) also receive dx shifted one
 // column right / left, zeros shifted in (needs w / 4 in {1, 2, 4, ..., 32} and 16-byte aligned buffers).
+// dx == nullptr: only dgamma and dbeta are computed (the caller produces dx itself, see conv1_bwd_fused.cu).
 int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                 const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                                 float* dgamma, float* dbeta, float* dbias_conv, float* dx_left, float* dx_right, const float* y_pooled) {
-    WB_REQUIRE(b && x && dy_pooled && dx && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
+    WB_REQUIRE(b && x && dy_pooled && dgamma && dbeta, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
     WB_REQUIRE(h % 2 == 0 && w % 2 == 0, WB_ERR_UNSUPPORTED, "wb_bn_relu_pool_bwd: height and width must be even");
+    WB_REQUIRE(dx || (!dx_left && !dbias_conv), WB_ERR_INVALID, "wb_bn_relu_pool_bwd: outputs of the dx pass asked for without dx");
     WB_REQUIRE((dx_left == nullptr) == (dx_right == nullptr), WB_ERR_INVALID, "wb_bn_relu_pool_bwd: give both shifted outputs or neither");
     WbProfileScope ps(b, "bn_relu_pool_bwd");
     const bool pairs = w % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dx_left) |
@@ -1003,6 +1005,7 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     WB_LAUNCH_OK(b);
     bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
+    if (!dx) return WB_OK;
     if (pairs && dx_left)
         bn_relu_pool_bwd_pair_kernel<true, true><<<flat_blocks, THREADS, 0, b->stream>>>(
             dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
@@ -1026,6 +1029,7 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
 extern "C" int wb_bn_relu_pool_bwd(WbBackend* b, const float* x, const float* dy_pooled, int64_t n, int64_t c, int64_t h, int64_t w,
                                    const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, float* dx,
                                    float* dgamma, float* dbeta, float* dbias_conv) {
+    WB_REQUIRE(dx, WB_ERR_INVALID, "wb_bn_relu_pool_bwd: null pointer");
     return wb_bn_relu_pool_bwd_shifted(b, x, dy_pooled, n, c, h, w, gamma, beta, save_mean, save_rstd, dx, dgamma, dbeta, dbias_conv, nullptr,
                                        nullptr, nullptr);
 }

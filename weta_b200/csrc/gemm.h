@@ -38,6 +38,18 @@ int wb_conv3_wgrad(WbBackend* b, const WbConv3& g, const float* dy, const float*
 bool wb_conv3_dgrad_needs_no_copies(const WbConv3& g);
 int wb_conv3_dgrad(WbBackend* b, const WbConv3& g, const float* const dy3[3], const float* wt, float* dx);
 
+// Tensor-map and error-flag access for tensor-core kernels outside gemm_tcgen05.cu.
+int wb_tc_encode(WbBackend* be, const float* ptr, const uint64_t dims[3], const uint64_t strides[2], const uint32_t box[3], bool swizzle128,
+                 CUtensorMap* map);
+int wb_tc_error_flag(WbBackend* be, int** flag);
+
+// BatchNorm+ReLU+pool backward of the first convolution block fused with that convolution's weight gradient
+// (conv1_bwd_fused.cu): dconv is never written.  `cols` is the block's im2col matrix [n][ck][h*w].
+bool wb_conv1_bwd_fused_ok(int64_t n, int64_t cout, int64_t h, int64_t w, int64_t ck, const float* x, const float* dy_pooled, const float* cols);
+int wb_conv1_bwd_fused(WbBackend* b, const float* x, const float* dy_pooled, const float* cols, int64_t n, int64_t h, int64_t w, int64_t ck,
+                       const float* gamma, const float* beta, const float* save_mean, const float* save_rstd, const float* dgamma,
+                       const float* dbeta, float* dweight, float* dbias_conv);
+
 // Tensor cores first, CUDA-core tiles otherwise (dense.cu).
 int wb_gemm_dispatch(WbBackend* be, int mode, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, int n, int k, tc::Epilogue ep,
                      int64_t span_batch, bool* used_tc);

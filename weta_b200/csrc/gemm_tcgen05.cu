@@ -305,6 +305,34 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
 
 }  // namespace
 
+// A 3-D tensor map of f32 elements for kernels outside this file (conv1_bwd_fused.cu): dims / box innermost first,
+// strides in bytes for dimensions 1 and 2; 128-byte swizzle (K-major operand tiles) or none.
+int wb_tc_encode(WbBackend* be, const float* ptr, const uint64_t dims[3], const uint64_t strides[2], const uint32_t box[3], bool swizzle128,
+                 CUtensorMap* map) {
+    GemmState* st = nullptr;
+    WB_TRY(get_state(be, &st));
+    cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
+    cuuint64_t sb[2] = {strides[0], strides[1]};
+    cuuint32_t bx[3] = {box[0], box[1], box[2]};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(ptr), d, sb, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        wb_set_error("cuTensorMapEncodeTiled failed with %d", static_cast<int>(r));
+        return WB_ERR_CUDA;
+    }
+    return WB_OK;
+}
+
+// The device flag the tensor-core kernels raise when a bounded wait runs out (read by wb_gemm_check).
+int wb_tc_error_flag(WbBackend* be, int** flag) {
+    GemmState* st = nullptr;
+    WB_TRY(get_state(be, &st));
+    *flag = st->error_flag;
+    return WB_OK;
+}
+
 // Runs D = A x B (+ epilogue) on the tensor cores.  mode: WB_MM_TF32 or WB_MM_TF32X3.
 // Returns WB_ERR_UNSUPPORTED (without setting an error message) if an operand cannot be read by TMA.
 // span_batch > 0: A and B are batched K-major operands of `span_batch` images and the contraction

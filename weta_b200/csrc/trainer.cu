@@ -674,6 +674,25 @@ extern "C" int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout
             g = dx;
         } else {
             const int64_t hw = static_cast<int64_t>(L.h) * L.w, ck = static_cast<int64_t>(L.cin) * 9;
+            // First block, 27-value contraction: its output gradient has no consumer but the weight and bias gradients,
+            // which one kernel computes from the pieces of it that it builds in shared memory (conv1_bwd_fused.cu).
+            if (!need_dx && !L.implicit && t->matmul_mode == WB_MM_TF32 &&
+                wb_conv1_bwd_fused_ok(B, L.cout, L.h, L.w, ck, L.conv_out, g, L.cols)) {
+                {
+                    OpTimer tm(t, i, "bn_relu_pool_bwd");
+                    WB_TRY(wb_bn_relu_pool_bwd_shifted(b, L.conv_out, g, B, L.cout, L.h, L.w, t->theta + L.off_gamma, t->theta + L.off_beta,
+                                                       L.save_mean, L.save_rstd, nullptr, t->grad + L.off_gamma, t->grad + L.off_beta, nullptr, nullptr,
+                                                       nullptr, L.out_act));
+                }
+                if (t->cb) t->cb(t->cb_user, nullptr, 0);
+                {
+                    OpTimer tm(t, i, "conv_wgrad_gemm");
+                    WB_TRY(wb_conv1_bwd_fused(b, L.conv_out, g, L.cols, B, L.h, L.w, ck, t->theta + L.off_gamma, t->theta + L.off_beta, L.save_mean,
+                                              L.save_rstd, t->grad + L.off_gamma, t->grad + L.off_beta, t->grad + L.off_w, t->grad + L.off_b));
+                }
+                if (t->cb && L.range_len > 0) t->cb(t->cb_user, t->grad + L.range_begin, L.range_len);
+                continue;
+            }
             float* dconv = t->gbuf[pp];
             pp ^= 1;
             {
