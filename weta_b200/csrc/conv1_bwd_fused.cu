@@ -11,7 +11,7 @@
 //
 //   warp 0      TMA: per step (one image, two image rows = 64 pixels) the conv output x [128][64], the pooled
 //               gradient [128][16] and two im2col boxes [32][32] into a ring of three slots
-//   warps 2-9   the BatchNorm+ReLU+pool backward of wb_bn_relu_pool_bwd (fused_bn.cu), same arithmetic, one 2x2 window
+//   warps 2-17  the BatchNorm+ReLU+pool backward of wb_bn_relu_pool_bwd (fused_bn.cu), same arithmetic, one 2x2 window
 //               per thread and round, from the slot into two K-major 128 x 32 operand tiles (128-byte swizzle, written
 //               with the same chunk permutation TMA gave the x boxes), then a proxy fence and an mbarrier arrival
 //   warp 1      tcgen05.mma kind::tf32, M = 128 channels, N = 32 im2col rows (27 used), K = 32 pixels per tile, into
@@ -28,7 +28,7 @@
 
 namespace {
 
-constexpr int TW = 8;                       // transform warps
+constexpr int TW = 16;                      // transform warps: eight channels each
 constexpr int THREADS = 64 + 32 * TW;
 constexpr int RAW = 3, AST = 2;             // ring depths: loaded slots, operand-tile slots
 constexpr int CH = 128, PXT = 32, NK = 32;  // channels (M), pixels per operand tile (K), im2col rows per tile (N)
@@ -139,10 +139,19 @@ __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __gri
         // ---- transform warps: dconv of the step's 128 x 64 piece into the operand tiles ---------------------
         const int tw = warp - 2;
         const int l = lane & 15, hi = lane >> 4;
-        float bias_acc[8];
-        double bias_sum[8];
+        constexpr int IT = CH / (2 * TW);  // rounds per step: two channels per warp and round
+        // this thread's channels never change: their constants live in registers
+        float cm[IT], cr[IT], cg[IT], cb[IT], cnk1[IT], cnk2[IT], cgr[IT];
+        float bias_acc[IT];
+        double bias_sum[IT];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { bias_acc[i] = 0.f; bias_sum[i] = 0.0; }
+        for (int i = 0; i < IT; ++i) {
+            const int c = 2 * IT * tw + 2 * i + hi;
+            cm[i] = ss.consts[c][0]; cr[i] = ss.consts[c][1]; cg[i] = ss.consts[c][2]; cb[i] = ss.consts[c][3];
+            cnk1[i] = ss.consts[c][4]; cnk2[i] = ss.consts[c][5]; cgr[i] = ss.consts[c][6];
+            bias_acc[i] = 0.f;
+            bias_sum[i] = 0.0;
+        }
         for (int it = 0; it < my_steps && ok; ++it) {
             const int s = it % RAW, a = it % AST;
             if (!tc::mbar_wait(&ss.raw_full[s], (it / RAW) & 1)) { ok = false; break; }
@@ -153,15 +162,14 @@ __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __gri
             float* a0 = &ss.a[a][0][0];
             float* a1 = &ss.a[a][1][0];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int c = 16 * tw + 2 * i + hi;
+            for (int i = 0; i < IT; ++i) {
+                const int c = 2 * IT * tw + 2 * i + hi;
                 // pixels 2l, 2l + 1 of the channel's 128-byte row: 16-byte chunk l / 2 sits at chunk (l / 2) ^ (c & 7)
                 const int off = c * PXT + ((((l >> 1) ^ (c & 7)) << 2) | ((l & 1) << 1));
                 const float2 r0 = *reinterpret_cast<const float2*>(x0 + off);
                 const float2 r1 = *reinterpret_cast<const float2*>(x1 + off);
                 const float gy = gs[c * 16 + l];
-                const float m = ss.consts[c][0], r = ss.consts[c][1], g = ss.consts[c][2], b = ss.consts[c][3];
-                const float negk1 = ss.consts[c][4], negk2 = ss.consts[c][5], gr = ss.consts[c][6];
+                const float m = cm[i], r = cr[i], g = cg[i], b = cb[i], negk1 = cnk1[i], negk2 = cnk2[i], gr = cgr[i];
                 const float v[4] = {r0.x, r0.y, r1.x, r1.y};
                 float xh[4], act[4];
 #pragma unroll
@@ -186,7 +194,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __gri
             }
             if ((it & 31) == 31) {  // keep the f32 partial sums short
 #pragma unroll
-                for (int i = 0; i < 8; ++i) { bias_sum[i] += static_cast<double>(bias_acc[i]); bias_acc[i] = 0.f; }
+                for (int i = 0; i < IT; ++i) { bias_sum[i] += static_cast<double>(bias_acc[i]); bias_acc[i] = 0.f; }
             }
             // the tiles were written through the generic proxy; the tensor core reads them through the async proxy
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -198,11 +206,11 @@ __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __gri
         }
         // bias partials: the 16 lanes of a half-warp hold the 16 windows of one channel's row pair
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < IT; ++i) {
             double t = bias_sum[i] + static_cast<double>(bias_acc[i]);
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) t += __shfl_down_sync(0xffffffffu, t, o, 16);
-            if (l == 0) args.bias_part[static_cast<int64_t>(blockIdx.x) * CH + 16 * tw + 2 * i + hi] = t;
+            if (l == 0) args.bias_part[static_cast<int64_t>(blockIdx.x) * CH + 2 * IT * tw + 2 * i + hi] = t;
         }
         // ---- the accumulator: four of the warps read 32 lanes each ------------------------------------------
         if (tw < 4) {
