@@ -255,14 +255,15 @@ def test_batch_norm_backward_sums_with_unusable_gamma(oracle, gpu, report):
     tr.close()
 
 
-def test_first_block_backward_fused_with_its_weight_gradient(gpu, report):
+@pytest.mark.parametrize("batch", [48, 512])
+def test_first_block_backward_fused_with_its_weight_gradient(gpu, report, batch):
     """The first block's BatchNorm+ReLU+pool backward and the convolution's weight gradient as one kernel (the output
     gradient never reaches memory) against the same trainer with the two stand-alone ops: the dconv values are computed
     with the same arithmetic and reach the tensor core as the same TF32 operands, so only the order of the f32
     accumulation differs.  Every other gradient is bit-identical."""
     import os
 
-    cfg, batch = WIDE_CNN, 48  # 48 images x 16 row pairs = 768 steps over 148 CTAs: unequal ranges, some of five steps, some of six
+    cfg = WIDE_CNN  # 48 images x 16 row pairs = 768 steps over 148 CTAs: unequal ranges, some of five steps, some of six; 512: the 8-GPU rank
     rng = np.random.default_rng(3)
     x = rng.random((batch, cfg.in_ch, cfg.hw, cfg.hw), dtype=np.float32)
     y = rng.integers(0, cfg.classes, batch).astype(np.int64)
@@ -294,8 +295,11 @@ def test_first_block_backward_fused_with_its_weight_gradient(gpu, report):
     # the bias gradient of a convolution followed by BatchNorm is rounding noise around zero: compare on the scale of
     # the sum of |dconv| it is the residue of, which the weight gradient's magnitude stands for
     db_err = float(np.abs(a[1] - b[1]).max() / max(float(np.abs(a[0]).max()), 1e-30))
-    report("first-block fused backward", dw_rel_l2=dw_err, dbias_abs_over_dw_max=db_err)
-    assert dw_err < 2e-6, dw_err
+    report(f"first-block fused backward, batch {batch}", dw_rel_l2=dw_err, dbias_abs_over_dw_max=db_err)
+    # 1.7e-6 at batch 48, 1.4e-5 at batch 512 (measured): the two paths split the contraction over images and pixels into
+    # different partial sums, and the tensor core adds into its f32 accumulator with truncation (about 2^-24 of the
+    # running sum per product), so the difference grows with the length of the contraction
+    assert dw_err < (5e-6 if batch <= 64 else 5e-5), dw_err
     assert db_err < 1e-4, db_err
     for i in range(2, len(a)):
         assert np.array_equal(a[i], b[i]), i
