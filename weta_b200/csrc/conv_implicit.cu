@@ -10,7 +10,8 @@
 // The tensor-core kernel fetches a tap's window as the image's own pixel run moved by whole rows; the
 // move by one column cannot be a TMA start address (4-byte granularity), so the image is kept in three
 // copies: itself, shifted right (left[y][x] = image[y][x-1]) and shifted left (right[y][x] = image[y][x+1]),
-// zeros shifted in.
+// zeros shifted in.  (The input gradient of layers that pass wb_conv3_dgrad_needs_no_copies applies the column
+// move to its result instead and reads dY alone.)
 namespace {
 
 __global__ void __launch_bounds__(256) shift_copies_kernel(const float* __restrict__ in, float* __restrict__ left, float* __restrict__ right,

@@ -86,7 +86,7 @@ struct WbTrainer {
     float* loss_pinned = nullptr;
     float* gbuf[2] = {nullptr, nullptr};  // ping-pong gradient-of-activation buffers
     float* dcols = nullptr;
-    float* dy_shift[2] = {nullptr, nullptr};  // shifted copies of a conv block's output gradient (implicit input gradient)
+    float* dy_shift[2] = {nullptr, nullptr};  // shifted copies of a conv block's output gradient (implicit input gradient; only for layers that need them)
     int64_t max_act = 0;
     int64_t t = 0;
     WbAdamConfig adam{};
