@@ -272,9 +272,12 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             else if (amn && !bmn) status = launch_tc<256, 3, true, false, 1, 8, 2>(be, st, args, grid);
             else status = launch_tc<256, 3, true, true, 1, 8, 2>(be, st, args, grid);
         } else if (BN == 256 && args.k_blocks * args.num_segments <= 2 && !amn) {
-            // One or two K blocks per tile: the epilogue is the whole cost, so it gets 16 warps and the ring 2 stages.
-            if (!bmn) status = launch_tc<256, 2, false, false, 1, 16>(be, st, args, grid);
-            else status = launch_tc<256, 2, false, true, 1, 16>(be, st, args, grid);
+            // One or two K blocks per tile: the epilogue is the whole cost, so it gets 16 warps; a ring of three slots
+            // (conv1 forward at batch 4096: 0.524 ms with two, 0.496 ms with three).  Compiling the common case of the
+            // epilogue (no column bias, no ReLU, vector stores) without its per-value tests made it slower
+            // (0.570 ms: more spills at this variant's 96 registers), so there is one general form.
+            if (!bmn) status = launch_tc<256, 3, false, false, 1, 16>(be, st, args, grid);
+            else status = launch_tc<256, 3, false, true, 1, 16>(be, st, args, grid);
         } else if (BN == 256) {
             if (!amn && !bmn) status = launch_tc<256, 4, false, false, 1>(be, st, args, grid);
             else if (!amn && bmn) status = launch_tc<256, 4, false, true, 1>(be, st, args, grid);
