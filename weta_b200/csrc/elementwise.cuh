@@ -210,40 +210,53 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile(TO* __restrict__ out, co
 // warp covers 8 float4 columns of P by 4 rows of L) and the 128-bit loads of the compute phase are both free of bank
 // conflicts.  Needs every size, stride and offset involved to be a multiple of 4 elements and 16-byte aligned base
 // pointers (checked by the launcher).
-template <class TI, class TO, int NOPS, class F>
+template <class TI, class TO, int NOPS, int DEPTH, class F>
 __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, const TI* __restrict__ a, const TI* __restrict__ b, Plan p,
-                                                         int pd, int tmode_a, int tmode_b, uint32_t tiles_p, uint32_t tiles_l, F f) {
+                                                         int pd, int tmode_a, int tmode_b, uint32_t tiles_p, uint32_t tiles_l, int dd, F f) {
+    constexpr int depth = DEPTH;
     static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "ew_tile4 is for 4-byte elements");
     static_assert(TILE == 64 && TILE_THREADS == 256, "the lane mappings below assume a 64 x 64 tile and 8 warps");
     extern __shared__ __align__(16) unsigned char tile_raw[];
-    TI(*sm)[TILE][TILE] = reinterpret_cast<TI(*)[TILE][TILE]>(tile_raw);  // sm[o][p][swizzled l]
+    TI(*sm)[TILE][TILE] = reinterpret_cast<TI(*)[TILE][TILE]>(tile_raw);  // sm[o * depth + slice][p][swizzled l]
     const int L = p.nd - 1;
     uint32_t bid = blockIdx.x;
     const uint32_t tl = bid % tiles_l;
     bid /= tiles_l;
     const uint32_t tp = bid % tiles_p;
     bid /= tiles_p;
-    int64_t oa = p.off[0], ob = p.off[1], oo = 0, s = p.size[L], ostride_p = 0;
+    // A block owns `depth` consecutive positions ("slices") of dim dd, the dim next to L: all their loads are issued
+    // before any of their stores, so a transposed operand whose dd stride continues its P runs is read in runs `depth`
+    // times as long, and the output (dd is its second-innermost dim) is written in runs `depth` tiles long.
+    int64_t oa = p.off[0], ob = p.off[1], oo = 0, s = p.size[L], ostride_p = 0, ostride_d = 0;
+    int slices = 1;
     for (int d = L - 1; d >= 0; --d) {
         const uint32_t sz = static_cast<uint32_t>(p.size[d]);
         if (d == pd) {
             ostride_p = s;
         } else {
-            const uint32_t q = bid / sz, c = bid - q * sz;
+            const uint32_t szb = d == dd ? (sz + depth - 1) / depth : sz;
+            const uint32_t q = bid / szb;
+            uint32_t c = bid - q * szb;
             bid = q;
+            if (d == dd) {
+                c *= depth;
+                slices = min(depth, static_cast<int>(sz - c));
+                ostride_d = s;
+            }
             oa += c * p.st[0][d];
             if (NOPS > 1) ob += c * p.st[1][d];
             oo += c * s;
         }
         s *= sz;
     }
+    const int64_t sad = dd >= 0 ? p.st[0][dd] : 0, sbd = dd >= 0 ? p.st[1][dd] : 0;
     const int64_t p0 = static_cast<int64_t>(tp) * TILE, l0 = static_cast<int64_t>(tl) * TILE;
     const int64_t szp = p.size[pd], szl = p.size[L];
     const int64_t sap = p.st[0][pd], sal = p.st[0][L], sbp = p.st[1][pd], sbl = p.st[1][L];
     using V4 = Pack<TI, 4>;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // Stage transposed operands: a thread loads 4 consecutive P positions of one L row (the operand's unit-stride dim is P).
-    auto stage = [&](const TI* __restrict__ src, int64_t base, int64_t sl, int o) {
+    auto stage = [&](const TI* __restrict__ src, int64_t base, int64_t sl, int o) {  // o: index of the shared-memory tile
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const int u = k * 8 + warp;                                   // 32 units of 4 L rows x 8 float4 columns
@@ -257,45 +270,63 @@ __global__ void __launch_bounds__(TILE_THREADS) ew_tile4(TO* __restrict__ out, c
             }
         }
     };
-    if (tmode_a) stage(a, oa, sal, 0);
-    if constexpr (NOPS > 1) {
-        if (tmode_b) stage(b, ob, sbl, 1);
+    auto stage_slice = [&](int sl) {
+        if (tmode_a) stage(a, oa + sl * sad, sal, sl);
+        if constexpr (NOPS > 1) {
+            if (tmode_b) stage(b, ob + sl * sbd, sbl, depth + sl);
+        }
+    };
+    if constexpr (DEPTH == 1) {
+        stage_slice(0);
+    } else {
+        // one slice after the other (measured: unrolling the slices into one batch of loads is slower, 0.62 against 0.83)
+#pragma unroll 1
+        for (int sl = 0; sl < slices; ++sl) stage_slice(sl);
     }
     __syncthreads();
     // Compute: a thread produces 4 consecutive L positions of one P row.
+    auto compute_slice = [&](int sl) {
+        const int64_t oas = oa + sl * sad, obs = ob + sl * sbd, oos = oo + sl * ostride_d;
 #pragma unroll
-    for (int k = 0; k < (TILE * TILE / 4) / TILE_THREADS; ++k) {
-        const int idx = threadIdx.x + k * TILE_THREADS;
-        const int pj = idx / (TILE / 4), l4 = idx % (TILE / 4);
-        const int64_t pi = p0 + pj, li = l0 + 4 * l4;
-        if (pi >= szp || li >= szl) continue;
-        const int col = 4 * (l4 ^ ((pj >> 2) & 7));
-        V4 x, y;
-        if (tmode_a) {
-            x = *reinterpret_cast<const V4*>(&sm[0][pj][col]);
-        } else if (sal == 1) {
-            x = *reinterpret_cast<const V4*>(a + oa + pi * sap + li);
-        } else {  // broadcast along L
-            const TI v = a[oa + pi * sap];
-            x.v[0] = x.v[1] = x.v[2] = x.v[3] = v;
-        }
-        Pack<TO, 4> r;
-        if constexpr (NOPS > 1) {
-            if (tmode_b) {
-                y = *reinterpret_cast<const V4*>(&sm[1][pj][col]);
-            } else if (sbl == 1) {
-                y = *reinterpret_cast<const V4*>(b + ob + pi * sbp + li);
-            } else {
-                const TI v = b[ob + pi * sbp];
-                y.v[0] = y.v[1] = y.v[2] = y.v[3] = v;
+        for (int k = 0; k < (TILE * TILE / 4) / TILE_THREADS; ++k) {
+            const int idx = threadIdx.x + k * TILE_THREADS;
+            const int pj = idx / (TILE / 4), l4 = idx % (TILE / 4);
+            const int64_t pi = p0 + pj, li = l0 + 4 * l4;
+            if (pi >= szp || li >= szl) continue;
+            const int col = 4 * (l4 ^ ((pj >> 2) & 7));
+            V4 x, y;
+            if (tmode_a) {
+                x = *reinterpret_cast<const V4*>(&sm[sl][pj][col]);
+            } else if (sal == 1) {
+                x = *reinterpret_cast<const V4*>(a + oas + pi * sap + li);
+            } else {  // broadcast along L
+                const TI v = a[oas + pi * sap];
+                x.v[0] = x.v[1] = x.v[2] = x.v[3] = v;
             }
+            Pack<TO, 4> r;
+            if constexpr (NOPS > 1) {
+                if (tmode_b) {
+                    y = *reinterpret_cast<const V4*>(&sm[depth + sl][pj][col]);
+                } else if (sbl == 1) {
+                    y = *reinterpret_cast<const V4*>(b + obs + pi * sbp + li);
+                } else {
+                    const TI v = b[obs + pi * sbp];
+                    y.v[0] = y.v[1] = y.v[2] = y.v[3] = v;
+                }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i], y.v[i]);
-        } else {
+                for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i], y.v[i]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i]);
+                for (int i = 0; i < 4; ++i) r.v[i] = f(x.v[i]);
+            }
+            *reinterpret_cast<Pack<TO, 4>*>(out + oos + pi * ostride_p + li) = r;
         }
-        *reinterpret_cast<Pack<TO, 4>*>(out + oo + pi * ostride_p + li) = r;
+    };
+    if constexpr (DEPTH == 1) {
+        compute_slice(0);
+    } else {
+#pragma unroll 1
+        for (int sl = 0; sl < slices; ++sl) compute_slice(sl);
     }
 }
 
@@ -389,17 +420,29 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
             }
             if (v4) {
                 if constexpr (sizeof(TI) == 4 && sizeof(TO) == 4) {
-                    auto kern4 = ew_tile4<TI, TO, NOPS, F>;
-                    if (tile_smem > 48 * 1024) {
+                    // Two positions of the dim next to L per block (see the kernel) for unary ops and for binary ops whose
+                    // operands are both transposed: transpose(1, 3) of [256, 64, 56, 56] went from 0.76 to 0.85 (ReLU) and
+                    // from 0.60 to 0.79 (add, mul) of the copy bandwidth.  Four positions measured slower (0.78 for ReLU),
+                    // and with one transposed and one inner-contiguous operand two are slower than one.
+                    const int dd = (L >= 1 && L - 1 != pd) ? L - 1 : -1;
+                    const bool deep = (NOPS == 1 || (tmode[0] && tmode[1])) && dd >= 0 && wp.size[dd] >= 2;
+                    const int depth = deep ? 2 : 1;
+                    const size_t smem4 = sizeof(TI) * NOPS * depth * TILE * TILE;
+                    const int64_t blocks4 = deep ? blocks / wp.size[dd] * ((wp.size[dd] + depth - 1) / depth) : blocks;
+                    if (deep && smem4 > 48 * 1024) {
                         static std::atomic<uint64_t> attr4_done{0};
                         const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
                         if (!(attr4_done.load(std::memory_order_acquire) & bit)) {
-                            WB_CHECK_CUDA(cudaFuncSetAttribute(kern4, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tile_smem)));
+                            WB_CHECK_CUDA(cudaFuncSetAttribute(ew_tile4<TI, TO, NOPS, 2, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem4)));
                             attr4_done.fetch_or(bit, std::memory_order_release);
                         }
                     }
-                    kern4<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
-                                                                                          static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), f);
+                    if (deep)
+                        ew_tile4<TI, TO, NOPS, 2, F><<<static_cast<unsigned>(blocks4), TILE_THREADS, smem4, st>>>(
+                            out, a, b, p, pd, tmode[0], tmode[1], static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), dd, f);
+                    else
+                        ew_tile4<TI, TO, NOPS, 1, F><<<static_cast<unsigned>(blocks4), TILE_THREADS, smem4, st>>>(
+                            out, a, b, p, pd, tmode[0], tmode[1], static_cast<uint32_t>(tiles_p), static_cast<uint32_t>(tiles_l), -1, f);
                 }
             } else {
                 kern<<<static_cast<unsigned>(blocks), TILE_THREADS, tile_smem, st>>>(out, a, b, p, pd, tmode[0], tmode[1],
