@@ -32,6 +32,7 @@ struct Plan {
     int64_t st[WB_PLAN_MAX_OPS][WB_MAX_DIMS];
     int64_t off[WB_PLAN_MAX_OPS];
     int mode[WB_PLAN_MAX_OPS];  // 0 scalar loads, 1 vector load (unit inner stride, aligned), 2 inner broadcast
+    FastDiv fd[WB_MAX_DIMS];    // division by size[d] as a multiply and a shift (32-bit index space only)
 };
 
 // ---- flat ---------------------------------------------------------------------------------------
@@ -94,7 +95,9 @@ __global__ void __launch_bounds__(THREADS) ew_strided(TO* __restrict__ out, cons
 #pragma unroll 1
     for (int d = p.nd - 1; d >= 0; --d) {
         IdxT sz = static_cast<IdxT>(p.size[d]);
-        IdxT q = rem / sz;
+        IdxT q;
+        if constexpr (sizeof(IdxT) == 4) q = p.fd[d].div(rem);
+        else q = rem / sz;
         IdxT c = rem - q * sz;
         rem = q;
         oa += static_cast<int64_t>(c) * p.st[0][d];
@@ -372,6 +375,8 @@ int launch(WbBackend* be, TO* out, const TI* a, const TI* b, const WbIterPlan& w
         for (int o = 0; o < WB_PLAN_MAX_OPS; ++o) p.st[o][d] = wp.st[o][d];
     }
     for (int o = 0; o < WB_PLAN_MAX_OPS; ++o) p.off[o] = wp.off[o];
+    for (int d = 0; d < wp.nd; ++d)
+        if (wp.size[d] >= 1 && wp.size[d] < (int64_t(1) << 32)) p.fd[d] = FastDiv(static_cast<uint32_t>(wp.size[d]));
     // tile: some operand has a non-unit, non-zero inner stride but unit stride along another dim
     // that is reasonably long; the other operands must be readable along L (inner stride 1 or 0)
     // or share that unit-stride dim.
