@@ -66,9 +66,11 @@ template <class T, int OP> __device__ __forceinline__ T fold(T acc, T v) {
 template <class T> __device__ __forceinline__ T shfl_down(T v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
 
 // ---- rows_smem ----------------------------------------------------------------------------------
+// vec4 (4-byte elements, len % 4 == 0, 16-byte aligned rows): the block's rows are fetched with 128-bit loads, four
+// elements of one row each (the three-reduce BatchNorm mean of [256, 64, 56, 56]: 0.085 -> 0.074-0.077 ms).
 template <class T, int OP>
 __global__ void __launch_bounds__(THREADS) reduce_rows_smem(T* __restrict__ out, const T* __restrict__ x, int64_t n_rows,
-                                                            int len, int rows_per_block) {
+                                                            int len, int rows_per_block, int vec4) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     T* sm = reinterpret_cast<T*>(smem_raw);
     const int pitch = len | 1;  // odd pitch: a warp's 32 rows hit 32 different banks
@@ -77,6 +79,22 @@ __global__ void __launch_bounds__(THREADS) reduce_rows_smem(T* __restrict__ out,
     int rows = left < rows_per_block ? static_cast<int>(left) : rows_per_block;
     const T* src = x + row0 * len;
     int total = rows * len;
+    if constexpr (sizeof(T) == 4) {
+        if (vec4) {
+            const int len4 = len >> 2, total4 = total >> 2;
+            int r4 = threadIdx.x / len4, c4 = threadIdx.x - r4 * len4;
+            const int dr4 = THREADS / len4, dc4 = THREADS - dr4 * len4;
+            for (int i = threadIdx.x; i < total4; i += THREADS) {
+                const uint4 v = reinterpret_cast<const uint4*>(src)[i];
+                uint32_t* dst = reinterpret_cast<uint32_t*>(sm) + r4 * pitch + 4 * c4;
+                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+                r4 += dr4;
+                c4 += dc4;
+                if (c4 >= len4) { c4 -= len4; ++r4; }
+            }
+            total = 0;  // nothing left for the scalar loop
+        }
+    }
     int r = threadIdx.x / len, c = threadIdx.x - r * len;
     const int dr = THREADS / len, dc = THREADS - dr * len;
     for (int i = threadIdx.x; i < total; i += THREADS) {
@@ -261,7 +279,8 @@ int reduce_value(WbBackend* be, const WbView& x, int axis, T* out) {
         int rpb = std::max(1, std::min(THREADS, budget / (len | 1)));
         size_t smem = static_cast<size_t>(rpb) * (len | 1) * sizeof(T);
         unsigned grid = static_cast<unsigned>((p.n_out + rpb - 1) / rpb);
-        reduce_rows_smem<T, OP><<<grid, THREADS, smem, st>>>(out, xp + p.off, p.n_out, len, rpb);
+        const int vec4 = sizeof(T) == 4 && len % 4 == 0 && (reinterpret_cast<uintptr_t>(xp + p.off) & 15) == 0;
+        reduce_rows_smem<T, OP><<<grid, THREADS, smem, st>>>(out, xp + p.off, p.n_out, len, rpb, vec4);
         WB_LAUNCH_OK(be);
         return WB_OK;
     }
