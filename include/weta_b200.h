@@ -337,6 +337,14 @@ int wb_trainer_set_bucket_callback(WbTrainer* t, wb_bucket_callback cb, void* us
 int wb_trainer_forward_backward(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds);
 /* Adam over the whole arena; grad_scale = 1/world after a summing all-reduce, else 1. */
 int wb_trainer_adam_step(WbTrainer* t, double grad_scale);
+/* One whole step on the staged batch: wb_trainer_forward_backward followed by wb_trainer_adam_step(t, 1.0), with the same
+ * results.  After wb_trainer_use_graph(t, 1) the step is captured once into a CUDA graph and replayed (one launch per
+ * step instead of 25-40; the first step always runs eagerly); per step only the dropout seeds and the Adam scalars are
+ * rewritten in the graph's kernel nodes.  A capture that fails, a bucket callback or per-op timing make the call issue
+ * its launches one by one as before.  No counterpart in the reference (its steps are ~400 separate launches,
+ * README.md:123-124). */
+int wb_trainer_use_graph(WbTrainer* t, int on);
+int wb_trainer_step(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds);
 /* The same update range by range, on another backend handle's stream (same device), for callers that overlap
  * the optimizer with backward: wb_trainer_begin_step advances and returns the step count, which every
  * wb_trainer_adam_range call of that step passes.  The ranges of one step must tile the arena exactly once.

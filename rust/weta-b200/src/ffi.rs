@@ -128,6 +128,8 @@ extern "C" {
     pub fn wb_trainer_init(t: *mut WbTrainer, seeds: *const u64, n_seeds: c_int) -> c_int;
     pub fn wb_trainer_step_host(t: *mut WbTrainer, host_x: *const f32, host_y: *const i64, dropout_seeds: *const u64, n_seeds: c_int,
                                 host_loss: *mut f32) -> c_int;
+    pub fn wb_trainer_use_graph(t: *mut WbTrainer, on: c_int) -> c_int;
+    pub fn wb_trainer_step(t: *mut WbTrainer, dropout_seeds: *const u64, n_seeds: c_int) -> c_int;
     pub fn wb_dp_unique_id(out: *mut WbDpId) -> c_int;
     pub fn wb_dp_create(t: *mut WbTrainer, id: *const WbDpId, rank: c_int, world: c_int, mode: c_int, bucket_elems: i64, out: *mut *mut WbDp) -> c_int;
     pub fn wb_dp_destroy(dp: *mut WbDp) -> c_int;

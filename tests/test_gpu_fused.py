@@ -377,3 +377,37 @@ def test_double_buffered_upload_matches_synchronous_steps(gpu):
         return losses
 
     assert run(True) == run(False)
+
+
+@pytest.mark.parametrize("model", ["mlp", "cnn"])
+def test_step_replayed_from_a_graph_equals_the_launch_by_launch_step(gpu, model):
+    """wb_trainer_step after wb_trainer_use_graph: the whole step is captured once and replayed with the dropout seeds and
+    the Adam scalars of each step rewritten in the graph.  Same seeds, same batches: losses and every parameter must be
+    bit-identical to forward_backward + adam_step issued launch by launch, over steps that straddle the capture."""
+    from weta_b200.trainer import mlp_specs
+    from weta_b200.workloads import MNIST_CNN
+
+    if model == "mlp":
+        specs, batch, shape = mlp_specs(), 128, (784, 1, 1)
+    else:
+        specs, batch, shape = cnn_specs(MNIST_CNN), 64, (1, 28, 28)
+    rng = np.random.default_rng(5)
+    xs = [rng.random((batch,) + shape, dtype=np.float32) for _ in range(6)]
+    ys = [rng.integers(0, 10, batch).astype(np.int64) for _ in range(6)]
+    out = {}
+    for graph in (False, True):
+        manual_seed(21)
+        tr = FusedTrainer(gpu, specs, batch, shape, lr=1e-3, matmul_mode=TF32)
+        tr.init_from_global_rng()
+        tr.use_graph(graph)
+        losses = []
+        for x, y in zip(xs, ys):
+            tr.stage(x, y)
+            tr.step()
+            losses.append(tr.loss())
+        gpu.gemm_check()
+        out[graph] = (losses, [tr.get_param(i) for i in range(len(tr.ranges))])
+        tr.close()
+    assert out[True][0] == out[False][0]
+    for a, b in zip(out[True][1], out[False][1]):
+        assert np.array_equal(a, b)

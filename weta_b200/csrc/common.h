@@ -112,6 +112,8 @@ inline bool wb_is_contiguous(const WbView& v) {
 int wb_arena_alloc(WbBackend* b, size_t bytes, void** out, size_t* klass);
 void wb_arena_free(WbBackend* b, void* p, size_t klass);
 int wb_scratch(WbBackend* b, size_t bytes, void** out);
+const void* wb_dropout_kernel_func();  // fused.cu
+const void* wb_adam_kernel_func();
 // The backend's 4096 zeroed block counters (created on first use).
 int wb_block_counters(WbBackend* b, unsigned int** out);
 int wb_new_storage(WbBackend* b, int64_t len, int dtype, WbStorage** out);

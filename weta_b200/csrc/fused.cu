@@ -347,6 +347,11 @@ extern "C" int wb_softmax_ce(WbBackend* b, const float* logits, const int64_t* l
     return wb_softmax_ce_pitched(b, logits, labels, rows, cols, probs, dlogits, cols, row_loss, mean_loss, upstream);
 }
 
+// Addresses and argument positions of the two kernels whose arguments change from step to step (the dropout seed, the
+// Adam scalars): a captured training step (trainer.cu) finds their nodes by these and rewrites those arguments.
+const void* wb_dropout_kernel_func() { return reinterpret_cast<const void*>(&dropout_kernel); }  // arguments: y, x, relu_src, n, kmin, scale, seed, vec
+const void* wb_adam_kernel_func() { return reinterpret_cast<const void*>(&adam_kernel); }        // arguments: theta, grad, m, v, n, AdamK, vec
+
 extern "C" int wb_adam_step(WbBackend* b, float* theta, const float* grad, float* m, float* v, int64_t n, int64_t t, double lr,
                             double beta1, double beta2, double eps, double weight_decay, int decoupled, double grad_scale) {
     WB_REQUIRE(b && theta && grad && m && v, WB_ERR_INVALID, "wb_adam_step: null pointer");

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "common.h"
+#include "adam.cuh"
 #include "gemm.h"
 
 int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, const float* gamma, const float* beta,
@@ -104,6 +105,18 @@ struct WbTrainer {
     std::vector<TimeRec> recs;
     std::vector<cudaEvent_t> event_pool;
     std::string timing_text;
+    // captured whole step (wb_trainer_use_graph / wb_trainer_step)
+    bool graph_on = false, graph_failed = false;
+    int eager_steps = 0;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t gexec = nullptr;
+    const float* g_x = nullptr;      // what the capture baked in: the staged batch and the backend's scratch block
+    const int64_t* g_y = nullptr;
+    const void* g_scratch = nullptr;
+    struct DropNode { cudaGraphNode_t node; cudaKernelNodeParams p; int ordinal; float* y; const float* x; const float* relu_src; int64_t n; uint64_t kmin; float scale; int vec; };
+    struct AdamNode { cudaGraphNode_t node; cudaKernelNodeParams p; float* theta; const float* grad; float *m, *v; int64_t n; int vec; };
+    std::vector<DropNode> g_drops;
+    std::vector<AdamNode> g_adams;
 };
 
 namespace {
@@ -411,6 +424,8 @@ extern "C" int wb_trainer_create(WbBackend* b, const WbLayerSpec* specs, int n_l
 extern "C" int wb_trainer_destroy(WbTrainer* t) {
     if (!t) return WB_OK;
     cudaStreamSynchronize(t->be->stream);
+    if (t->gexec) cudaGraphExecDestroy(t->gexec);
+    if (t->graph) cudaGraphDestroy(t->graph);
     for (void* p : t->owned) cudaFree(p);
     if (t->loss_pinned) cudaFreeHost(t->loss_pinned);
     delete t;
@@ -792,6 +807,135 @@ extern "C" int wb_trainer_adam_range(WbTrainer* t, WbBackend* on, int64_t offset
                         a.weight_decay, a.decoupled, grad_scale);
 }
 
+// ---- a whole step as one CUDA graph -----------------------------------------------------------------------------
+// The step of a small model is some 25-40 launches of a few microseconds each: the host's launch cost bounds it.
+// wb_trainer_step replays forward + loss + backward + Adam from a graph captured once; per step it rewrites the
+// arguments that change - the dropout seeds (found by the sentinel values the capture ran with) and the Adam scalars
+// of step t - in the graph's kernel nodes and launches it.  The first step runs eagerly (it sizes every scratch block,
+// sets kernel attributes and is the only one with Adam's first-step form); a capture that fails for any reason turns
+// the feature off for this trainer and the step runs eagerly as before.
+namespace {
+
+constexpr uint64_t SEED_SENTINEL = 0x5EEDC0DE00000000ull;
+
+void graph_drop(WbTrainer* t) {
+    if (t->gexec) cudaGraphExecDestroy(t->gexec);
+    if (t->graph) cudaGraphDestroy(t->graph);
+    t->gexec = nullptr;
+    t->graph = nullptr;
+    t->g_drops.clear();
+    t->g_adams.clear();
+}
+
+int eager_step(WbTrainer* t, const uint64_t* seeds, int n_seeds) {
+    WB_TRY(wb_trainer_forward_backward(t, seeds, n_seeds));
+    return wb_trainer_adam_step(t, 1.0);
+}
+
+// Captures one step on the trainer's stream.  Returns false (graph released, error state cleared) if anything fails.
+bool graph_capture(WbTrainer* t, int n_seeds) {
+    WbBackend* b = t->be;
+    std::vector<uint64_t> sentinels(static_cast<size_t>(std::max(n_seeds, 1)));
+    for (int i = 0; i < n_seeds; ++i) sentinels[i] = SEED_SENTINEL + static_cast<uint64_t>(i);
+    const int64_t saved_t = t->t;
+    if (cudaStreamBeginCapture(b->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { (void)cudaGetLastError(); return false; }
+    const int s = eager_step(t, sentinels.data(), n_seeds);
+    cudaGraph_t g = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(b->stream, &g);
+    t->t = saved_t;  // the captured Adam launch carries placeholder scalars; the step count advances when a step runs
+    if (s != WB_OK || e != cudaSuccess || !g) {
+        if (g) cudaGraphDestroy(g);
+        (void)cudaGetLastError();
+        return false;
+    }
+    t->graph = g;
+    if (cudaGraphInstantiate(&t->gexec, g, 0) != cudaSuccess) { (void)cudaGetLastError(); graph_drop(t); return false; }
+    size_t n_nodes = 0;
+    if (cudaGraphGetNodes(g, nullptr, &n_nodes) != cudaSuccess) { (void)cudaGetLastError(); graph_drop(t); return false; }
+    std::vector<cudaGraphNode_t> nodes(n_nodes);
+    if (n_nodes && cudaGraphGetNodes(g, nodes.data(), &n_nodes) != cudaSuccess) { (void)cudaGetLastError(); graph_drop(t); return false; }
+    std::vector<int> seen(static_cast<size_t>(std::max(n_seeds, 1)), 0);
+    for (cudaGraphNode_t node : nodes) {
+        cudaGraphNodeType type;
+        if (cudaGraphNodeGetType(node, &type) != cudaSuccess || type != cudaGraphNodeTypeKernel) continue;
+        cudaKernelNodeParams kp{};
+        if (cudaGraphKernelNodeGetParams(node, &kp) != cudaSuccess || !kp.kernelParams) { (void)cudaGetLastError(); continue; }
+        void** a = kp.kernelParams;
+        if (kp.func == wb_dropout_kernel_func()) {
+            const uint64_t seed = *static_cast<uint64_t*>(a[6]);
+            if (seed < SEED_SENTINEL || seed >= SEED_SENTINEL + static_cast<uint64_t>(n_seeds)) continue;  // a mask-free use of the kernel (ReLU backward)
+            WbTrainer::DropNode d{};
+            d.node = node; d.p = kp; d.ordinal = static_cast<int>(seed - SEED_SENTINEL);
+            d.y = *static_cast<float**>(a[0]); d.x = *static_cast<const float**>(a[1]); d.relu_src = *static_cast<const float**>(a[2]);
+            d.n = *static_cast<int64_t*>(a[3]); d.kmin = *static_cast<uint64_t*>(a[4]); d.scale = *static_cast<float*>(a[5]); d.vec = *static_cast<int*>(a[7]);
+            seen[d.ordinal]++;
+            t->g_drops.push_back(d);
+        } else if (kp.func == wb_adam_kernel_func()) {
+            WbTrainer::AdamNode d{};
+            d.node = node; d.p = kp;
+            d.theta = *static_cast<float**>(a[0]); d.grad = *static_cast<const float**>(a[1]); d.m = *static_cast<float**>(a[2]); d.v = *static_cast<float**>(a[3]);
+            d.n = *static_cast<int64_t*>(a[4]); d.vec = *static_cast<int*>(a[6]);
+            t->g_adams.push_back(d);
+        }
+    }
+    bool complete = !t->g_adams.empty();
+    for (int i = 0; i < n_seeds; ++i) complete = complete && seen[i] > 0;
+    if (!complete) { graph_drop(t); return false; }
+    t->g_x = t->x_in;
+    t->g_y = t->y_in;
+    t->g_scratch = b->scratch;
+    return true;
+}
+
+}  // namespace
+
+// Whether wb_trainer_step and wb_trainer_step_host replay a captured graph (1) or issue the launches one by one (0,
+// the default).  Not for trainers with a bucket callback (the data-parallel step issues work on other streams).
+extern "C" int wb_trainer_use_graph(WbTrainer* t, int on) {
+    WB_REQUIRE(t, WB_ERR_INVALID, "wb_trainer_use_graph: null trainer");
+    t->graph_on = on != 0;
+    if (!t->graph_on) graph_drop(t);
+    return WB_OK;
+}
+
+// One whole step on the staged batch: wb_trainer_forward_backward followed by wb_trainer_adam_step(1.0), same results.
+extern "C" int wb_trainer_step(WbTrainer* t, const uint64_t* dropout_seeds, int n_seeds) {
+    WB_REQUIRE(t, WB_ERR_INVALID, "wb_trainer_step: null trainer");
+    WbBackend* b = t->be;
+    if (!t->graph_on || t->graph_failed || t->cb || t->timing || b->profiling || t->eager_steps < 1) {
+        t->eager_steps++;
+        return eager_step(t, dropout_seeds, n_seeds);
+    }
+    int n_drop = 0;
+    for (const Layer& L : t->layers) n_drop += L.kind == L_DROPOUT && L.p > 0.0 && L.p < 1.0;
+    WB_REQUIRE(n_seeds == n_drop && (n_drop == 0 || dropout_seeds), WB_ERR_INVALID, "trainer: expected %d dropout seeds, got %d", n_drop, n_seeds);
+    // the capture baked in the staged batch's address and the backend's scratch block: capture again if either moved
+    if (t->gexec && (t->g_x != t->x_in || t->g_y != t->y_in || t->g_scratch != b->scratch)) graph_drop(t);
+    if (!t->gexec && !graph_capture(t, n_seeds)) {
+        t->graph_failed = true;
+        return eager_step(t, dropout_seeds, n_seeds);
+    }
+    t->t += 1;
+    const WbAdamConfig& ac = t->adam;
+    AdamK k = wb_adam_constants(t->t, ac.lr, ac.beta1, ac.beta2, ac.eps, ac.weight_decay, ac.decoupled, 1.0);
+    for (WbTrainer::DropNode& d : t->g_drops) {
+        uint64_t seed = dropout_seeds[d.ordinal];
+        void* args[8] = {&d.y, &d.x, &d.relu_src, &d.n, &d.kmin, &d.scale, &seed, &d.vec};
+        d.p.kernelParams = args;
+        d.p.extra = nullptr;
+        WB_CHECK_CUDA(cudaGraphExecKernelNodeSetParams(t->gexec, d.node, &d.p));
+    }
+    for (WbTrainer::AdamNode& d : t->g_adams) {
+        void* args[7] = {&d.theta, &d.grad, &d.m, &d.v, &d.n, &k, &d.vec};
+        d.p.kernelParams = args;
+        d.p.extra = nullptr;
+        WB_CHECK_CUDA(cudaGraphExecKernelNodeSetParams(t->gexec, d.node, &d.p));
+    }
+    WB_CHECK_CUDA(cudaGraphLaunch(t->gexec, b->stream));
+    b->launches++;
+    return WB_OK;
+}
+
 // The call a user makes per step: host batch in, loss out.  Copies the batch from (pinned) host
 // memory, runs forward/backward/Adam and reads the loss back; waits for the stream.
 extern "C" int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int64_t* host_y, const uint64_t* dropout_seeds, int n_seeds,
@@ -800,8 +944,7 @@ extern "C" int wb_trainer_step_host(WbTrainer* t, const float* host_x, const int
     WbBackend* b = t->be;
     WB_CHECK_CUDA(cudaMemcpyAsync(t->x_in, host_x, static_cast<size_t>(t->batch * t->in_elems) * sizeof(float), cudaMemcpyHostToDevice, b->stream));
     WB_CHECK_CUDA(cudaMemcpyAsync(t->y_in, host_y, static_cast<size_t>(t->batch) * sizeof(int64_t), cudaMemcpyHostToDevice, b->stream));
-    WB_TRY(wb_trainer_forward_backward(t, dropout_seeds, n_seeds));
-    WB_TRY(wb_trainer_adam_step(t, 1.0));
+    WB_TRY(wb_trainer_step(t, dropout_seeds, n_seeds));
     WB_CHECK_CUDA(cudaMemcpyAsync(t->loss_pinned, t->loss_dev, sizeof(float), cudaMemcpyDeviceToHost, b->stream));
     WB_CHECK_CUDA(cudaStreamSynchronize(b->stream));
     if (host_loss) *host_loss = *t->loss_pinned;

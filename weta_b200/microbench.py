@@ -263,6 +263,11 @@ def main():
         ms = timeit(lambda: tr.step_host(x.ctypes.data, y.ctypes.data), iters=50, warm=10)
         results[name] = {"ms": round(ms, 4), "samples_per_s": round(batch / ms * 1e3, 1), "batch": batch}
         print(name, results[name], flush=True)
+        # the same call with the step replayed from a CUDA graph (host batch in, loss out, every step)
+        tr.use_graph(True)
+        ms = timeit(lambda: tr.step_host(x.ctypes.data, y.ctypes.data), iters=50, warm=10)
+        results[name + ", graph"] = {"ms": round(ms, 4), "samples_per_s": round(batch / ms * 1e3, 1), "batch": batch}
+        print(name + ", graph", results[name + ", graph"], flush=True)
         tr.close()
 
     for mode, mname in ((0, "3xtf32"), (1, "tf32")):

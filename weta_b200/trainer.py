@@ -58,6 +58,8 @@ def _declare(lib):
         "wb_trainer_forward_backward": ([P, U64P, i32], i32),
         "wb_trainer_adam_step": ([P, f64], i32),
         "wb_trainer_step_host": ([P, P, P, U64P, i32, ctypes.POINTER(ctypes.c_float)], i32),
+        "wb_trainer_use_graph": ([P, i32], i32),
+        "wb_trainer_step": ([P, U64P, i32], i32),
         "wb_trainer_read_loss": ([P, ctypes.POINTER(ctypes.c_float)], i32),
         "wb_trainer_set_timing": ([P, i32], i32),
         "wb_trainer_timing_report": ([P], ctypes.c_char_p),
@@ -191,6 +193,15 @@ class FusedTrainer:
     def forward_backward(self, seeds=None):
         seeds = self.draw_dropout_seeds() if seeds is None else seeds
         self.be.check(self.lib.wb_trainer_forward_backward(self.handle, seeds, self.n_dropout))
+
+    def use_graph(self, on: bool = True):
+        """`step` and `step_host` replay the whole step from a CUDA graph captured once (one launch per step)."""
+        self.be.check(self.lib.wb_trainer_use_graph(self.handle, int(on)))
+
+    def step(self, seeds=None):
+        """forward_backward followed by adam_step(1.0), as one call (a graph replay after `use_graph`)."""
+        seeds = self.draw_dropout_seeds() if seeds is None else seeds
+        self.be.check(self.lib.wb_trainer_step(self.handle, seeds, self.n_dropout))
 
     def adam_step(self, grad_scale: float = 1.0):
         self.be.check(self.lib.wb_trainer_adam_step(self.handle, grad_scale))
