@@ -351,7 +351,14 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
     // 128 x 256 tiles when the output is wide enough: half the A traffic and twice the MMA work per pipeline
     // stage; 128 x 128 otherwise.  (128-wide tiles for one-K-block contractions, with four accumulators in
     // flight, measured slower than 256-wide ones.)
-    const int BN = n > 128 ? 256 : 128;
+    int BN = n > 128 ? 256 : 128;
+    {
+        // Small outputs: with 256-wide tiles a 512^3 product keeps 16 SMs busy; 128-wide tiles keep four times as many
+        // (16.0 -> 19.7 TFLOP/s, cuBLAS: 23).  WETA_B200_WIDE_TILES=1 keeps the wide tiles (diagnostic).
+        static const bool wide = [] { const char* e = std::getenv("WETA_B200_WIDE_TILES"); return e && e[0] == '1'; }();
+        const int64_t tiles256 = static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * grid_batch;
+        if (!wide && BN == 256 && tiles256 * 8 <= be->sm_count) BN = 128;
+    }
     // 256 x 256 tiles come in two forms: a CTA pair, or one CTA with two row blocks (better sustained rate: 641 /
     // 681 / 532 against 583 / 645 / 475 TFLOP/s on 4096^3 NN / NT / TN; but its epilogue does not overlap the next
     // tile).  The single-CTA form is taken when the contraction is long and there are enough tiles to fill the GPU
