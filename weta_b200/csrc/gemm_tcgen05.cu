@@ -357,7 +357,9 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
         // (16.0 -> 19.7 TFLOP/s, cuBLAS: 23).  WETA_B200_WIDE_TILES=1 keeps the wide tiles (diagnostic).
         static const bool wide = [] { const char* e = std::getenv("WETA_B200_WIDE_TILES"); return e && e[0] == '1'; }();
         const int64_t tiles256 = static_cast<int64_t>((m + 255) / 256) * ((n + 255) / 256) * grid_batch;
-        if (!wide && BN == 256 && tiles256 * 8 <= be->sm_count) BN = 128;
+        // (short contractions only: with a long K the 256-wide pair tiles and split-K win, fc1 forward at batch 512:
+        // 47 against 57 us)
+        if (!wide && BN == 256 && tiles256 * 8 <= be->sm_count && (k + tc::BK - 1) / tc::BK <= 64 && span_batch <= 0) BN = 128;
     }
     // 256 x 256 tiles come in two forms: a CTA pair, or one CTA with two row blocks (better sustained rate: 641 /
     // 681 / 532 against 583 / 645 / 475 TFLOP/s on 4096^3 NN / NT / TN; but its epilogue does not overlap the next
