@@ -68,51 +68,74 @@ __global__ void __launch_bounds__(THREADS) col2im_kernel(T* __restrict__ out, co
 }
 
 // ---- 3x3, stride 1, padding 1, dilation 1 on contiguous f32 images (every convolution of the named models) ----
-// Same gather, four consecutive output columns per thread and 32-bit index arithmetic: one 128-bit
-// store per thread, the nine shifted reads of each pixel come from L1/L2.
+// Same gather, V consecutive output columns per thread (V = 4, 2 or 1: the largest that divides the width) and 32-bit
+// index arithmetic by multiply and shift: one vector store per thread, the nine shifted reads of each pixel come
+// from L1/L2.  (MNIST's 14-wide second layer ran the generic 64-bit kernels at 31 us per call; with V = 2: see the
+// launch list in the design notes.)
+template <int V>
+struct VecOf;
+template <> struct VecOf<4> { using type = float4; };
+template <> struct VecOf<2> { using type = float2; };
+template <> struct VecOf<1> { using type = float; };
+
+template <int V>
 __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ out, const float* __restrict__ x, int h, int w,
-                                                           uint32_t groups, FastDiv div_wq, FastDiv div_h) {
+                                                           uint32_t groups, FastDiv div_wq, FastDiv div_h, FastDiv div_9) {
+    using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
-    const uint32_t wq = static_cast<uint32_t>(w) >> 2;
+    const uint32_t wq = static_cast<uint32_t>(w) / V;
     uint32_t t = div_wq.div(i);
     const uint32_t xq = i - t * wq;
     const uint32_t t2 = div_h.div(t);
     const uint32_t y = t - t2 * static_cast<uint32_t>(h);
     t = t2;
-    uint32_t k9 = t % 9u, nc = t / 9u;
+    const uint32_t nc = div_9.div(t), k9 = t - nc * 9u;
     int ki = static_cast<int>(k9 / 3u), kj = static_cast<int>(k9 % 3u);
     int iy = static_cast<int>(y) + ki - 1;
-    int ix0 = static_cast<int>(xq * 4u) + kj - 1;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    int ix0 = static_cast<int>(xq * V) + kj - 1;
+    float v[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) v[k] = 0.f;
     if (iy >= 0 && iy < h) {
         const float* row = x + (static_cast<int64_t>(nc) * h + iy) * w;
-        if (kj == 1) {  // the unshifted tap: one aligned 128-bit load
-            const float4 q = *reinterpret_cast<const float4*>(row + ix0);
-            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        if (V > 1 && kj == 1) {  // the unshifted tap: one aligned vector load
+            const Vec q = *reinterpret_cast<const Vec*>(row + ix0);
+            const float* qf = reinterpret_cast<const float*>(&q);
+#pragma unroll
+            for (int k = 0; k < V; ++k) v[k] = qf[k];
         } else {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < V; ++k) {
                 int ix = ix0 + k;
                 if (ix >= 0 && ix < w) v[k] = row[ix];
             }
         }
     }
-    *reinterpret_cast<float4*>(out + static_cast<int64_t>(i) * 4) = make_float4(v[0], v[1], v[2], v[3]);
+    Vec r;
+    float* rf = reinterpret_cast<float*>(&r);
+#pragma unroll
+    for (int k = 0; k < V; ++k) rf[k] = v[k];
+    *reinterpret_cast<Vec*>(out + static_cast<int64_t>(i) * V) = r;
 }
 
-// Adjoint: each thread owns four consecutive pixels of one (n, c) plane and adds its (up to) nine
+// Adjoint: each thread owns V consecutive pixels of one (n, c) plane and adds its (up to) nine
 // column entries in (ki, kj) order, the order the CPU backend's scatter reaches them.
+template <int V>
 __global__ void __launch_bounds__(THREADS) col2im3_kernel(float* __restrict__ out, const float* __restrict__ cols, int h, int w,
-                                                           uint32_t groups) {
+                                                           uint32_t groups, FastDiv div_wq, FastDiv div_h) {
+    using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
-    const uint32_t wq = static_cast<uint32_t>(w) >> 2;
-    uint32_t xq = i % wq, t = i / wq;
-    uint32_t y = t % static_cast<uint32_t>(h), nc = t / static_cast<uint32_t>(h);
+    const uint32_t wq = static_cast<uint32_t>(w) / V;
+    uint32_t t = div_wq.div(i);
+    const uint32_t xq = i - t * wq;
+    const uint32_t nc = div_h.div(t), y = t - nc * static_cast<uint32_t>(h);
     const int64_t l = static_cast<int64_t>(h) * w;
     const float* base = cols + static_cast<int64_t>(nc) * 9 * l;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) acc[k] = 0.f;
 #pragma unroll
     for (int ki = 0; ki < 3; ++ki) {
         int oy = static_cast<int>(y) + 1 - ki;
@@ -120,15 +143,19 @@ __global__ void __launch_bounds__(THREADS) col2im3_kernel(float* __restrict__ ou
 #pragma unroll
         for (int kj = 0; kj < 3; ++kj) {
             const float* row = base + (ki * 3 + kj) * l + static_cast<int64_t>(oy) * w;
-            int ox0 = static_cast<int>(xq * 4u) + 1 - kj;
+            int ox0 = static_cast<int>(xq * V) + 1 - kj;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
+            for (int k = 0; k < V; ++k) {
                 int ox = ox0 + k;
                 if (ox >= 0 && ox < w) acc[k] = acc[k] + row[ox];
             }
         }
     }
-    *reinterpret_cast<float4*>(out + static_cast<int64_t>(i) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    Vec r;
+    float* rf = reinterpret_cast<float*>(&r);
+#pragma unroll
+    for (int k = 0; k < V; ++k) rf[k] = acc[k];
+    *reinterpret_cast<Vec*>(out + static_cast<int64_t>(i) * V) = r;
 }
 
 inline bool same_conv3(const WbConvParams& p) {
@@ -163,12 +190,17 @@ extern "C" int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams*
     int64_t total = p.n * p.c * p.kh * p.kw * p.oh * p.ow;
     if (total == 0) return WB_OK;
     WbProfileScope ps(b, "im2col");
-    if (same_conv3(*cp) && x->dtype == WB_F32 && wb_is_contiguous(*x) && p.w % 4 == 0 && total / 4 < (int64_t(1) << 31) &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(static_cast<const float*>(x->data) + x->offset) & 15) == 0) {
-        int64_t groups = total / 4;
-        im2col3_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-            static_cast<float*>(out), static_cast<const float*>(x->data) + x->offset, static_cast<int>(p.h), static_cast<int>(p.w),
-            static_cast<uint32_t>(groups), FastDiv(static_cast<uint32_t>(p.w / 4)), FastDiv(static_cast<uint32_t>(p.h)));
+    if (same_conv3(*cp) && x->dtype == WB_F32 && wb_is_contiguous(*x) && total < (int64_t(1) << 31)) {
+        const float* xp = static_cast<const float*>(x->data) + x->offset;
+        const uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(xp);
+        const int v = (p.w % 4 == 0 && (bits & 15) == 0) ? 4 : ((p.w % 2 == 0 && (bits & 7) == 0) ? 2 : 1);
+        const int64_t groups = total / v;
+        const unsigned grid3 = static_cast<unsigned>((groups + THREADS - 1) / THREADS);
+        const FastDiv dwq(static_cast<uint32_t>(p.w / v)), dh(static_cast<uint32_t>(p.h)), d9(9u);
+        float* op = static_cast<float*>(out);
+        if (v == 4) im2col3_kernel<4><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
+        else if (v == 2) im2col3_kernel<2><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
+        else im2col3_kernel<1><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
         WB_LAUNCH_OK(b);
         return WB_OK;
     }
@@ -205,12 +237,16 @@ extern "C" int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvPara
     int64_t total = p.n * c * h * w;
     if (total == 0) return WB_OK;
     WbProfileScope ps(b, "col2im");
-    if (same_conv3(*cp) && cols->dtype == WB_F32 && wb_is_contiguous(*cols) && w % 4 == 0 && total / 4 < (int64_t(1) << 31) &&
-        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-        int64_t groups = total / 4;
-        col2im3_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
-            static_cast<float*>(out), static_cast<const float*>(cols->data) + cols->offset, static_cast<int>(h), static_cast<int>(w),
-            static_cast<uint32_t>(groups));
+    if (same_conv3(*cp) && cols->dtype == WB_F32 && wb_is_contiguous(*cols) && total < (int64_t(1) << 31) && total * 9 < (int64_t(1) << 40)) {
+        const int v = (w % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) ? 4 : ((w % 2 == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0) ? 2 : 1);
+        const int64_t groups = total / v;
+        const unsigned grid3 = static_cast<unsigned>((groups + THREADS - 1) / THREADS);
+        const FastDiv dwq(static_cast<uint32_t>(w / v)), dh(static_cast<uint32_t>(h));
+        float* op = static_cast<float*>(out);
+        const float* cp3 = static_cast<const float*>(cols->data) + cols->offset;
+        if (v == 4) col2im3_kernel<4><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
+        else if (v == 2) col2im3_kernel<2><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
+        else col2im3_kernel<1><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
         WB_LAUNCH_OK(b);
         return WB_OK;
     }
