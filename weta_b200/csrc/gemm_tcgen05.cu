@@ -217,7 +217,19 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     if (ep.row_stats) force_splits = 1;  // row statistics come from finished values, not split-K partials
     if (force_splits > 0) splits = force_splits;
     else if (tiles * 2 <= workers && args.k_blocks >= 16) {
-        splits = static_cast<int>(std::min<int64_t>(workers / tiles, args.k_blocks / 8));
+        // A rough cost in microseconds per candidate: pipeline fill + this split's share of the (K block, segment)
+        // iterations + a reduction pass that reads every split's partial result.  Measured anchors: a 25-block TF32
+        // product (the MLP's first layer) is faster unsplit, its 3xTF32 form (75 iterations) and the 128-block logits
+        // weight gradient are faster split 4-16 ways.
+        const int64_t max_s = std::min<int64_t>(workers / tiles, args.k_blocks / 4);
+        const double iters = static_cast<double>(args.k_blocks) * args.num_segments;
+        const double out_mb = static_cast<double>(grid_batch) * m * n * 4.0 / 1e6;
+        const double t_iter = two_blocks ? 0.55 : (BN == 256 ? 0.28 : 0.13);  // one iteration of a 2 x 128 x 256, a 256-wide and a 128 x 128 tile
+        double best = 3.0 + iters * t_iter;
+        for (int64_t c = 2; c <= max_s; ++c) {
+            const double cost = 3.0 + iters / c * t_iter + 3.0 + c * out_mb * 0.5;
+            if (cost < best) { best = cost; splits = static_cast<int>(c); }
+        }
     }
     splits = std::max(1, std::min(splits, args.k_blocks));
     // Make every split non-empty.
