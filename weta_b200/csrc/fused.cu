@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(THREADS) dropout_mask_kernel(float* __restrict
 // ---- softmax cross-entropy ----------------------------------------------------------------------
 // One warp per row.  loss_row = -(z[y] - max - log(sum exp(z - max))); p = exp(z - lse);
 // dz = (p - onehot) * gscale, with gscale = upstream_grad / N for the mean reduction.
-__global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+__device__ __forceinline__ void softmax_ce_rows(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
                                                               int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                               float* __restrict__ row_loss, float gscale) {
     int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __rest
 
 // Same, for rows of at most 32*PER_LANE classes: the row lives in registers, so the logits are read once.
 template <int PER_LANE>
-__global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+__device__ __forceinline__ void softmax_ce_reg_rows(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
                                                                   int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                                   float* __restrict__ row_loss, float gscale) {
     int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __
 // The same with 128-bit accesses: cols a multiple of 4 (so is dz_pitch), rows 16-byte aligned; lane l holds the
 // float4 groups l, l + 32, ... of its row (Q of them).
 template <int Q>
-__global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+__device__ __forceinline__ void softmax_ce_reg4_rows(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
                                                                    int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                                    float* __restrict__ row_loss, float gscale) {
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) >> 5;
@@ -206,18 +206,53 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* _
     if (dz) for (int c = cols + lane; c < dz_pitch; c += 32) dz[row * dz_pitch + c] = 0.f;
 }
 
-// mean of row_loss in a fixed order (one block; rows is a batch size).
-__global__ void __launch_bounds__(THREADS) mean_kernel(const float* __restrict__ v, int64_t n, float* __restrict__ out) {
+// The mean of row_loss in a fixed order, by the last block of the launch to finish (one launch instead of two; every
+// block's row losses are fenced before its arrival is counted).  `counter` is zero before and after.
+__device__ __forceinline__ void mean_by_last_block(const float* __restrict__ v, int64_t n, float* __restrict__ out, unsigned int* __restrict__ counter) {
     __shared__ double part[THREADS];
+    __shared__ unsigned int last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
     double acc = 0.0;
-    for (int64_t i = threadIdx.x; i < n; i += THREADS) acc += v[i];
+    for (int64_t i = threadIdx.x; i < n; i += THREADS) acc += __ldcg(v + i);
     part[threadIdx.x] = acc;
     __syncthreads();
     for (int s = THREADS / 2; s > 0; s >>= 1) {
         if (threadIdx.x < s) part[threadIdx.x] += part[threadIdx.x + s];
         __syncthreads();
     }
-    if (threadIdx.x == 0) *out = static_cast<float>(part[0] / static_cast<double>(n));
+    if (threadIdx.x == 0) {
+        *out = static_cast<float>(part[0] / static_cast<double>(n));
+        *counter = 0;
+    }
+}
+
+__global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows, int cols,
+                                                              float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
+                                                              float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
+                                                              unsigned int* __restrict__ counter) {
+    softmax_ce_rows(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
+    if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
+}
+template <int PER_LANE>
+__global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+                                                                  int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
+                                                                  float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
+                                                                  unsigned int* __restrict__ counter) {
+    softmax_ce_reg_rows<PER_LANE>(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
+    if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
+}
+template <int PER4>
+__global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* __restrict__ z, const int64_t* __restrict__ labels, int64_t rows,
+                                                                   int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
+                                                                   float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
+                                                                   unsigned int* __restrict__ counter) {
+    softmax_ce_reg4_rows<PER4>(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
+    if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
 }
 
 // ---- Adam ---------------------------------------------------------------------------------------
@@ -328,17 +363,16 @@ int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labe
     const int ic = static_cast<int>(cols), ip = static_cast<int>(dz_pitch);
     const bool v4 = cols % 4 == 0 && dz_pitch % 4 == 0 &&
                     ((reinterpret_cast<uintptr_t>(logits) | reinterpret_cast<uintptr_t>(probs) | reinterpret_cast<uintptr_t>(dlogits)) & 15) == 0;
-    if (v4 && cols > 32 && cols <= 128) softmax_ce_reg4_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
-    else if (v4 && cols > 128 && cols <= 1024) softmax_ce_reg4_kernel<8><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
-    else if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
-    else if (cols <= 128) softmax_ce_reg_kernel<4><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
-    else if (cols <= 1024) softmax_ce_reg_kernel<32><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
-    else softmax_ce_kernel<<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale);
+    unsigned int* counter = nullptr;
+    if (mean_loss) WB_TRY(wb_block_counters(b, &counter));
+    float* mo = mean_loss;
+    if (v4 && cols > 32 && cols <= 128) softmax_ce_reg4_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (v4 && cols > 128 && cols <= 1024) softmax_ce_reg4_kernel<8><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 128) softmax_ce_reg_kernel<4><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 1024) softmax_ce_reg_kernel<32><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else softmax_ce_kernel<<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
     WB_LAUNCH_OK(b);
-    if (mean_loss) {
-        mean_kernel<<<1, THREADS, 0, b->stream>>>(rl, rows, mean_loss);
-        WB_LAUNCH_OK(b);
-    }
     return WB_OK;
 }
 
