@@ -70,8 +70,8 @@ __global__ void __launch_bounds__(THREADS) col2im_kernel(T* __restrict__ out, co
 // ---- 3x3, stride 1, padding 1, dilation 1 on contiguous f32 images (every convolution of the named models) ----
 // Same gather, V consecutive output columns per thread (V = 4, 2 or 1: the largest that divides the width) and 32-bit
 // index arithmetic by multiply and shift: one vector store per thread, the nine shifted reads of each pixel come
-// from L1/L2.  (MNIST's 14-wide second layer ran the generic 64-bit kernels at 31 us per call; with V = 2: see the
-// launch list in the design notes.)
+// from L1/L2.  (MNIST's 14-wide second layer ran the generic 64-bit kernels at 31 us per call; with V = 2 the gather
+// takes 8 us and its adjoint 5.5 us.)
 template <int V>
 struct VecOf;
 template <> struct VecOf<4> { using type = float4; };
