@@ -411,3 +411,39 @@ def test_step_replayed_from_a_graph_equals_the_launch_by_launch_step(gpu, model)
     assert out[True][0] == out[False][0]
     for a, b in zip(out[True][1], out[False][1]):
         assert np.array_equal(a, b)
+
+
+def test_graph_is_captured_again_when_the_staged_batch_moves(gpu):
+    """The capture bakes in the address of the staged batch.  wb_trainer_set_input points the trainer at another
+    device buffer: the next step must not replay the old graph on the old buffer."""
+    specs, batch, shape = mlp_specs(), 64, (784, 1, 1)
+    rng = np.random.default_rng(6)
+    xs = [rng.random((batch, 784), dtype=np.float32) for _ in range(5)]
+    ys = [rng.integers(0, 10, batch).astype(np.int64) for _ in range(5)]
+    P = ctypes.c_void_p
+    out = {}
+    for graph in (False, True):
+        manual_seed(3)
+        tr = FusedTrainer(gpu, specs, batch, shape, lr=1e-3, matmul_mode=TF32)
+        tr.init_from_global_rng()
+        tr.use_graph(graph)
+        # steps 0-2 on the trainer's own staging buffers, steps 3-4 on buffers the caller owns
+        ext_x = Tensor.from_numpy(xs[3], gpu)
+        ext_y = Tensor.from_numpy(ys[3], gpu)
+        losses = []
+        for i in range(5):
+            if i < 3:
+                tr.stage(xs[i], ys[i])
+            elif i == 3:
+                gpu.check(tr.lib.wb_trainer_set_input(tr.handle, P(ext_x.storage.ptr), P(ext_y.storage.ptr)))
+            else:
+                ext_x2, ext_y2 = Tensor.from_numpy(xs[4], gpu), Tensor.from_numpy(ys[4], gpu)
+                gpu.check(tr.lib.wb_trainer_set_input(tr.handle, P(ext_x2.storage.ptr), P(ext_y2.storage.ptr)))
+            tr.step()
+            losses.append(tr.loss())
+        out[graph] = (losses, [tr.get_param(i) for i in range(len(tr.ranges))])
+        gpu.check(tr.lib.wb_trainer_set_input(tr.handle, None, None))
+        tr.close()
+    assert out[True][0] == out[False][0]
+    for a, b in zip(out[True][1], out[False][1]):
+        assert np.array_equal(a, b)
