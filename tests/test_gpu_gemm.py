@@ -1,5 +1,6 @@
 """The tcgen05 TF32 GEMM against float64 numpy: every operand layout the trait can hand over
-(row-major, transposed, batched, batch-broadcast), ragged edges, split-K, 1x and 3x TF32."""
+(row-major, transposed, batched, batch-broadcast), ragged edges, split-K (two launches, and inside a cluster), 1x and
+3x TF32."""
 import numpy as np
 import pytest
 
@@ -89,6 +90,26 @@ def test_batched_and_broadcast(gpu, mode):
 def test_split_k(gpu, mode):
     check(gpu, rnd(4096, 128), rnd(4096, 256), tr, ident, mode, "long K, few tiles (a weight gradient)")
     check(gpu, rnd(128, 8192), rnd(8192, 128), ident, ident, mode, "one tile, K = 8192")
+
+
+@pytest.mark.parametrize("mode", [TF32, TF32X3])
+def test_split_k_inside_a_cluster(gpu, mode):
+    """Few 128 x 128 tiles and a short contraction: the K blocks are split over a cluster of 2, 4 or 8 CTAs that sum
+    their partial tiles through distributed shared memory.  Whole and ragged tiles, every operand layout, a batch, and
+    the same answer bit for bit on a second run."""
+    for m, n, k in [(128, 128, 128), (128, 128, 256), (128, 128, 512), (100, 70, 520), (256, 256, 128), (130, 260, 1028 if mode == TF32 else 516),
+                    (128, 512, 784), (37, 10 * 4, 2048 if mode == TF32 else 672)]:
+        check(gpu, rnd(m, k), rnd(k, n), ident, ident, mode, f"NN {m}x{n}x{k}")
+        check(gpu, rnd(m, k), rnd(n, k), ident, tr, mode, f"NT {m}x{n}x{k}")
+        check(gpu, rnd(k, m), rnd(k, n), tr, ident, mode, f"TN {m}x{n}x{k}")
+        check(gpu, rnd(k, m), rnd(n, k), tr, tr, mode, f"TT {m}x{n}x{k}")
+    check(gpu, rnd(3, 128, 192), rnd(3, 192, 256), ident, ident, mode, "batched, three clusters per tile column")
+    gpu.set_matmul_mode(mode)
+    a, b = Tensor.from_numpy(rnd(200, 512), gpu), Tensor.from_numpy(rnd(512, 136), gpu)
+    first, second = a.matmul(b).numpy(), a.matmul(b).numpy()
+    gpu.gemm_check()
+    gpu.set_matmul_mode(TF32X3)
+    assert np.array_equal(first, second)
 
 
 def test_fallback_layouts(gpu):

@@ -152,12 +152,12 @@ __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, 
     lo[i] = v - h;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8, int MT = 1, int HALO = 0>
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW = 8, int MT = 1, int HALO = 0, int CSPLIT = 0>
 int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
     using SS = tc::SharedStorage<BN, STAGES, CTAS, EPW, MT, HALO>;
     constexpr size_t smem = sizeof(SS) + 1024;
     static_assert(smem <= 227 * 1024, "shared-memory ring does not fit");
-    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW, MT, HALO>;
+    auto kern = tc::gemm_tf32_kernel<BN, STAGES, A_MN, B_MN, CTAS, EPW, MT, HALO, CSPLIT>;
     // The attribute belongs to the device's context: one flag per device ordinal and instantiation.
     static std::atomic<uint64_t> attr_done{0};
     const uint64_t bit = uint64_t(1) << (be->ordinal & 63);
@@ -165,10 +165,10 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_done.fetch_or(bit, std::memory_order_release);
     }
-    if (CTAS == 1) {
+    if (CTAS == 1 && CSPLIT == 0) {
         kern<<<grid, tc::threads_for(EPW), smem, be->stream>>>(args);
     } else {
-        // Clusters of two CTAs (an MMA pair); grid.x is even.
+        // Clusters of two CTAs (an MMA pair; grid.x is even), or of args.splits CTAs (split-K inside a cluster).
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(tc::threads_for(EPW));
@@ -176,7 +176,7 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
         cfg.stream = be->stream;
         cudaLaunchAttribute attr{};
         attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.x = CSPLIT ? static_cast<unsigned>(args.splits) : 2u;
         attr.val.clusterDim.y = 1;
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
@@ -184,7 +184,7 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
         cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args);
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
-            wb_set_error("cluster launch of the paired GEMM failed: %s", cudaGetErrorString(e));
+            wb_set_error("cluster launch of the GEMM failed: %s", cudaGetErrorString(e));
             return WB_ERR_CUDA;
         }
     }
@@ -197,6 +197,35 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
 bool pair_mode(int m, int BN) {
     static const bool off = [] { const char* e = std::getenv("WETA_B200_NO_PAIRS"); return e && e[0] == '1'; }();
     return !off && BN == 256 && m > tc::BM;
+}
+
+// How many clusters of `c` CTAs of the cluster split-K kernel the GPU holds at once (every instantiation has the same
+// block size and shared memory, so one of them is asked); looked up once per cluster size.
+int max_clusters_128(WbBackend* be, int c) {
+    static std::atomic<int> cached[9] = {};
+    int v = cached[c].load(std::memory_order_acquire);
+    if (v) return v - 1;
+    using SS = tc::SharedStorage<128, 5, 1, 8, 1, 0>;
+    auto kern = tc::gemm_tf32_kernel<128, 5, false, false, 1, 8, 1, 0, 1>;
+    int n = 0;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(c));
+    cfg.blockDim = dim3(tc::threads_for(8));
+    cfg.dynamicSmemBytes = sizeof(SS) + 1024;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(c);
+    attr.val.clusterDim.y = attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(cfg.dynamicSmemBytes)) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        n = 0;
+    }
+    cached[c].store(n + 1, std::memory_order_release);
+    (void)be;
+    return n;
 }
 
 // Common tail of every tensor-core contraction: tile count, split-K decision and workspace, launch of
@@ -215,7 +244,21 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     const int64_t tiles = static_cast<int64_t>(tiles_m) * tiles_n * grid_batch;
     int splits = 1;
     if (ep.row_stats) force_splits = 1;  // row statistics come from finished values, not split-K partials
-    if (force_splits > 0) splits = force_splits;
+    // Split-K inside a cluster (see tc_gemm.cuh) for plain 128 x 128 tiles that leave most SMs idle: the largest of
+    // 8, 4, 2 CTAs per tile that the GPU can hold at once, with at least two K blocks each, for contractions of at most
+    // 64 (K block, segment) iterations; longer ones are faster split more than 8 ways with the separate reduction
+    // (the 422k-parameter CNN's step went from 232 to 316 us when they took this path too).  Measured: 512^3 TF32
+    // 12.4 / 10.7 / 14.5 -> 10.4 us (3xTF32 32.9 / 28.8 / 39.1 -> 22.7 / 20.6 / 22.7), the MLP's captured step 136 -> 131 us.
+    // WETA_B200_NO_CLUSTER_SPLITK=1 keeps the two-launch form.
+    static const bool cluster_off = [] { const char* e = std::getenv("WETA_B200_NO_CLUSTER_SPLITK"); return e && e[0] == '1'; }();
+    int cluster_splits = 0;
+    if (!cluster_off && force_splits <= 0 && BN == 128 && !pair && !two_blocks && !shared_taps && !three_blocks && tiles * 2 <= workers &&
+        static_cast<int64_t>(args.k_blocks) * args.num_segments <= 64) {
+        for (int c = 8; c >= 2 && !cluster_splits; c /= 2)
+            if (tiles * c <= workers && tiles <= max_clusters_128(be, c) && args.k_blocks >= 2 * c) cluster_splits = c;
+    }
+    if (cluster_splits) splits = cluster_splits;
+    else if (force_splits > 0) splits = force_splits;
     else if (tiles * 2 <= workers && args.k_blocks >= 16) {
         // A rough cost in microseconds per candidate: pipeline fill + this split's share of the (K block, segment)
         // iterations + a reduction pass that reads every split's partial result.  Measured anchors: a 25-block TF32
@@ -232,14 +275,16 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
         }
     }
     splits = std::max(1, std::min(splits, args.k_blocks));
-    // Make every split non-empty.
-    int per = (args.k_blocks + splits - 1) / splits;
-    splits = (args.k_blocks + per - 1) / per;
+    if (!cluster_splits) {
+        // Make every split non-empty.
+        int per = (args.k_blocks + splits - 1) / splits;
+        splits = (args.k_blocks + per - 1) / per;
+    }
     args.splits = splits;
     int status = WB_OK;
     void* part = nullptr;
     size_t kp = 0;
-    if (splits > 1) {
+    if (splits > 1 && !cluster_splits) {
         const int64_t per_split = grid_batch * static_cast<int64_t>(m) * n;
         status = wb_arena_alloc(be, static_cast<size_t>(per_split) * splits * sizeof(float), &part, &kp);
         if (status == WB_OK) {
@@ -259,7 +304,7 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             status = WB_ERR_UNSUPPORTED;
         }
         args.total_tiles = static_cast<int>(total_tiles);
-        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, workers) * (pair ? 2 : 1)));
+        dim3 grid(static_cast<unsigned>(std::min<int64_t>(total_tiles, workers) * (pair ? 2 : 1)));  // cluster split-K: total_tiles <= workers
         // Shared memory: a 192 KB ring (6 x 32 KB per CTA of a pair, 4 x 48 KB for BN = 256, 5 x 32 KB for BN = 128)
         // + 32 KB epilogue staging; one persistent CTA per SM.
         if (status != WB_OK) {
@@ -295,6 +340,11 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             else if (!amn && bmn) status = launch_tc<256, 4, false, true, 1>(be, st, args, grid);
             else if (amn && !bmn) status = launch_tc<256, 4, true, false, 1>(be, st, args, grid);
             else status = launch_tc<256, 4, true, true, 1>(be, st, args, grid);
+        } else if (cluster_splits) {
+            if (!amn && !bmn) status = launch_tc<128, 5, false, false, 1, 8, 1, 0, 1>(be, st, args, grid);
+            else if (!amn && bmn) status = launch_tc<128, 5, false, true, 1, 8, 1, 0, 1>(be, st, args, grid);
+            else if (amn && !bmn) status = launch_tc<128, 5, true, false, 1, 8, 1, 0, 1>(be, st, args, grid);
+            else status = launch_tc<128, 5, true, true, 1, 8, 1, 0, 1>(be, st, args, grid);
         } else {
             if (!amn && !bmn) status = launch_tc<128, 5, false, false, 1>(be, st, args, grid);
             else if (!amn && bmn) status = launch_tc<128, 5, false, true, 1>(be, st, args, grid);
@@ -302,7 +352,7 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
             else status = launch_tc<128, 5, true, true, 1>(be, st, args, grid);
         }
     }
-    if (status == WB_OK && splits > 1) {
+    if (status == WB_OK && splits > 1 && !cluster_splits) {
         const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
         if (splits >= 32 && total <= (1 << 16))
             splitk_reduce_warp<<<static_cast<unsigned>((total * 32 + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits,

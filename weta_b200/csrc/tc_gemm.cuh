@@ -253,10 +253,25 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // the order middle, upper, lower; the lower tap's ring slot carries weights only and its MMAs read the pixels from
 // the upper tap's slot, which is handed back together with its own.  Two pixel copies instead of three per kernel
 // column: a fifth fewer operand bytes through L2 on 128 x 256 tiles.  (Works for CTA pairs too; measured no gain there.)
-template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT, int HALO = 0>
+//
+// CSPLIT = 1: split-K inside a thread-block cluster, for outputs of so few tiles that most SMs would idle while each
+// busy one pulls a whole contraction's operands through its own L2 port (a 128 x 128 tile takes in 32 KB per K block
+// at about 50 bytes per clock, whatever the tensor cores could do).  The grid is one cluster of `splits` (2, 4 or 8)
+// CTAs per tile, one tile per cluster; CTA r accumulates K blocks [r * k_blocks / splits, (r + 1) * k_blocks / splits),
+// writes its accumulator into its own shared memory (the operand ring, idle by then) and, after a cluster barrier,
+// sums rows [r * 128 / splits, (r + 1) * 128 / splits) of all the CTAs' partial tiles through distributed shared
+// memory in rank order (one order, every run), applies the epilogue and stores them: no partial results in global
+// memory and no second launch.  A second cluster barrier keeps every CTA's shared memory alive until its peers have
+// read it.  (Sending the rows to their owners with remote stores instead, which needs no second barrier, was slower:
+// 3 us for the exchange against 0.7 + 2.3 us for barrier and remote reads on a 512^3 product.)
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CTAS, int EPW, int MT, int HALO = 0, int CSPLIT = 0>
 __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __grid_constant__ Args args) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using SS = SharedStorage<BN, STAGES, CTAS, EPW, MT, HALO>;
+    static_assert(CSPLIT == 0 || (CTAS == 1 && MT == 1 && HALO == 0 && BN == 128 && EPW == 8), "cluster split-K: plain 128 x 128 tiles");
+    constexpr int RED_LD = BN + 4;  // floats between rows of the partial tile in shared memory (padded against bank conflicts)
+    static_assert(CSPLIT == 0 || BM * RED_LD <= STAGES * MT * BM * BK, "the partial tile must fit the A ring");
+
     static_assert(MT == 1 || (MT == 2 && CTAS == 1 && BN == 256) || (MT == 3 && CTAS == 1 && BN == 128 && B_MN && !A_MN && HALO == 0),
                   "two row blocks per CTA: single CTAs with 256-wide tiles; three (conv_mode 3): 128-wide tiles");
     static_assert(HALO == 0 || (MT == 1 && B_MN && !A_MN && STAGES >= 3), "shared tap windows: implicit convolution tiles only");
@@ -301,6 +316,18 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
 
     // Tile t -> (n block, m block, z = batch * splits + split); n fastest so neighbouring CTAs share A.
     auto decode = [&](int t, int& m0, int& n0, int& batch, int& split, int& kb_begin, int& kb_end) {
+        if constexpr (CSPLIT) {
+            // split fastest: the CTAs of a cluster are the splits of one tile, and the K blocks are dealt out evenly
+            split = t % args.splits;
+            t /= args.splits;
+            n0 = (t % args.tiles_n) * BN;
+            const int r = t / args.tiles_n;
+            m0 = (r % args.tiles_m) * TILE_M;
+            batch = r / args.tiles_m;
+            kb_begin = static_cast<int>(static_cast<int64_t>(split) * args.k_blocks / args.splits);
+            kb_end = static_cast<int>(static_cast<int64_t>(split + 1) * args.k_blocks / args.splits);
+            return;
+        }
         const int nb = t % args.tiles_n;
         const int r = t / args.tiles_n;
         const int mb = r % args.tiles_m;
@@ -524,7 +551,24 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
         for (int t = first_tile; t < args.total_tiles && ok; t += tile_step, ++tile_iter) {
             int tile_m0, n0, batch, split, kb_begin, kb_end;
             decode(t, tile_m0, n0, batch, split, kb_begin, kb_end);
-          if constexpr (MT == 3) {
+          if constexpr (CSPLIT) {
+            // The partial tile goes to shared memory as it is; the sum over the cluster follows the role branches.
+            if (!mbar_wait(&ss.tmem_full[0], 0)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(half * HALF_N) + (static_cast<uint32_t>(lg * 32) << 16);
+            float* dst = &ss.a[0][0] + (lg * 32 + lane) * RED_LD + half * HALF_N;
+#pragma unroll 1
+            for (int c = 0; c < HALF_N; c += 32) {
+                uint32_t raw[32];
+                tmem_ld32_issue(tmem_d + c, raw);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    *reinterpret_cast<float4*>(dst + c + 4 * i) = make_float4(__uint_as_float(raw[4 * i]), __uint_as_float(raw[4 * i + 1]),
+                                                                              __uint_as_float(raw[4 * i + 2]), __uint_as_float(raw[4 * i + 3]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          } else if constexpr (MT == 3) {
             // conv_mode 3: the tile's three accumulators (kernel columns 0, 1, 2 at TMEM columns 0, BN, 2 * BN) are read
             // together and combined with a move of one pixel each way; plain stores only (no bias, no statistics).
             if (!mbar_wait(&ss.tmem_full[0], static_cast<uint32_t>(tile_iter) & 1)) { ok = false; break; }
@@ -716,6 +760,66 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
         }
         if (row_stats) flush_stats();
     }
+    if constexpr (CSPLIT) {
+        // Every CTA of the cluster has its partial tile in shared memory after this barrier (a CTA whose wait ran out
+        // arrives too, with the error flag set below; the tile is then garbage and reported as such).
+        __syncthreads();
+        cluster_sync_all();
+        if (warp >= 2 && static_cast<int>(blockIdx.x) < args.total_tiles) {
+            int m0, n0, batch, split, kb_begin, kb_end;
+            decode(static_cast<int>(blockIdx.x), m0, n0, batch, split, kb_begin, kb_end);
+            const uint32_t red_base = smem_u32(&ss.a[0][0]);
+            float* out_base = args.ep.out + static_cast<int64_t>(batch) * args.ep.batch_stride_d;
+            const bool vec_ok = (args.ep.ldd % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.ep.out) & 15) == 0) && (args.ep.batch_stride_d % 4 == 0);
+            // A thread sums BM * BN / 4 / (32 * EPW) / PARTS groups of four columns, each from PARTS CTAs: sixteen remote
+            // loads whatever the cluster size, all issued before the first is used.
+            auto reduce = [&](auto parts_tag) {
+                constexpr int PARTS = decltype(parts_tag)::value, ROWS = BM / PARTS, ITEMS = ROWS * (BN / 4) / (32 * EPW);
+                float4 part[ITEMS][PARTS];
+#pragma unroll
+                for (int it = 0; it < ITEMS; ++it) {
+                    const int idx = static_cast<int>(threadIdx.x) - 64 + it * 32 * EPW;
+                    const uint32_t off = red_base + static_cast<uint32_t>(((split * ROWS + idx / (BN / 4)) * RED_LD + 4 * (idx % (BN / 4))) * sizeof(float));
+#pragma unroll
+                    for (int p = 0; p < PARTS; ++p)
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(part[it][p].x), "=f"(part[it][p].y), "=f"(part[it][p].z), "=f"(part[it][p].w)
+                                     : "r"(map_to_cta(off, static_cast<uint32_t>(p)))
+                                     : "memory");
+                }
+#pragma unroll
+                for (int it = 0; it < ITEMS; ++it) {
+                    const int idx = static_cast<int>(threadIdx.x) - 64 + it * 32 * EPW;
+                    const int row = m0 + split * ROWS + idx / (BN / 4), col = n0 + 4 * (idx % (BN / 4));
+                    if (row >= args.m || col >= args.n) continue;
+                    float v[4] = {part[it][0].x, part[it][0].y, part[it][0].z, part[it][0].w};
+#pragma unroll
+                    for (int p = 1; p < PARTS; ++p) { v[0] += part[it][p].x; v[1] += part[it][p].y; v[2] += part[it][p].z; v[3] += part[it][p].w; }
+                    const float bm = args.ep.bias_m ? args.ep.bias_m[row] : 0.f;
+                    float* dst = out_base + static_cast<int64_t>(row) * args.ep.ldd + col;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[j] += bm;
+                        if (args.ep.bias_n && col + j < args.n) v[j] += args.ep.bias_n[col + j];
+                        if (args.ep.relu) v[j] = fmaxf(v[j], 0.f);
+                    }
+                    if (vec_ok && col + 4 <= args.n) {
+                        float4 o = make_float4(v[0], v[1], v[2], v[3]);
+                        if (args.ep.accumulate) {
+                            const float4 old = *reinterpret_cast<const float4*>(dst);
+                            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = o;
+                    } else {
+                        for (int j = 0; j < 4 && col + j < args.n; ++j) dst[j] = args.ep.accumulate ? dst[j] + v[j] : v[j];
+                    }
+                }
+            };
+            if (args.splits == 8) reduce(std::integral_constant<int, 8>{});
+            else if (args.splits == 4) reduce(std::integral_constant<int, 4>{});
+            else reduce(std::integral_constant<int, 2>{});
+        }
+    }
     if (!ok) {
         atomicExch(args.error_flag, 1);
         // Give copies and MMAs that are still in flight time to finish before the CTA retires.
@@ -724,7 +828,7 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if constexpr (CTAS == 2) cluster_sync_all();  // neither CTA frees TMEM or leaves while its peer may still signal or write it
+    if constexpr (CTAS == 2 || CSPLIT != 0) cluster_sync_all();  // no CTA frees TMEM or leaves while a peer may still signal it or read its shared memory
     if (warp == 1) {
         if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
         else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
