@@ -521,8 +521,10 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(c
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * THREADS) >> 5, first = (blockIdx.x * THREADS + threadIdx.x) >> 5;
     const uint32_t q = static_cast<uint32_t>(pooled >> 2);  // pooled % 4 == 0 (checked by the host)
+    // Channel fastest: the warps that run side by side read neighbouring planes of the same images, so the 1-4 KB
+    // pieces they fetch lie next to one another in memory.
     for (int item = first; item < c_total * slabs; item += warps) {
-        const int c = item / slabs, sl = item - c * slabs;
+        const int sl = item / c_total, c = item - sl * c_total;
         const float g = __ldg(gamma + c), b = __ldg(beta + c);
         const int64_t n0 = min(n_img, static_cast<int64_t>(sl) * per), n1 = min(n_img, n0 + per);
         const int64_t stride = static_cast<int64_t>(c_total) * pooled, base = (n0 * c_total + c) * pooled;
@@ -583,8 +585,8 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(c
             s2 += __shfl_down_sync(0xffffffffu, s2, sh);
         }
         if (lane == 0) {
-            part[static_cast<int64_t>(item) * 2] = s1;
-            part[static_cast<int64_t>(item) * 2 + 1] = s2;
+            part[(static_cast<int64_t>(c) * slabs + sl) * 2] = s1;
+            part[(static_cast<int64_t>(c) * slabs + sl) * 2 + 1] = s2;
         }
     }
 }
@@ -613,7 +615,10 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     __shared__ double red[2][THREADS / 32];
     for (int item = blockIdx.x; item < c_total * slabs; item += gridDim.x) {
-        const int c = item / slabs, sl = item - c * slabs;
+        // channel fastest: blocks that run side by side read neighbouring planes of the same images (the dx pass of the
+        // 128 -> 256 channel block: 0.548 -> 0.537 ms against slab fastest)
+        const int sl = item / c_total, c = item - sl * c_total;
+        const int64_t slot = static_cast<int64_t>(c) * slabs + sl;
         const float m = __ldg(mean + c), r = __ldg(rstd + c), g = __ldg(gamma + c), b = __ldg(beta + c);
         // sums pass only: this channel's sums were already taken from the pooled tensors (block-uniform)
         if (!WRITE_DX && skip_pooled_ok && pooled_sums_ok(g, b)) continue;
@@ -713,10 +718,10 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
             double t1 = 0.0, t2 = 0.0;
             for (int q = 0; q < THREADS / 32; ++q) { t1 += red[0][q]; t2 += red[1][q]; }
             if (WRITE_DX) {
-                part[item] = t1;  // sum of dx: the conv bias gradient
+                part[slot] = t1;  // sum of dx: the conv bias gradient
             } else {
-                part[static_cast<int64_t>(item) * 2] = t1;
-                part[static_cast<int64_t>(item) * 2 + 1] = t2;
+                part[slot * 2] = t1;
+                part[slot * 2 + 1] = t2;
             }
         }
         __syncthreads();
