@@ -298,6 +298,9 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     if (status == WB_OK) {
         args.tiles_m = tiles_m;
         args.tiles_n = tiles_n;
+        args.div_tiles_m = FastDiv(static_cast<uint32_t>(tiles_m));
+        args.div_tiles_n = FastDiv(static_cast<uint32_t>(tiles_n));
+        args.div_splits = FastDiv(static_cast<uint32_t>(splits));
         const int64_t total_tiles = tiles * splits;
         if (total_tiles >= (int64_t(1) << 31)) {
             wb_set_error("gemm: too many tiles");

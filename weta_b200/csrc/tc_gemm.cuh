@@ -61,6 +61,8 @@ struct Args {
     int batched_a, batched_b;  // 0: operand shared by every batch (TMA coordinate 0)
     int kpb;                   // K blocks per image when the contraction spans the batch, else 0
     int tiles_m, tiles_n, total_tiles;  // tile list walked by the persistent CTAs
+    FastDiv div_tiles_m, div_tiles_n, div_splits;  // the same counts as multiply-shift divisors: a tile index is taken apart by one
+                                                   // thread per role before its first copy, MMA or store can start
     // Implicit-GEMM convolution (3x3, stride 1, padding 1, NCHW).  The B operand is not a matrix in memory
     // but windows of an image tensor [n][c][h*w]: a run of pixels moved by (ky-1) rows is the same run at
     // flattened offset (ky-1)*w, which TMA can start at when w is a multiple of 4; the horizontal move by
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
     constexpr int NACC = 512 / BN;      // accumulators in TMEM (all 512 columns), used round-robin: 2 or 4 tiles in flight
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kb_per = (args.k_blocks + args.splits - 1) / args.splits;
+    const int kb_per = static_cast<int>(args.div_splits.div(static_cast<uint32_t>(args.k_blocks + args.splits - 1)));
     const int rank = CTAS == 2 ? static_cast<int>(cluster_ctarank()) : 0;
     const int first_tile = static_cast<int>(blockIdx.x) / CTAS, tile_step = static_cast<int>(gridDim.x) / CTAS;
 
@@ -316,26 +318,23 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
 
     // Tile t -> (n block, m block, z = batch * splits + split); n fastest so neighbouring CTAs share A.
     auto decode = [&](int t, int& m0, int& n0, int& batch, int& split, int& kb_begin, int& kb_end) {
+        const uint32_t ut = static_cast<uint32_t>(t);
         if constexpr (CSPLIT) {
             // split fastest: the CTAs of a cluster are the splits of one tile, and the K blocks are dealt out evenly
-            split = t % args.splits;
-            t /= args.splits;
-            n0 = (t % args.tiles_n) * BN;
-            const int r = t / args.tiles_n;
-            m0 = (r % args.tiles_m) * TILE_M;
-            batch = r / args.tiles_m;
-            kb_begin = static_cast<int>(static_cast<int64_t>(split) * args.k_blocks / args.splits);
-            kb_end = static_cast<int>(static_cast<int64_t>(split + 1) * args.k_blocks / args.splits);
+            const uint32_t q = args.div_splits.div(ut), r = args.div_tiles_n.div(q), b = args.div_tiles_m.div(r);
+            split = static_cast<int>(ut - q * args.splits);
+            n0 = static_cast<int>(q - r * args.tiles_n) * BN;
+            m0 = static_cast<int>(r - b * args.tiles_m) * TILE_M;
+            batch = static_cast<int>(b);
+            kb_begin = static_cast<int>(args.div_splits.div(static_cast<uint32_t>(split * args.k_blocks)));
+            kb_end = static_cast<int>(args.div_splits.div(static_cast<uint32_t>((split + 1) * args.k_blocks)));
             return;
         }
-        const int nb = t % args.tiles_n;
-        const int r = t / args.tiles_n;
-        const int mb = r % args.tiles_m;
-        const int z = r / args.tiles_m;
-        m0 = mb * TILE_M;
-        n0 = nb * BN;
-        batch = z / args.splits;
-        split = z % args.splits;
+        const uint32_t r = args.div_tiles_n.div(ut), z = args.div_tiles_m.div(r), bz = args.div_splits.div(z);
+        m0 = static_cast<int>(r - z * args.tiles_m) * TILE_M;
+        n0 = static_cast<int>(ut - r * args.tiles_n) * BN;
+        batch = static_cast<int>(bz);
+        split = static_cast<int>(z - bz * args.splits);
         kb_begin = split * kb_per;
         kb_end = min(args.k_blocks, kb_begin + kb_per);
     };
