@@ -163,6 +163,13 @@ struct WbIterPlan {
 void wb_make_plan(const WbView* const* ops, int nops, WbIterPlan* plan);
 
 // Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
+// Lets the next kernel of the stream begin, if it was launched as a programmatic dependent of this one (the tensor-core
+// GEMM is): that kernel runs its preamble while this one works, and waits for this one's completion before it touches
+// global memory.  No effect otherwise.
+#ifdef __CUDACC__
+__device__ __forceinline__ void wb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 struct FastDiv {
     uint32_t d, s;
     uint64_t mul;

@@ -81,6 +81,7 @@ template <> struct VecOf<1> { using type = float; };
 template <int V>
 __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ out, const float* __restrict__ x, int h, int w,
                                                            uint32_t groups, FastDiv div_wq, FastDiv div_h, FastDiv div_9) {
+    wb_launch_dependents();
     using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
@@ -124,6 +125,7 @@ __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ ou
 template <int V>
 __global__ void __launch_bounds__(THREADS) col2im3_kernel(float* __restrict__ out, const float* __restrict__ cols, int h, int w,
                                                            uint32_t groups, FastDiv div_wq, FastDiv div_h) {
+    wb_launch_dependents();
     using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;

@@ -39,6 +39,7 @@ constexpr uint64_t GOLDEN = 0x9E3779B97F4A7C15ull;
 // relu_src != null the incoming value is additionally multiplied by step(relu_src) (ReLU backward folded in).
 __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ relu_src,
                                                            int64_t n, uint64_t kmin, float scale, uint64_t seed, int vec) {
+    wb_launch_dependents();
     int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
     uint64_t z = seed + (static_cast<uint64_t>(i) + 1) * GOLDEN;
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* _
 // One thread per four elements (128-bit accesses); the last, partial group is done element by element.
 __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta, const float* __restrict__ grad, float* __restrict__ m,
                                                         float* __restrict__ v, int64_t n, AdamK k, int vec) {
+    wb_launch_dependents();
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
     if (vec && i + 4 <= n) {

@@ -318,6 +318,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_quad_kernel(float* _
                                                                          const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                          int c_total, int h, int w, uint32_t total, FastDiv div_ipp,
                                                                          FastDiv div_owq, FastDiv div_c) {
+    wb_launch_dependents();
     const uint32_t owq = static_cast<uint32_t>(w >> 3), ipp = static_cast<uint32_t>(h >> 1) * owq;
     const int64_t plane_elems = static_cast<int64_t>(h) * w;
     const uint32_t stride = gridDim.x * THREADS;
@@ -361,6 +362,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_kernel(float* __rest
                                                                     const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                     int c_total, int h, int w, int64_t total) {
+    wb_launch_dependents();
     int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
     if (i >= total) return;
     const int ow = w >> 1, oh = h >> 1;
@@ -458,6 +460,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
                                                                        const float* __restrict__ beta, const float* __restrict__ dgamma,
                                                                        const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
                                                                        int w, float inv_count, double* __restrict__ bias_part) {
+    wb_launch_dependents();
     const int c = blockIdx.x;
     const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
     const float k1 = dbeta[c] * inv_count, k2 = dgamma[c] * inv_count, gr = g * r;
@@ -605,6 +608,7 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
                                                                             const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
                                                                             int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
                                                                             FastDiv div_owp, int slabs, int skip_pooled_ok) {
+    wb_launch_dependents();
     // Work items are (channel, slab of images) pairs, many more than blocks, walked round-robin: every SM stays
     // equally loaded whatever the channel count.  The two windows a thread owns are computed side by side in
     // packed f32x2 arithmetic (.x = left window, .y = right window).
@@ -730,6 +734,7 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
 
 // One warp per channel, as bn_bwd_finalize_kernel.
 __global__ void __launch_bounds__(128) sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
+    wb_launch_dependents();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= c_total) return;
     double s = 0.0;

@@ -102,6 +102,7 @@ int make_map(GemmState* st, const WbGemmOperand& o, int64_t batch, int box_rows,
 // Split-K finish: out = epilogue(sum over splits of partial).
 __global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
                                                      int m, int n, tc::Epilogue ep) {
+    wb_launch_dependents();
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
     int64_t per = static_cast<int64_t>(m) * n;
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ p
 // splits in ascending order, the lanes' sums are combined by a fixed shuffle tree: one order, every run).
 __global__ void __launch_bounds__(256) splitk_reduce_warp(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
                                                           int m, int n, tc::Epilogue ep) {
+    wb_launch_dependents();
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (i >= total) return;
@@ -141,6 +143,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_warp(const float* __restric
 // hi = x with the 13 low mantissa bits cleared (exactly a tf32 value), lo = x - hi (exact in f32).
 __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
                                                    int64_t nb, int64_t outer, int64_t inner, int64_t bs, int64_t ld, int64_t inner_p) {
+    wb_launch_dependents();
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     int64_t total = nb * outer * inner_p;
     if (i >= total) return;
@@ -165,28 +168,36 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
         WB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_done.fetch_or(bit, std::memory_order_release);
     }
-    if (CTAS == 1 && CSPLIT == 0) {
-        kern<<<grid, tc::threads_for(EPW), smem, be->stream>>>(args);
-    } else {
-        // Clusters of two CTAs (an MMA pair; grid.x is even), or of args.splits CTAs (split-K inside a cluster).
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(tc::threads_for(EPW));
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = be->stream;
-        cudaLaunchAttribute attr{};
-        attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = CSPLIT ? static_cast<unsigned>(args.splits) : 2u;
-        attr.val.clusterDim.y = 1;
-        attr.val.clusterDim.z = 1;
-        cfg.attrs = &attr;
-        cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();
-            wb_set_error("cluster launch of the GEMM failed: %s", cudaGetErrorString(e));
-            return WB_ERR_CUDA;
-        }
+    // Every launch is a programmatic dependent of the kernel before it in the stream (the kernel waits with
+    // griddepcontrol.wait after its preamble, see tc_gemm.cuh); CTA pairs and cluster split-K add the cluster size
+    // (2; args.splits).  WETA_B200_NO_PDL=1 launches plainly.
+    static const bool no_pdl = [] { const char* e = std::getenv("WETA_B200_NO_PDL"); return e && e[0] == '1'; }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(tc::threads_for(EPW));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = be->stream;
+    cudaLaunchAttribute attrs[2]{};
+    unsigned na = 0;
+    if (CTAS == 2 || CSPLIT != 0) {
+        attrs[na].id = cudaLaunchAttributeClusterDimension;
+        attrs[na].val.clusterDim.x = CSPLIT ? static_cast<unsigned>(args.splits) : 2u;  // grid.x is a multiple of it
+        attrs[na].val.clusterDim.y = 1;
+        attrs[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (!no_pdl) {
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        wb_set_error("launch of the tensor-core GEMM failed: %s", cudaGetErrorString(e));
+        return WB_ERR_CUDA;
     }
     WB_LAUNCH_OK(be);
     return WB_OK;

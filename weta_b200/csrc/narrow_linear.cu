@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(512) narrow_wgrad_kernel(float* __restrict__ d
 template <int S>
 __global__ void __launch_bounds__(256) narrow_dgrad_kernel(float* __restrict__ dx, const float* __restrict__ dy, int64_t dy_pitch,
                                                             const float* __restrict__ w, int n, int in, int out, int tf32) {
+    wb_launch_dependents();
     const int64_t t = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     const int q = in >> 2;  // in % 4 == 0
     if (t >= static_cast<int64_t>(n) * q) return;

@@ -315,6 +315,11 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = ss.tmem_base;
     bool ok = true;
+    // Launched as a programmatic dependent of the kernel before it in the stream: everything above (barriers, TMEM,
+    // and the launch itself) may run while that kernel is still finishing; nothing below touches global memory before
+    // it has completed and its writes are visible.  Kernels after this one may start their own preamble at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Tile t -> (n block, m block, z = batch * splits + split); n fastest so neighbouring CTAs share A.
     auto decode = [&](int t, int& m0, int& n0, int& batch, int& split, int& kb_begin, int& kb_end) {

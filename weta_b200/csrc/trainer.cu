@@ -186,6 +186,7 @@ int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, i
 // strip's slabs in ascending order.
 __global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int64_t per,
                                                          float* __restrict__ part, unsigned int* __restrict__ counter, float* __restrict__ dst) {
+    wb_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + lane;
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * per, r1 = min(rows, r0 + per);
