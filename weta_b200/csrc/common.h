@@ -5,6 +5,8 @@
 #include <stdint.h>
 
 #include <cstdarg>
+#include <cstdlib>
+#include <utility>
 #include <cstdio>
 #include <map>
 #include <mutex>
@@ -163,11 +165,31 @@ struct WbIterPlan {
 void wb_make_plan(const WbView* const* ops, int nops, WbIterPlan* plan);
 
 // Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
-// Lets the next kernel of the stream begin, if it was launched as a programmatic dependent of this one (the tensor-core
-// GEMM is): that kernel runs its preamble while this one works, and waits for this one's completion before it touches
-// global memory.  No effect otherwise.
+// Programmatic dependent launch.  A kernel launched with wb_launch_pdl may be scheduled while the kernel before it in
+// the stream is still running; its first statement is wb_pdl_enter(), which waits until that kernel has completed and
+// its writes are visible, and then lets the kernel after it be scheduled in the same way.  What overlaps is the launch
+// itself (and, in the tensor-core GEMM, the preamble it runs before its own wait): one to two microseconds per kernel,
+// which is most of a small model's step.  Dependencies through events are not relaxed.  WETA_B200_NO_PDL=1 launches plainly.
 #ifdef __CUDACC__
-__device__ __forceinline__ void wb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void wb_pdl_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <class... Params, class... Args>
+inline cudaError_t wb_launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    static const bool plain = [] { const char* e = std::getenv("WETA_B200_NO_PDL"); return e && e[0] == '1'; }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = plain ? nullptr : &attr;
+    cfg.numAttrs = plain ? 0u : 1u;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 #endif
 
 struct FastDiv {

@@ -56,6 +56,7 @@ struct Args {
 };
 
 __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __grid_constant__ Args args) {
+    wb_pdl_enter();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     Smem& ss = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) conv1_bwd_fused_kernel(const __gri
 // order, a fixed shuffle tree.
 __global__ void __launch_bounds__(256) conv1_bwd_reduce_kernel(const float* __restrict__ part, const double* __restrict__ bias_part, int ctas, int ck,
                                                                float* __restrict__ dweight, float* __restrict__ dbias) {
+    wb_pdl_enter();
     const int item = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (item < CH * ck) {
         const int o = item / ck, k = item - o * ck;
@@ -319,10 +321,10 @@ int wb_conv1_bwd_fused(WbBackend* b, const float* x, const float* dy_pooled, con
         WB_CHECK_CUDA(cudaFuncSetAttribute(conv1_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_done.fetch_or(bit, std::memory_order_release);
     }
-    conv1_bwd_fused_kernel<<<ctas, THREADS, smem, b->stream>>>(args);
+    wb_launch_pdl(conv1_bwd_fused_kernel, dim3(ctas), dim3(THREADS), smem, b->stream, args);
     WB_LAUNCH_OK(b);
     const int items = static_cast<int>(CH * ck + CH);
-    conv1_bwd_reduce_kernel<<<(items * 32 + 255) / 256, 256, 0, b->stream>>>(args.part, args.bias_part, ctas, static_cast<int>(ck), dweight, dbias_conv);
+    wb_launch_pdl(conv1_bwd_reduce_kernel, dim3((items * 32 + 255) / 256), dim3(256), 0, b->stream, args.part, args.bias_part, ctas, static_cast<int>(ck), dweight, dbias_conv);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

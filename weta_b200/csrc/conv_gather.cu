@@ -81,7 +81,7 @@ template <> struct VecOf<1> { using type = float; };
 template <int V>
 __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ out, const float* __restrict__ x, int h, int w,
                                                            uint32_t groups, FastDiv div_wq, FastDiv div_h, FastDiv div_9) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(THREADS) im2col3_kernel(float* __restrict__ ou
 template <int V>
 __global__ void __launch_bounds__(THREADS) col2im3_kernel(float* __restrict__ out, const float* __restrict__ cols, int h, int w,
                                                            uint32_t groups, FastDiv div_wq, FastDiv div_h) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     using Vec = typename VecOf<V>::type;
     uint32_t i = blockIdx.x * THREADS + threadIdx.x;
     if (i >= groups) return;
@@ -200,9 +200,9 @@ extern "C" int wb_im2col_into(WbBackend* b, const WbView* x, const WbConvParams*
         const unsigned grid3 = static_cast<unsigned>((groups + THREADS - 1) / THREADS);
         const FastDiv dwq(static_cast<uint32_t>(p.w / v)), dh(static_cast<uint32_t>(p.h)), d9(9u);
         float* op = static_cast<float*>(out);
-        if (v == 4) im2col3_kernel<4><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
-        else if (v == 2) im2col3_kernel<2><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
-        else im2col3_kernel<1><<<grid3, THREADS, 0, b->stream>>>(op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
+        if (v == 4) wb_launch_pdl(im2col3_kernel<4>, dim3(grid3), dim3(THREADS), 0, b->stream, op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
+        else if (v == 2) wb_launch_pdl(im2col3_kernel<2>, dim3(grid3), dim3(THREADS), 0, b->stream, op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
+        else wb_launch_pdl(im2col3_kernel<1>, dim3(grid3), dim3(THREADS), 0, b->stream, op, xp, static_cast<int>(p.h), static_cast<int>(p.w), static_cast<uint32_t>(groups), dwq, dh, d9);
         WB_LAUNCH_OK(b);
         return WB_OK;
     }
@@ -246,9 +246,9 @@ extern "C" int wb_col2im_into(WbBackend* b, const WbView* cols, const WbConvPara
         const FastDiv dwq(static_cast<uint32_t>(w / v)), dh(static_cast<uint32_t>(h));
         float* op = static_cast<float*>(out);
         const float* cp3 = static_cast<const float*>(cols->data) + cols->offset;
-        if (v == 4) col2im3_kernel<4><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
-        else if (v == 2) col2im3_kernel<2><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
-        else col2im3_kernel<1><<<grid3, THREADS, 0, b->stream>>>(op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
+        if (v == 4) wb_launch_pdl(col2im3_kernel<4>, dim3(grid3), dim3(THREADS), 0, b->stream, op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
+        else if (v == 2) wb_launch_pdl(col2im3_kernel<2>, dim3(grid3), dim3(THREADS), 0, b->stream, op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
+        else wb_launch_pdl(col2im3_kernel<1>, dim3(grid3), dim3(THREADS), 0, b->stream, op, cp3, static_cast<int>(h), static_cast<int>(w), static_cast<uint32_t>(groups), dwq, dh);
         WB_LAUNCH_OK(b);
         return WB_OK;
     }

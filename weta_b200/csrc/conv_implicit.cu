@@ -16,6 +16,7 @@ namespace {
 
 __global__ void __launch_bounds__(256) shift_copies_kernel(const float* __restrict__ in, float* __restrict__ left, float* __restrict__ right,
                                                            int64_t groups, int w4) {
+    wb_pdl_enter();
     // one thread per 4 consecutive pixels of a row (w is a multiple of 4)
     for (int64_t gi = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; gi < groups; gi += static_cast<int64_t>(gridDim.x) * 256) {
         const int xg = static_cast<int>(gi % w4);
@@ -33,6 +34,7 @@ __global__ void __launch_bounds__(256) shift_copies_kernel(const float* __restri
 // kind 3: kinds 0 and 1 in one launch, into dst and dst2 (both operands of a step from the same parameters)
 __global__ void __launch_bounds__(256) weight_reorder_kernel(const float* __restrict__ src, float* __restrict__ dst, float* __restrict__ dst2,
                                                              int o_n, int c_n, int kind) {
+    wb_pdl_enter();
     const int64_t total = static_cast<int64_t>(o_n) * c_n * 9;
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
@@ -59,7 +61,7 @@ int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, fl
     const int64_t groups = rows * (w / 4);
     if (groups == 0) return WB_OK;
     const int64_t blocks = std::min<int64_t>((groups + 255) / 256, static_cast<int64_t>(b->sm_count) * 16);
-    shift_copies_kernel<<<static_cast<unsigned>(blocks), 256, 0, b->stream>>>(in, left, right, groups, w / 4);
+    wb_launch_pdl(shift_copies_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, b->stream, in, left, right, groups, w / 4);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -67,7 +69,7 @@ int wb_conv3_shift_copies(WbBackend* b, const float* in, int64_t rows, int w, fl
 int wb_conv3_weight_reorder(WbBackend* b, int kind, const float* src, float* dst, int o_n, int c_n, float* dst2) {
     const int64_t total = static_cast<int64_t>(o_n) * c_n * 9;
     if (total == 0) return WB_OK;
-    weight_reorder_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, b->stream>>>(src, dst, dst2, o_n, c_n, kind);
+    wb_launch_pdl(weight_reorder_kernel, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, b->stream, src, dst, dst2, o_n, c_n, kind);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

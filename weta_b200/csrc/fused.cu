@@ -39,7 +39,7 @@ constexpr uint64_t GOLDEN = 0x9E3779B97F4A7C15ull;
 // relu_src != null the incoming value is additionally multiplied by step(relu_src) (ReLU backward folded in).
 __global__ void __launch_bounds__(THREADS) dropout_kernel(float* __restrict__ y, const float* __restrict__ x, const float* __restrict__ relu_src,
                                                            int64_t n, uint64_t kmin, float scale, uint64_t seed, int vec) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
     uint64_t z = seed + (static_cast<uint64_t>(i) + 1) * GOLDEN;
@@ -279,6 +279,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_kernel(const float* __rest
                                                               float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                               float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
                                                               unsigned int* __restrict__ counter) {
+    wb_pdl_enter();
     softmax_ce_rows(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
     if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
 }
@@ -287,6 +288,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg_kernel(const float* __
                                                                   int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                                   float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
                                                                   unsigned int* __restrict__ counter) {
+    wb_pdl_enter();
     softmax_ce_reg_rows<PER_LANE>(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
     if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
 }
@@ -295,6 +297,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* _
                                                                    int cols, float* __restrict__ probs, float* __restrict__ dz, int dz_pitch,
                                                                    float* __restrict__ row_loss, float gscale, float* __restrict__ mean_out,
                                                                    unsigned int* __restrict__ counter) {
+    wb_pdl_enter();
     softmax_ce_reg4_rows<PER4>(z, labels, rows, cols, probs, dz, dz_pitch, row_loss, gscale);
     if (mean_out) mean_by_last_block(row_loss, rows, mean_out, counter);
 }
@@ -304,7 +307,7 @@ __global__ void __launch_bounds__(THREADS) softmax_ce_reg4_kernel(const float* _
 // One thread per four elements (128-bit accesses); the last, partial group is done element by element.
 __global__ void __launch_bounds__(THREADS) adam_kernel(float* __restrict__ theta, const float* __restrict__ grad, float* __restrict__ m,
                                                         float* __restrict__ v, int64_t n, AdamK k, int vec) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x) * 4;
     if (i >= n) return;
     if (vec && i + 4 <= n) {
@@ -358,7 +361,7 @@ extern "C" int wb_dropout_fwd(WbBackend* b, const float* x, float* y, int64_t n,
     WbProfileScope ps(b, "dropout");
     int64_t threads = (n + 3) / 4;
     const int vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
-    dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+    wb_launch_pdl(dropout_kernel, dim3(static_cast<unsigned>((threads + THREADS - 1) / THREADS)), dim3(THREADS), 0, b->stream, 
         y, x, nullptr, n, dropout_threshold(p), p < 1.0 ? static_cast<float>(1.0 / (1.0 - p)) : 0.f, seed, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
@@ -371,7 +374,7 @@ extern "C" int wb_dropout_relu_bwd(WbBackend* b, const float* dy, const float* r
     WbProfileScope ps(b, "dropout_bwd");
     int64_t threads = (n + 3) / 4;
     const int vec = ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(relu_out)) & 15) == 0;
-    dropout_kernel<<<static_cast<unsigned>((threads + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+    wb_launch_pdl(dropout_kernel, dim3(static_cast<unsigned>((threads + THREADS - 1) / THREADS)), dim3(THREADS), 0, b->stream, 
         dx, dy, relu_out, n, dropout_threshold(p), p < 1.0 ? static_cast<float>(1.0 / (1.0 - p)) : 0.f, seed, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
@@ -411,12 +414,12 @@ int wb_softmax_ce_pitched(WbBackend* b, const float* logits, const int64_t* labe
     unsigned int* counter = nullptr;
     if (mean_loss) WB_TRY(wb_block_counters(b, &counter));
     float* mo = mean_loss;
-    if (v4 && cols > 32 && cols <= 128) softmax_ce_reg4_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
-    else if (v4 && cols > 128 && cols <= 1024) softmax_ce_reg4_kernel<8><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
-    else if (cols <= 32) softmax_ce_reg_kernel<1><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
-    else if (cols <= 128) softmax_ce_reg_kernel<4><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
-    else if (cols <= 1024) softmax_ce_reg_kernel<32><<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
-    else softmax_ce_kernel<<<grid, THREADS, 0, b->stream>>>(logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    if (v4 && cols > 32 && cols <= 128) wb_launch_pdl(softmax_ce_reg4_kernel<1>, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (v4 && cols > 128 && cols <= 1024) wb_launch_pdl(softmax_ce_reg4_kernel<8>, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 32) wb_launch_pdl(softmax_ce_reg_kernel<1>, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 128) wb_launch_pdl(softmax_ce_reg_kernel<4>, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else if (cols <= 1024) wb_launch_pdl(softmax_ce_reg_kernel<32>, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
+    else wb_launch_pdl(softmax_ce_kernel, dim3(grid), dim3(THREADS), 0, b->stream, logits, labels, rows, ic, probs, dlogits, ip, rl, gscale, mo, counter);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -441,7 +444,7 @@ extern "C" int wb_adam_step(WbBackend* b, float* theta, const float* grad, float
     const int vec = ((reinterpret_cast<uintptr_t>(theta) | reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(m) |
                       reinterpret_cast<uintptr_t>(v)) & 15) == 0;
     const int64_t groups = (n + 3) / 4;
-    adam_kernel<<<static_cast<unsigned>((groups + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(theta, grad, m, v, n, k, vec);
+    wb_launch_pdl(adam_kernel, dim3(static_cast<unsigned>((groups + THREADS - 1) / THREADS)), dim3(THREADS), 0, b->stream, theta, grad, m, v, n, k, vec);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

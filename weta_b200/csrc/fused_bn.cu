@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(THREADS) bn_stats_from_sums_kernel(const float
                                                                  float momentum, float one_minus_momentum, float* __restrict__ mean,
                                                                  float* __restrict__ rstd, float* __restrict__ running_mean,
                                                                  float* __restrict__ running_var) {
+    wb_pdl_enter();
     const int c = blockIdx.x;
     const int64_t count = n_img * hw;
     const double e1 = sums[2 * c] / static_cast<double>(count), e2 = sums[2 * c + 1] / static_cast<double>(count);
@@ -255,6 +256,7 @@ __global__ void __launch_bounds__(THREADS) bn_bwd_stats_kernel(const float* __re
 // fixed shuffle tree (one order, every run).
 __global__ void __launch_bounds__(128) bn_bwd_finalize_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ dgamma,
                                                               float* __restrict__ dbeta) {
+    wb_pdl_enter();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= c_total) return;
     double s1 = 0.0, s2 = 0.0;
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_quad_kernel(float* _
                                                                          const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                          int c_total, int h, int w, uint32_t total, FastDiv div_ipp,
                                                                          FastDiv div_owq, FastDiv div_c) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const uint32_t owq = static_cast<uint32_t>(w >> 3), ipp = static_cast<uint32_t>(h >> 1) * owq;
     const int64_t plane_elems = static_cast<int64_t>(h) * w;
     const uint32_t stride = gridDim.x * THREADS;
@@ -362,7 +364,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_fwd_kernel(float* __rest
                                                                     const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                     const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                     int c_total, int h, int w, int64_t total) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     int64_t i = static_cast<int64_t>(blockIdx.x) * THREADS + threadIdx.x;
     if (i >= total) return;
     const int ow = w >> 1, oh = h >> 1;
@@ -410,6 +412,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_stats_kernel(const f
                                                                           const float* __restrict__ mean, const float* __restrict__ rstd,
                                                                           const float* __restrict__ gamma, const float* __restrict__ beta,
                                                                           int64_t n_img, int c_total, int h, int w, double* __restrict__ part) {
+    wb_pdl_enter();
     const int c = blockIdx.x;
     const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
     const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
@@ -460,7 +463,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_dx_kernel(float* __r
                                                                        const float* __restrict__ beta, const float* __restrict__ dgamma,
                                                                        const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
                                                                        int w, float inv_count, double* __restrict__ bias_part) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int c = blockIdx.x;
     const float m = mean[c], r = rstd[c], g = gamma[c], b = beta[c];
     const float k1 = dbeta[c] * inv_count, k2 = dgamma[c] * inv_count, gr = g * r;
@@ -519,6 +522,7 @@ __global__ void __launch_bounds__(THREADS) bn_relu_pool_bwd_sums_pooled_kernel(c
                                                                                 const float* __restrict__ rstd, const float* __restrict__ gamma,
                                                                                 const float* __restrict__ beta, int64_t n_img, int c_total, int h,
                                                                                 int w, double* __restrict__ part, int slabs) {
+    wb_pdl_enter();
     const int ow = w >> 1, oh = h >> 1, pooled = ow * oh;
     const int64_t per = (n_img + slabs - 1) / slabs;
     const int lane = threadIdx.x & 31;
@@ -608,7 +612,7 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
                                                                             const float* __restrict__ dbeta, int64_t n_img, int c_total, int h,
                                                                             int w, float inv_count, double* __restrict__ part, FastDiv div_pairs,
                                                                             FastDiv div_owp, int slabs, int skip_pooled_ok) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     // Work items are (channel, slab of images) pairs, many more than blocks, walked round-robin: every SM stays
     // equally loaded whatever the channel count.  The two windows a thread owns are computed side by side in
     // packed f32x2 arithmetic (.x = left window, .y = right window).
@@ -734,7 +738,7 @@ __global__ void __launch_bounds__(THREADS, 5) bn_relu_pool_bwd_pair_kernel(float
 
 // One warp per channel, as bn_bwd_finalize_kernel.
 __global__ void __launch_bounds__(128) sum_parts_kernel(const double* __restrict__ part, int splits, int c_total, float* __restrict__ out) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (c >= c_total) return;
     double s = 0.0;
@@ -884,7 +888,7 @@ extern "C" int wb_bn2d_bwd(WbBackend* b, const float* x, const float* dy, int64_
     bn_bwd_stats_kernel<<<dim3(static_cast<unsigned>(c), splits), THREADS, 0, b->stream>>>(x, dy, save_mean, save_rstd, n, static_cast<int>(c), hw,
                                                                                           static_cast<double*>(s));
     WB_LAUNCH_OK(b);
-    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
+    wb_launch_pdl(bn_bwd_finalize_kernel, dim3(static_cast<unsigned>((c + 3) / 4)), dim3(128), 0, b->stream, static_cast<double*>(s), splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
     unsigned gx = static_cast<unsigned>(std::max<int64_t>(1, std::min<int64_t>((hw / 4 + THREADS - 1) / THREADS, 64)));
     for (int64_t p0 = 0; p0 < n * c; p0 += 65535 / c * c) {
@@ -911,7 +915,7 @@ int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t
         // (sum, sum of squares) per channel already accumulated by the kernel that wrote x
         WB_REQUIRE(n * h * w > 0, WB_ERR_INVALID, "wb_bn_relu_pool_fwd: empty input");
         // One block per channel: statistics straight from the sums, or recomputed from x where the sums cancel.
-        bn_stats_from_sums_kernel<<<static_cast<unsigned>(c), THREADS, 0, b->stream>>>(x, channel_sums, sums_pivot, n, static_cast<int>(c), h * w,
+        wb_launch_pdl(bn_stats_from_sums_kernel, dim3(static_cast<unsigned>(c)), dim3(THREADS), 0, b->stream, x, channel_sums, sums_pivot, n, static_cast<int>(c), h * w,
                                                                                   static_cast<float>(eps), static_cast<float>(momentum),
                                                                                   static_cast<float>(1.0 - momentum), save_mean, save_rstd, running_mean,
                                                                                   running_var);
@@ -932,15 +936,15 @@ int wb_bn_relu_pool_fwd_shifted(WbBackend* b, const float* x, int64_t n, int64_t
         const FastDiv div_ipp(static_cast<uint32_t>((h / 2) * (w / 8))), div_owq(static_cast<uint32_t>(w / 8)), div_c(static_cast<uint32_t>(c));
         const unsigned grid = static_cast<unsigned>(std::min<int64_t>((items + THREADS - 1) / THREADS, static_cast<int64_t>(b->sm_count) * 8));
         if (y_left)
-            bn_relu_pool_fwd_quad_kernel<true><<<grid, THREADS, 0, b->stream>>>(y_pooled, y_left, y_right, x, save_mean, save_rstd, gamma, beta,
+            wb_launch_pdl(bn_relu_pool_fwd_quad_kernel<true>, dim3(grid), dim3(THREADS), 0, b->stream, y_pooled, y_left, y_right, x, save_mean, save_rstd, gamma, beta,
                                                                                static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
                                                                                items, div_ipp, div_owq, div_c);
         else
-            bn_relu_pool_fwd_quad_kernel<false><<<grid, THREADS, 0, b->stream>>>(y_pooled, nullptr, nullptr, x, save_mean, save_rstd, gamma, beta,
+            wb_launch_pdl(bn_relu_pool_fwd_quad_kernel<false>, dim3(grid), dim3(THREADS), 0, b->stream, y_pooled, nullptr, nullptr, x, save_mean, save_rstd, gamma, beta,
                                                                                 static_cast<int>(c), static_cast<int>(h), static_cast<int>(w),
                                                                                 items, div_ipp, div_owq, div_c);
     } else {
-        bn_relu_pool_fwd_kernel<<<static_cast<unsigned>((total + THREADS - 1) / THREADS), THREADS, 0, b->stream>>>(
+        wb_launch_pdl(bn_relu_pool_fwd_kernel, dim3(static_cast<unsigned>((total + THREADS - 1) / THREADS)), dim3(THREADS), 0, b->stream, 
             y_pooled, x, save_mean, save_rstd, gamma, beta, static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), total);
     }
     WB_LAUNCH_OK(b);
@@ -1003,34 +1007,34 @@ int wb_bn_relu_pool_bwd_shifted(WbBackend* b, const float* x, const float* dy_po
     if (from_pooled) {
         const int64_t warps_needed = static_cast<int64_t>(c) * splits;
         const unsigned grid = static_cast<unsigned>(std::min<int64_t>((warps_needed + THREADS / 32 - 1) / (THREADS / 32), 8LL * b->sm_count));
-        bn_relu_pool_bwd_sums_pooled_kernel<<<grid, THREADS, 0, b->stream>>>(y_pooled, dy_pooled, x, save_mean, save_rstd, gamma, beta, n,
+        wb_launch_pdl(bn_relu_pool_bwd_sums_pooled_kernel, dim3(grid), dim3(THREADS), 0, b->stream, y_pooled, dy_pooled, x, save_mean, save_rstd, gamma, beta, n,
                                                                             static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), part, splits);
     } else if (pairs)
-        bn_relu_pool_bwd_pair_kernel<false, false><<<flat_blocks, THREADS, 0, b->stream>>>(
+        wb_launch_pdl(bn_relu_pool_bwd_pair_kernel<false, false>, dim3(flat_blocks), dim3(THREADS), 0, b->stream, 
             nullptr, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, nullptr, nullptr, n, static_cast<int>(c), static_cast<int>(h),
             static_cast<int>(w), inv_count, part, div_pairs, div_owp, splits, 0);
     else
-        bn_relu_pool_bwd_stats_kernel<<<grid, THREADS, 0, b->stream>>>(x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
+        wb_launch_pdl(bn_relu_pool_bwd_stats_kernel, dim3(grid), dim3(THREADS), 0, b->stream, x, dy_pooled, save_mean, save_rstd, gamma, beta, n, static_cast<int>(c),
                                                                       static_cast<int>(h), static_cast<int>(w), part);
     WB_LAUNCH_OK(b);
-    bn_bwd_finalize_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(part, splits, static_cast<int>(c), dgamma, dbeta);
+    wb_launch_pdl(bn_bwd_finalize_kernel, dim3(static_cast<unsigned>((c + 3) / 4)), dim3(128), 0, b->stream, part, splits, static_cast<int>(c), dgamma, dbeta);
     WB_LAUNCH_OK(b);
     if (!dx) return WB_OK;
     if (pairs && dx_left)
-        bn_relu_pool_bwd_pair_kernel<true, true><<<flat_blocks, THREADS, 0, b->stream>>>(
+        wb_launch_pdl(bn_relu_pool_bwd_pair_kernel<true, true>, dim3(flat_blocks), dim3(THREADS), 0, b->stream, 
             dx, dx_left, dx_right, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
             static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits, 0);
     else if (pairs)
-        bn_relu_pool_bwd_pair_kernel<true, false><<<flat_blocks, THREADS, 0, b->stream>>>(
+        wb_launch_pdl(bn_relu_pool_bwd_pair_kernel<true, false>, dim3(flat_blocks), dim3(THREADS), 0, b->stream, 
             dx, nullptr, nullptr, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n, static_cast<int>(c), static_cast<int>(h),
             static_cast<int>(w), inv_count, dbias_conv ? bias_part : nullptr, div_pairs, div_owp, splits, 0);
     else
-        bn_relu_pool_bwd_dx_kernel<<<grid, THREADS, 0, b->stream>>>(dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
+        wb_launch_pdl(bn_relu_pool_bwd_dx_kernel, dim3(grid), dim3(THREADS), 0, b->stream, dx, x, dy_pooled, save_mean, save_rstd, gamma, beta, dgamma, dbeta, n,
                                                                    static_cast<int>(c), static_cast<int>(h), static_cast<int>(w), inv_count,
                                                                    dbias_conv ? bias_part : nullptr);
     WB_LAUNCH_OK(b);
     if (dbias_conv) {
-        sum_parts_kernel<<<static_cast<unsigned>((c + 3) / 4), 128, 0, b->stream>>>(bias_part, splits, static_cast<int>(c), dbias_conv);
+        wb_launch_pdl(sum_parts_kernel, dim3(static_cast<unsigned>((c + 3) / 4)), dim3(128), 0, b->stream, bias_part, splits, static_cast<int>(c), dbias_conv);
         WB_LAUNCH_OK(b);
     }
     return WB_OK;

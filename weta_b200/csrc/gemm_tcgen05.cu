@@ -102,7 +102,7 @@ int make_map(GemmState* st, const WbGemmOperand& o, int64_t batch, int box_rows,
 // Split-K finish: out = epilogue(sum over splits of partial).
 __global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
                                                      int m, int n, tc::Epilogue ep) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
     int64_t per = static_cast<int64_t>(m) * n;
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(256) splitk_reduce(const float* __restrict__ p
 // splits in ascending order, the lanes' sums are combined by a fixed shuffle tree: one order, every run).
 __global__ void __launch_bounds__(256) splitk_reduce_warp(const float* __restrict__ part, int splits, int64_t split_stride, int64_t total,
                                                           int m, int n, tc::Epilogue ep) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (i >= total) return;
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_warp(const float* __restric
 // hi = x with the 13 low mantissa bits cleared (exactly a tf32 value), lo = x - hi (exact in f32).
 __global__ void __launch_bounds__(256) split_hi_lo(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
                                                    int64_t nb, int64_t outer, int64_t inner, int64_t bs, int64_t ld, int64_t inner_p) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     int64_t total = nb * outer * inner_p;
     if (i >= total) return;
@@ -369,10 +369,10 @@ int run_tiles(WbBackend* be, GemmState* st, tc::Args& args, int m, int n, int64_
     if (status == WB_OK && splits > 1 && !cluster_splits) {
         const int64_t total = grid_batch * static_cast<int64_t>(m) * n;
         if (splits >= 32 && total <= (1 << 16))
-            splitk_reduce_warp<<<static_cast<unsigned>((total * 32 + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits,
+            wb_launch_pdl(splitk_reduce_warp, dim3(static_cast<unsigned>((total * 32 + 255) / 256)), dim3(256), 0, be->stream, static_cast<const float*>(part), splits,
                                                                                                       total, total, m, n, ep);
         else
-            splitk_reduce<<<static_cast<unsigned>((total + 255) / 256), 256, 0, be->stream>>>(static_cast<const float*>(part), splits, total,
+            wb_launch_pdl(splitk_reduce, dim3(static_cast<unsigned>((total + 255) / 256)), dim3(256), 0, be->stream, static_cast<const float*>(part), splits, total,
                                                                                             total, m, n, ep);
         cudaError_t e = cudaPeekAtLastError();
         if (e != cudaSuccess) { wb_set_error("split-K reduce launch failed: %s", cudaGetErrorString(e)); status = WB_ERR_CUDA; }
@@ -459,7 +459,7 @@ int wb_tc_gemm(WbBackend* be, WbGemmOperand A, WbGemmOperand B, int64_t batch_in
             WB_TRY(wb_arena_alloc(be, static_cast<size_t>(2 * count) * sizeof(float), buf, klass));
             float* h = static_cast<float*>(*buf);
             float* l = h + count;
-            split_hi_lo<<<static_cast<unsigned>((count + 255) / 256), 256, 0, be->stream>>>(o.ptr, h, l, nb, outer, inner, o.batch_stride,
+            wb_launch_pdl(split_hi_lo, dim3(static_cast<unsigned>((count + 255) / 256)), dim3(256), 0, be->stream, o.ptr, h, l, nb, outer, inner, o.batch_stride,
                                                                                           o.ld, inner_p);
             WB_LAUNCH_OK(be);
             oh = o; ol = o;

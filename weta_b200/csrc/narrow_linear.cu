@@ -25,6 +25,7 @@ __device__ __forceinline__ float operand(float v, int tf32) { return tf32 ? __ui
 template <int S>
 __global__ void __launch_bounds__(512) narrow_wgrad_kernel(float* __restrict__ dw, const float* __restrict__ dy, int64_t dy_pitch,
                                                             const float* __restrict__ x, int n, int in, int out, int tf32) {
+    wb_pdl_enter();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int j = blockIdx.x * 32 + lane;
     const int per = (n + 15) / 16, b0 = min(n, warp * per), b1 = min(n, b0 + per);
@@ -73,7 +74,7 @@ __global__ void __launch_bounds__(512) narrow_wgrad_kernel(float* __restrict__ d
 template <int S>
 __global__ void __launch_bounds__(256) narrow_dgrad_kernel(float* __restrict__ dx, const float* __restrict__ dy, int64_t dy_pitch,
                                                             const float* __restrict__ w, int n, int in, int out, int tf32) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int64_t t = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     const int q = in >> 2;  // in % 4 == 0
     if (t >= static_cast<int64_t>(n) * q) return;
@@ -102,8 +103,8 @@ bool wb_narrow_linear_ok(int64_t n, int64_t in, int64_t out, const float* x, con
 int wb_narrow_linear_wgrad(WbBackend* b, int mode, const float* dy, int64_t dy_pitch, const float* x, int n, int in, int out, float* dw) {
     const int tf32 = mode == WB_MM_TF32;
     const unsigned grid = static_cast<unsigned>((in + 31) / 32);
-    if (out <= 10) narrow_wgrad_kernel<10><<<grid, 512, 0, b->stream>>>(dw, dy, dy_pitch, x, n, in, out, tf32);
-    else narrow_wgrad_kernel<16><<<grid, 512, 0, b->stream>>>(dw, dy, dy_pitch, x, n, in, out, tf32);
+    if (out <= 10) wb_launch_pdl(narrow_wgrad_kernel<10>, dim3(grid), dim3(512), 0, b->stream, dw, dy, dy_pitch, x, n, in, out, tf32);
+    else wb_launch_pdl(narrow_wgrad_kernel<16>, dim3(grid), dim3(512), 0, b->stream, dw, dy, dy_pitch, x, n, in, out, tf32);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }
@@ -112,8 +113,8 @@ int wb_narrow_linear_dgrad(WbBackend* b, int mode, const float* dy, int64_t dy_p
     const int tf32 = mode == WB_MM_TF32;
     const int64_t threads = static_cast<int64_t>(n) * (in / 4);
     const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
-    if (out <= 10) narrow_dgrad_kernel<10><<<grid, 256, 0, b->stream>>>(dx, dy, dy_pitch, w, n, in, out, tf32);
-    else narrow_dgrad_kernel<16><<<grid, 256, 0, b->stream>>>(dx, dy, dy_pitch, w, n, in, out, tf32);
+    if (out <= 10) wb_launch_pdl(narrow_dgrad_kernel<10>, dim3(grid), dim3(256), 0, b->stream, dx, dy, dy_pitch, w, n, in, out, tf32);
+    else wb_launch_pdl(narrow_dgrad_kernel<16>, dim3(grid), dim3(256), 0, b->stream, dx, dy, dy_pitch, w, n, in, out, tf32);
     WB_LAUNCH_OK(b);
     return WB_OK;
 }

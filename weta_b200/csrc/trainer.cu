@@ -186,7 +186,7 @@ int gemm(WbTrainer* t, WbGemmOperand A, WbGemmOperand B, int64_t batch, int m, i
 // strip's slabs in ascending order.
 __global__ void __launch_bounds__(256) column_sum_kernel(const float* __restrict__ src, int64_t rows, int64_t cols, int64_t pitch, int64_t per,
                                                          float* __restrict__ part, unsigned int* __restrict__ counter, float* __restrict__ dst) {
-    wb_launch_dependents();
+    wb_pdl_enter();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t col = static_cast<int64_t>(blockIdx.x) * 32 + lane;
     const int64_t r0 = static_cast<int64_t>(blockIdx.y) * per, r1 = min(rows, r0 + per);
@@ -238,7 +238,7 @@ int column_sum(WbTrainer* t, const float* src, int64_t rows, int64_t cols, int64
     WB_TRY(wb_scratch(b, static_cast<size_t>(slabs) * cols * sizeof(float), &scratch));
     unsigned int* counters = nullptr;
     WB_TRY(wb_block_counters(b, &counters));
-    column_sum_kernel<<<dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs)), 256, 0, b->stream>>>(src, rows, cols, pitch, per,
+    wb_launch_pdl(column_sum_kernel, dim3(dim3(static_cast<unsigned>(col_blocks), static_cast<unsigned>(slabs))), dim3(256), 0, b->stream, src, rows, cols, pitch, per,
                                                                                                                       static_cast<float*>(scratch), counters, dst);
     WB_LAUNCH_OK(b);
     return WB_OK;
