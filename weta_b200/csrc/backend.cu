@@ -5,6 +5,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include <atomic>
 #include "common.h"
 
 static thread_local char g_err[1024] = "";
@@ -168,6 +169,21 @@ void wb_arena_free(WbBackend* b, void* p, size_t klass) {
     std::lock_guard<std::mutex> g(b->mu);
     b->free_blocks.emplace(klass, p);
 }
+
+namespace {
+std::atomic<int> g_pdl_state{0};  // 0: not looked up, 1: allowed, 2: off
+}
+bool wb_pdl_allowed() {
+    int v = g_pdl_state.load(std::memory_order_relaxed);
+    if (v == 0) {
+        const char* e = std::getenv("WETA_B200_NO_PDL");
+        int want = (e && e[0] == '1') ? 2 : 1, expected = 0;
+        g_pdl_state.compare_exchange_strong(expected, want, std::memory_order_relaxed);
+        v = g_pdl_state.load(std::memory_order_relaxed);
+    }
+    return v == 1;
+}
+void wb_pdl_disallow() { g_pdl_state.store(2, std::memory_order_relaxed); }
 
 int wb_block_counters(WbBackend* b, unsigned int** out) {
     if (!b->narrow_counters) {

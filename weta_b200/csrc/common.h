@@ -169,7 +169,12 @@ void wb_make_plan(const WbView* const* ops, int nops, WbIterPlan* plan);
 // the stream is still running; its first statement is wb_pdl_enter(), which waits until that kernel has completed and
 // its writes are visible, and then lets the kernel after it be scheduled in the same way.  What overlaps is the launch
 // itself (and, in the tensor-core GEMM, the preamble it runs before its own wait): one to two microseconds per kernel,
-// which is most of a small model's step.  Dependencies through events are not relaxed.  WETA_B200_NO_PDL=1 launches plainly.
+// which is most of a small model's step.  Dependencies through events are not relaxed.
+// Process-wide switch (backend.cu): off with WETA_B200_NO_PDL=1, and turned off by a data-parallel handle over more than
+// one rank: with the gradient exchange running beside backward, blocks that sit on an SM waiting for the kernel before
+// them take room from the exchange kernels (2 GPUs: 1.057 M samples/s without against 1.036 M with).
+bool wb_pdl_allowed();
+void wb_pdl_disallow();
 #ifdef __CUDACC__
 __device__ __forceinline__ void wb_pdl_enter() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -177,7 +182,7 @@ __device__ __forceinline__ void wb_pdl_enter() {
 }
 template <class... Params, class... Args>
 inline cudaError_t wb_launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
-    static const bool plain = [] { const char* e = std::getenv("WETA_B200_NO_PDL"); return e && e[0] == '1'; }();
+    const bool plain = !wb_pdl_allowed();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = block;

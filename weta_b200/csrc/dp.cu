@@ -608,6 +608,7 @@ extern "C" int wb_dp_create(WbTrainer* t, const WbDpId* id, int rank, int world,
     if (world == 1) {
         dp->mode = WB_DP_ALLREDUCE;
     } else {
+        wb_pdl_disallow();  // see common.h: dependents parked on the SMs slow the exchange kernels that run beside backward
         dp->nccl = load_nccl();
         if (!dp->nccl) return fail(WB_ERR_UNSUPPORTED);
         ncclUniqueId nid;

@@ -170,8 +170,8 @@ int launch_tc(WbBackend* be, GemmState* st, const tc::Args& args, dim3 grid) {
     }
     // Every launch is a programmatic dependent of the kernel before it in the stream (the kernel waits with
     // griddepcontrol.wait after its preamble, see tc_gemm.cuh); CTA pairs and cluster split-K add the cluster size
-    // (2; args.splits).  WETA_B200_NO_PDL=1 launches plainly.
-    static const bool no_pdl = [] { const char* e = std::getenv("WETA_B200_NO_PDL"); return e && e[0] == '1'; }();
+    // (2; args.splits).
+    const bool no_pdl = !wb_pdl_allowed();
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(tc::threads_for(EPW));
