@@ -413,6 +413,27 @@ def test_step_replayed_from_a_graph_equals_the_launch_by_launch_step(gpu, model)
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("model", ["mlp", "cnn", "wide"])
+def test_programmatic_dependent_launch_changes_no_result(gpu, model):
+    """The trainer's kernels are launched as programmatic dependents of the kernel before them (their launch overlaps that
+    kernel's tail; each waits for it before touching memory).  Six steps with and without the attribute, in two child
+    processes: every loss and every parameter bit for bit the same."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "pdl_worker.py")
+    out = {}
+    for off in ("0", "1"):
+        env = dict(os.environ, WETA_B200_NO_PDL=off)
+        r = subprocess.run([sys.executable, worker, model], env=env, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        out[off] = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["0"]["losses"] == out["1"]["losses"]
+    assert out["0"]["params"] == out["1"]["params"]
+
+
 def test_graph_is_captured_again_when_the_staged_batch_moves(gpu):
     """The capture bakes in the address of the staged batch.  wb_trainer_set_input points the trainer at another
     device buffer: the next step must not replay the old graph on the old buffer."""
