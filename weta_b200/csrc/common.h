@@ -167,7 +167,7 @@ void wb_make_plan(const WbView* const* ops, int nops, WbIterPlan* plan);
 // Division of a 32-bit index by a launch-invariant divisor, as a multiply-high (exact for n < 2^31).
 // Programmatic dependent launch.  A kernel launched with wb_launch_pdl may be scheduled while the kernel before it in
 // the stream is still running; its first statement is wb_pdl_enter(), which waits until that kernel has completed and
-// its writes are visible, and then lets the kernel after it be scheduled in the same way.  What overlaps is the launch
+// its writes are visible, and then (in a kernel of few blocks) lets the kernel after it be scheduled in the same way.  What overlaps is the launch
 // itself (and, in the tensor-core GEMM, the preamble it runs before its own wait): one to two microseconds per kernel,
 // which is most of a small model's step.  Dependencies through events are not relaxed.
 // Process-wide switch (backend.cu): off with WETA_B200_NO_PDL=1, and turned off by a data-parallel handle over more than
@@ -178,7 +178,10 @@ void wb_pdl_disallow();
 #ifdef __CUDACC__
 __device__ __forceinline__ void wb_pdl_enter() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // A small grid is a short kernel: the next kernel's blocks may as well be scheduled now.  A large one releases its
+    // dependents as its blocks exit: blocks parked on the SMs for the length of a long kernel slow it down (the
+    // 4096-sample step of the wide CNN lost 3 % when every kernel released its dependents at once).
+    if (gridDim.x * gridDim.y * gridDim.z <= 296u) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 template <class... Params, class... Args>
 inline cudaError_t wb_launch_pdl(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {

@@ -317,9 +317,12 @@ __global__ void __launch_bounds__(threads_for(EPW), 1) gemm_tf32_kernel(const __
     bool ok = true;
     // Launched as a programmatic dependent of the kernel before it in the stream: everything above (barriers, TMEM,
     // and the launch itself) may run while that kernel is still finishing; nothing below touches global memory before
-    // it has completed and its writes are visible.  Kernels after this one may start their own preamble at once.
+    // it has completed and its writes are visible.
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // Only a short product (one tile per CTA at most, a short contraction) releases its dependents now; blocks parked
+    // on the SMs for the length of a long one would slow it down, so that one releases them as its CTAs exit.
+    if (args.total_tiles <= static_cast<int>(gridDim.x) && args.k_blocks * args.num_segments <= 64)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // Tile t -> (n block, m block, z = batch * splits + split); n fastest so neighbouring CTAs share A.
     auto decode = [&](int t, int& m0, int& n0, int& batch, int& split, int& kb_begin, int& kb_end) {
